@@ -1,0 +1,86 @@
+"""ctypes binding of ``libdyllm_b200.so`` (the C ABI declared in ``include/dyllm_b200.h``).
+
+There is no fallback: if the shared library is missing or a call returns a non-zero status a
+``RuntimeError`` is raised, as the reference's pybind11 extensions do through ``TORCH_CHECK``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libdyllm_b200.so")
+
+P, I, F, Z = c_void_p, c_int, c_float, c_size_t
+
+# name -> (restype, argtypes); mirrors include/dyllm_b200.h one to one.
+SIGNATURES: dict[str, tuple] = {
+    "dyllm_version": (I, []),
+    "dyllm_last_error": (c_char_p, []),
+    "dyllm_device_status": (I, []),
+    "dyllm_context_stats": (I, [P, P, P, I, I, I, P]),
+    "dyllm_cosine_mask": (I, [P, P, I, F, P]),
+    "dyllm_salient_select_workspace_bytes": (Z, [I]),
+    "dyllm_salient_select": (I, [P, I, F, P, I, P, P, P, P, P, P, P, P, Z, P]),
+    "dyllm_fused_offset": (I, [P, P, P, P, I, P, I, P]),
+    "dyllm_cache_get_seqs": (I, [P, P, P, P, P, I, I, I, I, P]),
+    "dyllm_cache_get_block": (I, [P, P, P, P, P, P, I, I, I, I, P]),
+    "dyllm_cache_reset_full": (I, [P, P, P, P, P, I, I, I, I, P]),
+    "dyllm_cache_reset_block": (I, [P, P, P, P, P, P, I, I, I, I, P]),
+    "dyllm_cache_scatter_update": (I, [P, P, P, P, I, P, P, I, I, P, I, I, P]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m dyllm_b200.build` "
+                "(dyllm_b200 has no CPU or PyTorch fallback)"
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+    return _lib
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    """Device address of a tensor (None -> NULL)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream_ptr(device: torch.device | None = None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def call(name: str, *args) -> None:
+    """Calls a status-returning entry point and raises RuntimeError on failure."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = lib.dyllm_last_error().decode(errors="replace")
+        raise RuntimeError(f"{name} failed with status {rc}: {msg}")
+
+
+def require_cuda(t: torch.Tensor, name: str, dtype: torch.dtype | None = None, dim: int | None = None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise RuntimeError(f"{name} must be {dim}-D, got {t.dim()}-D")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")

@@ -1,0 +1,177 @@
+// Per-sequence activation cache: row copies between the packed step buffers and the cache.
+//
+// One warp moves one row with 16-byte accesses, four independent loads in flight per lane; the
+// sequence of a packed row is found by binary search in the prefix-sum array.  All kernels are
+// HBM-bound: 2 * width * elem_bytes bytes per row (one read, one write).
+#include "common.cuh"
+
+namespace dyllm {
+namespace {
+
+constexpr int kCopyWarps = 8;
+
+__device__ __forceinline__ void copy_row_vec16(const uint4* __restrict__ src, uint4* __restrict__ dst, int vecs,
+                                               int lane) {
+  int v = lane;
+  for (; v + 96 < vecs; v += 128) {
+    const uint4 a = __ldg(src + v), b = __ldg(src + v + 32), c = __ldg(src + v + 64), d = __ldg(src + v + 96);
+    dst[v] = a;
+    dst[v + 32] = b;
+    dst[v + 64] = c;
+    dst[v + 96] = d;
+  }
+  for (; v < vecs; v += 32)
+    dst[v] = __ldg(src + v);
+}
+
+template <typename T>
+__device__ __forceinline__ int seq_of_row(const T* __restrict__ cu, int batch, int64_t row) {
+  // largest b in [0, batch) with cu[b] <= row
+  int lo = 0, hi = batch;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<int64_t>(cu[mid + 1]) <= row)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  return lo < batch ? lo : batch - 1;
+}
+
+// TO_CACHE = false: packed[p] = cache[...]; true: cache[...] = packed[p].
+// cu_k == nullptr: rows of sequence b start at the first cache row of the sequence;
+// otherwise at its last (cu_pack[b+1] - cu_pack[b]) rows.
+template <bool TO_CACHE>
+__global__ void __launch_bounds__(kCopyWarps * 32)
+cache_rows_kernel(uint4* __restrict__ cache, uint4* __restrict__ packed, const int64_t* __restrict__ seq_starts,
+                  const int32_t* __restrict__ cu_pack, const int32_t* __restrict__ cu_k,
+                  const int64_t* __restrict__ seq_ids, int batch, int packed_rows, int vecs) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int live_rows = min(packed_rows, cu_pack[batch]);
+  for (int p = blockIdx.x * kCopyWarps + warp; p < live_rows; p += gridDim.x * kCopyWarps) {
+    const int b = seq_of_row(cu_pack, batch, p);
+    const int first = cu_pack[b];
+    if (p < first)
+      continue;  // rows below cu_pack[0]
+    int64_t cache_row = seq_starts[seq_ids[b]] + (p - first);
+    if (cu_k)
+      cache_row += (cu_k[b + 1] - cu_k[b]) - (cu_pack[b + 1] - first);
+    uint4* c = cache + cache_row * vecs;
+    uint4* q = packed + static_cast<int64_t>(p) * vecs;
+    if (TO_CACHE)
+      copy_row_vec16(q, c, vecs, lane);
+    else
+      copy_row_vec16(c, q, vecs, lane);
+  }
+}
+
+template <typename CuT>
+__global__ void __launch_bounds__(kCopyWarps * 32)
+scatter_rows_kernel(uint4* __restrict__ cache, const uint4* __restrict__ new_rows,
+                    const int64_t* __restrict__ row_idx, const CuT* __restrict__ cu,
+                    const int64_t* __restrict__ seq_starts, const int64_t* __restrict__ seq_ids, int batch,
+                    int num_rows, const int32_t* __restrict__ num_rows_dev, int vecs) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
+  for (int m = blockIdx.x * kCopyWarps + warp; m < n; m += gridDim.x * kCopyWarps) {
+    const int64_t r = row_idx[m];
+    const int b = seq_of_row(cu, batch, r);
+    const int64_t dest = seq_starts[seq_ids[b]] + (r - static_cast<int64_t>(cu[b]));
+    copy_row_vec16(new_rows + static_cast<int64_t>(m) * vecs, cache + dest * vecs, vecs, lane);
+  }
+}
+
+int check_common(const char* name, const void* cache, const void* other, const int64_t* seq_starts,
+                 const void* cu, const int64_t* seq_ids, int batch, int rows, int width, int elem_bytes) {
+  DYLLM_REQUIRE(batch >= 0 && rows >= 0 && width > 0 && elem_bytes > 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "%s: batch %d rows %d width %d elem_bytes %d", name, batch, rows, width, elem_bytes);
+  DYLLM_REQUIRE((static_cast<int64_t>(width) * elem_bytes) % 16 == 0, DYLLM_ERR_UNSUPPORTED,
+                "%s: row size %lld bytes is not a multiple of 16", name,
+                static_cast<long long>(width) * elem_bytes);
+  if (rows == 0 || batch == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(cache && other && seq_starts && cu && seq_ids, DYLLM_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(other) & 15) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "%s: buffers must be 16-byte aligned", name);
+  return DYLLM_OK;
+}
+
+template <bool TO_CACHE>
+int launch_rows(const char* name, void* cache, void* packed, const int64_t* seq_starts, const int32_t* cu_pack,
+                const int32_t* cu_k, const int64_t* seq_ids, int batch, int rows, int width, int elem_bytes,
+                void* stream) {
+  int rc = check_common(name, cache, packed, seq_starts, cu_pack, seq_ids, batch, rows, width, elem_bytes);
+  if (rc != DYLLM_OK || rows == 0 || batch == 0)
+    return rc;
+  const int vecs = static_cast<int>(static_cast<int64_t>(width) * elem_bytes / 16);
+  const int blocks = min(cdiv_i(rows, kCopyWarps), sm_count() * 8);
+  cache_rows_kernel<TO_CACHE><<<blocks, kCopyWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(cache), static_cast<uint4*>(packed), seq_starts, cu_pack, cu_k, seq_ids, batch, rows,
+      vecs);
+  return check_launch(name);
+}
+
+}  // namespace
+}  // namespace dyllm
+
+using namespace dyllm;
+
+extern "C" {
+
+int dyllm_cache_get_seqs(const void* cache, void* out, const int64_t* seq_starts, const int32_t* cu_seqlens,
+                         const int64_t* seq_ids, int batch, int total_rows, int width, int elem_bytes,
+                         void* stream) {
+  return launch_rows<false>("cache_get_seqs", const_cast<void*>(cache), out, seq_starts, cu_seqlens, nullptr,
+                            seq_ids, batch, total_rows, width, elem_bytes, stream);
+}
+
+int dyllm_cache_get_block(const void* cache, void* out, const int64_t* seq_starts, const int32_t* cu_seqlens_k,
+                          const int32_t* cu_seqlens_q, const int64_t* seq_ids, int batch, int total_rows, int width,
+                          int elem_bytes, void* stream) {
+  DYLLM_REQUIRE(batch == 0 || total_rows == 0 || cu_seqlens_k, DYLLM_ERR_INVALID_ARGUMENT,
+                "cache_get_block: null cu_seqlens_k");
+  return launch_rows<false>("cache_get_block", const_cast<void*>(cache), out, seq_starts, cu_seqlens_q,
+                            cu_seqlens_k, seq_ids, batch, total_rows, width, elem_bytes, stream);
+}
+
+int dyllm_cache_reset_full(void* cache, const void* in, const int64_t* seq_starts, const int32_t* cu_seqlens,
+                           const int64_t* seq_ids, int batch, int total_rows, int width, int elem_bytes,
+                           void* stream) {
+  return launch_rows<true>("cache_reset_full", cache, const_cast<void*>(in), seq_starts, cu_seqlens, nullptr,
+                           seq_ids, batch, total_rows, width, elem_bytes, stream);
+}
+
+int dyllm_cache_reset_block(void* cache, const void* in, const int64_t* seq_starts, const int32_t* cu_seqlens_k,
+                            const int32_t* cu_seqlens_q, const int64_t* seq_ids, int batch, int total_rows,
+                            int width, int elem_bytes, void* stream) {
+  DYLLM_REQUIRE(batch == 0 || total_rows == 0 || cu_seqlens_k, DYLLM_ERR_INVALID_ARGUMENT,
+                "cache_reset_block: null cu_seqlens_k");
+  return launch_rows<true>("cache_reset_block", cache, const_cast<void*>(in), seq_starts, cu_seqlens_q,
+                           cu_seqlens_k, seq_ids, batch, total_rows, width, elem_bytes, stream);
+}
+
+int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t* row_idx, const void* cu_seqlens,
+                               int cu_is_int64, const int64_t* seq_starts, const int64_t* seq_ids, int batch,
+                               int num_rows, const int32_t* num_rows_dev, int width, int elem_bytes, void* stream) {
+  int rc = check_common("cache_scatter_update", cache, new_rows, seq_starts, cu_seqlens, seq_ids, batch, num_rows,
+                        width, elem_bytes);
+  if (rc != DYLLM_OK || num_rows == 0 || batch == 0)
+    return rc;
+  DYLLM_REQUIRE(row_idx, DYLLM_ERR_INVALID_ARGUMENT, "cache_scatter_update: null row_idx");
+  const int vecs = static_cast<int>(static_cast<int64_t>(width) * elem_bytes / 16);
+  const int blocks = min(cdiv_i(num_rows, kCopyWarps), sm_count() * 8);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cu_is_int64)
+    scatter_rows_kernel<int64_t><<<blocks, kCopyWarps * 32, 0, s>>>(
+        static_cast<uint4*>(cache), static_cast<const uint4*>(new_rows), row_idx,
+        static_cast<const int64_t*>(cu_seqlens), seq_starts, seq_ids, batch, num_rows, num_rows_dev, vecs);
+  else
+    scatter_rows_kernel<int32_t><<<blocks, kCopyWarps * 32, 0, s>>>(
+        static_cast<uint4*>(cache), static_cast<const uint4*>(new_rows), row_idx,
+        static_cast<const int32_t*>(cu_seqlens), seq_starts, seq_ids, batch, num_rows, num_rows_dev, vecs);
+  return check_launch("cache_scatter_update");
+}
+
+}  // extern "C"

@@ -1,0 +1,126 @@
+/*
+ * dyllm_b200 — C ABI of the sm_100a implementation of DyLLM's per-denoising-step saliency path.
+ *
+ * Every entry point takes raw device pointers, plain sizes and a CUDA stream (as void*), launches on
+ * that stream, never synchronises, never throws and returns an int status (0 = ok, < 0 = error; the
+ * text of the last error of the calling thread is returned by dyllm_last_error()).  Unless a
+ * function says otherwise it allocates nothing: outputs and workspaces are provided by the caller.
+ *
+ * Citations of the form "ref: path:line" name the file of the reference project (scale-snu/DyLLM)
+ * whose behaviour the entry point reproduces.
+ *
+ * Conventions: bf16 tensors are row-major and contiguous; "rows" are token rows of the packed
+ * (varlen) batch; cu_* arrays are int32 prefix sums of length batch + 1.
+ */
+#ifndef DYLLM_B200_H_
+#define DYLLM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DYLLM_OK 0
+#define DYLLM_ERR_INVALID_ARGUMENT (-1)
+#define DYLLM_ERR_UNSUPPORTED (-2)
+#define DYLLM_ERR_CUDA (-3)
+#define DYLLM_ERR_WORKSPACE (-4)
+#define DYLLM_ERR_DEVICE_TIMEOUT (-5)
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int dyllm_version(void);
+/* Message of the last failing call made by the calling thread ("" when none). */
+const char* dyllm_last_error(void);
+/* Reads and clears the per-device status word that kernels with bounded waits set when a wait ran
+ * out.  Synchronises the device.  Returns 0 when no kernel gave up, else a positive site code. */
+int dyllm_device_status(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Salient-token selection: statistics, mask, compaction
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Per-row additive cosine statistics between the previous and the current attention context:
+ * stats[r] = { sum(new*old), sum(new^2), sum(old^2) } over `width` bf16 elements, fp32 accumulation in
+ * a fixed order (run-to-run identical).  When accumulate != 0 the three sums are added to the values
+ * already in `stats` (one call per tensor-parallel head shard held on the same device); otherwise
+ * they overwrite them.
+ * ref: dyllm/csrc/attention/attention_ops_kernels_sm80.cu:407-481 (epilogue statistics),
+ *      dyllm/csrc/attention/attention_aux_kernels.cu:34-71 (bf16 rows). */
+int dyllm_context_stats(const void* c_old, const void* c_new, float* stats, int rows, int width,
+                        int accumulate, void* stream);
+
+/* mask[r] = dot * rsqrt(max(a, 1e-8)) * rsqrt(max(b, 1e-8)) < threshold, one byte per row.
+ * ref: dyllm/csrc/attention/attention_aux_kernels.cu:10-20,138-146;
+ *      dyllm/distributed/parallel_state.py:52-66. */
+int dyllm_cosine_mask(const float* stats, uint8_t* mask, int rows, float threshold, void* stream);
+
+/* Bytes of scratch memory dyllm_salient_select needs for `rows` rows. */
+size_t dyllm_salient_select_workspace_bytes(int rows);
+
+/* Fused mask + compaction.  From the (already all-reduced) statistics of `rows` query rows it writes
+ *   idx_out[0..n)            ascending row numbers with cosine < threshold      (int64)
+ *   idx32_out[0..n)          the same list as int32, nullable
+ *   idx_k_out[0..n)          idx + cu_promptlens[b + 1], b = sequence of the row (int64, nullable;
+ *                            requires cu_promptlens)
+ *   cu_salientlens_out[b]    number of selected rows below cu_seqlens_q[b], b = 0..batch (int32)
+ *   count_out[0]             n                                                   (int32)
+ *   mask_out[r]              the per-row decision, nullable                       (uint8)
+ * in one launch, without a host synchronisation.  `workspace` must hold
+ * dyllm_salient_select_workspace_bytes(rows) bytes; its content on entry is irrelevant.
+ * ref: dyllm/distributed/parallel_state.py:52-66 (mask rule),
+ *      dyllm/model_executor/layers/attention.py:147-150,172-173 (nonzero + searchsorted),
+ *      dyllm/csrc/attention/attention_aux_kernels.cu:112-128 (K-space offsets). */
+int dyllm_salient_select(const float* stats, int rows, float threshold, const int32_t* cu_seqlens_q,
+                         int batch, const int32_t* cu_promptlens, int64_t* idx_out, int32_t* idx32_out,
+                         int64_t* idx_k_out, int32_t* cu_salientlens_out, int32_t* count_out,
+                         uint8_t* mask_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* out[t] = idxs[t] + cu_promptlens[g + 1] for t < *num_idxs, g = group with
+ * cu_salientlens[g] <= t < cu_salientlens[g + 1]; at most max_threads entries are written.
+ * ref: dyllm/csrc/attention/attention_aux_kernels.cu:112-128,173-200 (fused_offset_launch). */
+int dyllm_fused_offset(const int32_t* idxs, const int32_t* num_idxs, const int32_t* cu_promptlens,
+                       const int32_t* cu_salientlens, int num_groups, int64_t* out, int max_threads,
+                       void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Per-sequence activation cache (rows of `width` elements of `elem_bytes` bytes each;
+ * width * elem_bytes must be a multiple of 16).  seq_starts[seq_ids[b]] is the first cache row of
+ * batch entry b.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* out[cu[b] + i] = cache[seq_starts[seq_ids[b]] + i], i < cu[b+1] - cu[b].
+ * ref: dyllm/csrc/cache/cache_kernels.cu:18-108 (get_seqs_cuda). */
+int dyllm_cache_get_seqs(const void* cache, void* out, const int64_t* seq_starts, const int32_t* cu_seqlens,
+                         const int64_t* seq_ids, int batch, int total_rows, int width, int elem_bytes,
+                         void* stream);
+/* out[cu_q[b] + i] = cache[seq_starts[seq_ids[b]] + len_k(b) - len_q(b) + i]: the last len_q rows.
+ * ref: dyllm/csrc/cache/cache_kernels.cu:249-294 (get_block_cuda). */
+int dyllm_cache_get_block(const void* cache, void* out, const int64_t* seq_starts, const int32_t* cu_seqlens_k,
+                          const int32_t* cu_seqlens_q, const int64_t* seq_ids, int batch, int total_rows,
+                          int width, int elem_bytes, void* stream);
+/* cache[seq_starts[seq_ids[b]] + i] = in[cu[b] + i].
+ * ref: dyllm/csrc/cache/cache_kernels.cu:110-198 (reset_full_cuda). */
+int dyllm_cache_reset_full(void* cache, const void* in, const int64_t* seq_starts, const int32_t* cu_seqlens,
+                           const int64_t* seq_ids, int batch, int total_rows, int width, int elem_bytes,
+                           void* stream);
+/* cache[seq_starts[seq_ids[b]] + len_k(b) - len_q(b) + i] = in[cu_q[b] + i].
+ * ref: dyllm/csrc/cache/cache_kernels.cu:296-386 (reset_block_cuda). */
+int dyllm_cache_reset_block(void* cache, const void* in, const int64_t* seq_starts, const int32_t* cu_seqlens_k,
+                            const int32_t* cu_seqlens_q, const int64_t* seq_ids, int batch, int total_rows,
+                            int width, int elem_bytes, void* stream);
+/* cache[seq_starts[seq_ids[b]] + row_idx[m] - cu[b]] = new_rows[m], b = sequence containing packed
+ * row row_idx[m].  `num_rows_dev`, when not null, is a device int32 that bounds m from above
+ * (m < min(num_rows, *num_rows_dev)).  cu_is_int64 selects the element type of cu_seqlens.
+ * ref: dyllm/csrc/cache/cache_kernels.cu:388-459 (scatter_update_cuda). */
+int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t* row_idx, const void* cu_seqlens,
+                               int cu_is_int64, const int64_t* seq_starts, const int64_t* seq_ids, int batch,
+                               int num_rows, const int32_t* num_rows_dev, int width, int elem_bytes,
+                               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DYLLM_B200_H_ */

@@ -1,0 +1,95 @@
+"""Parity of the activation-cache copy kernels with the CPU oracle (bit-exact byte movement)."""
+import pytest
+import torch
+
+from oracle import dyllm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(lens, width, dtype, seed=0, max_seqs=64):
+    g = torch.Generator().manual_seed(seed)
+    total = sum(lens)
+    cache = torch.randn(total + 5, width, generator=g).to(dtype)
+    # sequences live in the cache in a shuffled order with arbitrary ids
+    order = torch.randperm(len(lens), generator=g).tolist()
+    ids = torch.randperm(max_seqs, generator=g)[: len(lens)]
+    seq_starts = torch.full((max_seqs,), -1, dtype=torch.int64)
+    pos = 0
+    for j in order:
+        seq_starts[ids[j]] = pos
+        pos += lens[j]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    return cache, seq_starts, ids.to(torch.int64), cu
+
+
+CASES = [([512], 4096, torch.bfloat16), ([5, 0, 17, 33], 128, torch.bfloat16), ([512] * 16, 512, torch.bfloat16),
+         ([7, 9], 8, torch.bfloat16), ([3, 4], 12, torch.float32)]
+
+
+@pytest.mark.parametrize("lens,width,dtype", CASES)
+def test_get_and_reset_full(cuda_device, lens, width, dtype):
+    from dyllm_b200 import cache as C
+
+    cache, ss, ids, cu = _setup(lens, width, dtype)
+    total = int(cu[-1])
+    d = lambda t: t.to(cuda_device)
+    got = C.get_seqs_cuda(d(cache), d(ss), d(cu), d(ids), total)
+    want = orc.cache_get_seqs(cache, ss, cu, ids, total)
+    assert torch.equal(got.cpu(), want)
+    new = torch.randn(total, width).to(dtype)
+    dc = d(cache)
+    C.reset_full_cuda(dc, d(new), d(ss), d(cu), d(ids), total)
+    assert torch.equal(dc.cpu(), orc.cache_reset_full(cache.clone(), new, ss, cu, ids))
+
+
+@pytest.mark.parametrize("lens,width,dtype", CASES[:4])
+def test_get_and_reset_block(cuda_device, lens, width, dtype):
+    from dyllm_b200 import cache as C
+
+    cache, ss, ids, cu_k = _setup(lens, width, dtype, seed=1)
+    qlens = [l // 2 for l in lens]
+    cu_q = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32)
+    total = int(cu_q[-1])
+    d = lambda t: t.to(cuda_device)
+    got = C.get_block_cuda(d(cache), d(ss), d(cu_k), d(cu_q), d(ids), total)
+    assert torch.equal(got.cpu(), orc.cache_get_block(cache, ss, cu_k, cu_q, ids, total))
+    new = torch.randn(total, width).to(dtype)
+    dc = d(cache)
+    C.reset_block_cuda(dc, d(new), d(ss), d(cu_k), d(cu_q), d(ids), total)
+    assert torch.equal(dc.cpu(), orc.cache_reset_block(cache.clone(), new, ss, cu_k, cu_q, ids))
+
+
+@pytest.mark.parametrize("cu_dtype", [torch.int32, torch.int64])
+def test_scatter_update(cuda_device, cu_dtype):
+    from dyllm_b200 import cache as C
+
+    lens = [512] * 4 + [100]
+    cache, ss, ids, cu = _setup(lens, 1024, torch.bfloat16, seed=2)
+    total = int(cu[-1])
+    g = torch.Generator().manual_seed(9)
+    rows = torch.sort(torch.randperm(total, generator=g)[:211]).values
+    new = torch.randn(211, 1024, generator=g).bfloat16()
+    d = lambda t: t.to(cuda_device)
+    dc = d(cache)
+    C.scatter_update_cuda(dc, d(new), d(rows), d(cu.to(cu_dtype)), d(ss), d(ids))
+    assert torch.equal(dc.cpu(), orc.cache_scatter_update(cache.clone(), new, rows, cu, ss, ids))
+    # device-side row count: only the first 100 rows are consumed; zero rows is a no-op
+    dc2 = d(cache)
+    C.scatter_update_cuda(dc2, d(new), d(rows), d(cu), d(ss), d(ids),
+                          num_rows_dev=torch.tensor([100], dtype=torch.int32, device=cuda_device))
+    assert torch.equal(dc2.cpu(), orc.cache_scatter_update(cache.clone(), new[:100], rows[:100], cu, ss, ids))
+    C.scatter_update_cuda(dc2, d(new[:0]), d(rows[:0]), d(cu), d(ss), d(ids))
+
+
+def test_errors_are_runtime_errors(cuda_device):
+    from dyllm_b200 import cache as C
+
+    cache, ss, ids, cu = _setup([4], 8, torch.bfloat16)
+    d = lambda t: t.to(cuda_device)
+    with pytest.raises(RuntimeError):
+        C.get_seqs_cuda(d(cache), d(ss), d(cu).long(), d(ids), 4)  # cu must be int32
+    with pytest.raises(RuntimeError):
+        C.get_seqs_cuda(d(cache)[:, :3].contiguous(), d(ss), d(cu), d(ids), 4)  # row not a multiple of 16 bytes
+    with pytest.raises(RuntimeError):
+        C.reset_full_cuda(d(cache), d(cache)[:, :4].contiguous(), d(ss), d(cu), d(ids), 4)
