@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 
 import torch
 
@@ -32,6 +32,10 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_cache_reset_full": (I, [P, P, P, P, P, I, I, I, I, P]),
     "dyllm_cache_reset_block": (I, [P, P, P, P, P, P, I, I, I, I, P]),
     "dyllm_cache_scatter_update": (I, [P, P, P, P, I, P, P, I, I, P, I, I, P]),
+    "dyllm_gathered_linear": (I, [P, I, I, c_int64, P, I, P, P, I, P, c_int64, P, P, I, I, P]),
+    "dyllm_swiglu_ffn_workspace_bytes": (Z, [I, I]),
+    "dyllm_swiglu_ffn": (I, [P, I, I, c_int64, P, I, P, P, P, I, P, c_int64, P, P, Z, I, I, P]),
+    "dyllm_cache_dest_rows": (I, [P, P, P, P, I, I, P, P, P]),
 }
 
 _lib = None

@@ -91,3 +91,82 @@ def salient_select(stats: torch.Tensor, threshold: float, cu_seqlens_q: torch.Te
     call("dyllm_salient_select", ptr(stats), rows, float(threshold), ptr(cu_seqlens_q), batch, ptr(cu_promptlens),
          ptr(idx), ptr(idx32), ptr(idx_k), ptr(cu_sal), ptr(count), ptr(mask), ptr(ws), ws.numel(), stream_ptr(dev))
     return SalientSelection(idx, idx32, idx_k, cu_sal, count, mask)
+
+
+def cache_dest_rows(row_idx: torch.Tensor, cu_seqlens: torch.Tensor, seq_starts: torch.Tensor,
+                    seq_ids: torch.Tensor, num_rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """Cache row that ``scatter_update`` would write for each packed row (int32, -1 past the live rows).
+
+    ref: dyllm/csrc/cache/cache_kernels.cu:398-421.
+    """
+    require_cuda(row_idx, "row_idx", torch.int64, 1)
+    require_cuda(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    n = row_idx.numel()
+    dest = torch.empty((n,), dtype=torch.int32, device=row_idx.device)
+    call("dyllm_cache_dest_rows", ptr(row_idx), ptr(cu_seqlens), ptr(seq_starts), ptr(seq_ids), seq_ids.numel(), n,
+         ptr(num_rows_dev), ptr(dest), stream_ptr(row_idx.device))
+    return dest
+
+
+def gathered_linear(x: torch.Tensor, weight: torch.Tensor, idx: torch.Tensor | None = None,
+                    num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None,
+                    out: torch.Tensor | None = None, out_row_map: torch.Tensor | None = None,
+                    row_scale: torch.Tensor | None = None, a_mode: int = -1, tile_n: int = 0) -> torch.Tensor:
+    """``out[map[m]] = scale[m] * (x[idx[m]] @ weight.T)`` on the tcgen05 tensor cores.
+
+    ref: dyllm/model_executor/models/llada.py:108 (``kv_proj(hidden_states[idx_salient_row])``).
+    """
+    require_cuda(x, "x", torch.bfloat16, 2)
+    require_cuda(weight, "weight", torch.bfloat16, 2)
+    if idx is not None:
+        require_cuda(idx, "idx", torch.int32, 1)
+    if num_rows is None:
+        num_rows = idx.numel() if idx is not None else x.size(0)
+    n_out = weight.size(0)
+    if out is None:
+        out = torch.empty((num_rows, n_out), dtype=torch.bfloat16, device=x.device)
+    call("dyllm_gathered_linear", ptr(x), x.size(0), x.size(1), x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev),
+         ptr(weight), n_out, ptr(out), out.stride(0), ptr(out_row_map), ptr(row_scale), a_mode, tile_n,
+         stream_ptr(x.device))
+    return out
+
+
+_ffn_workspaces: dict = {}
+
+
+def _ffn_workspace(num_rows: int, inter: int, device) -> torch.Tensor:
+    need = load().dyllm_swiglu_ffn_workspace_bytes(num_rows, inter)
+    ws = _ffn_workspaces.get(device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=device)
+        _ffn_workspaces[device] = ws
+    return ws
+
+
+def swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor | None = None,
+               num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None,
+               out: torch.Tensor | None = None, out_row_map: torch.Tensor | None = None, a_mode: int = -1,
+               tile_n: int = 0) -> torch.Tensor:
+    """``out[map[m]] = down(silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T))`` for the gathered rows.
+
+    ref: dyllm/model_executor/models/llada.py:38-43,184-185.
+    """
+    require_cuda(x, "x", torch.bfloat16, 2)
+    require_cuda(w_gate_up, "w_gate_up", torch.bfloat16, 2)
+    require_cuda(w_down, "w_down", torch.bfloat16, 2)
+    hidden, inter = x.size(1), w_down.size(1)
+    if w_gate_up.shape != (2 * inter, hidden) or w_down.size(0) != hidden:
+        raise RuntimeError("w_gate_up must be [2 * inter, hidden] and w_down [hidden, inter]")
+    if idx is not None:
+        require_cuda(idx, "idx", torch.int32, 1)
+    if num_rows is None:
+        num_rows = idx.numel() if idx is not None else x.size(0)
+    if out is None:
+        out = torch.empty((num_rows, hidden), dtype=torch.bfloat16, device=x.device)
+    if num_rows == 0:
+        return out
+    ws = _ffn_workspace(num_rows, inter, x.device)
+    call("dyllm_swiglu_ffn", ptr(x), x.size(0), hidden, x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev),
+         ptr(w_gate_up), ptr(w_down), inter, ptr(out), out.stride(0), ptr(out_row_map), ptr(ws), ws.numel(), a_mode,
+         tile_n, stream_ptr(x.device))
+    return out

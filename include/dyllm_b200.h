@@ -119,6 +119,43 @@ int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t*
                                int num_rows, const int32_t* num_rows_dev, int width, int elem_bytes,
                                void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Gathered tensor-core GEMMs (tcgen05 / TMEM).  Weights are bf16 [out, in] row-major as in
+ * torch.nn.Linear.  a_mode selects how activation rows reach shared memory: 1 = TMA gather4
+ * (default when negative), 2 = 16-byte vector loads; tile_n = 64, 128 or 0 (choose).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* out[map[m]] = scale[m] * (x[idx[m]] W^T), m < min(num_rows, *num_rows_dev).  idx null = identity,
+ * out_row_map null = m (negative entries drop the row), row_scale null = 1.  in_features % 64 == 0,
+ * out_features % 64 == 0.  Used for the K/V projection of salient rows
+ * (ref: dyllm/model_executor/models/llada.py:108, dyllm/model_executor/layers/linear.py:50-51). */
+int dyllm_gathered_linear(const void* x, int x_rows, int in_features, int64_t ldx, const int32_t* idx,
+                          int num_rows, const int32_t* num_rows_dev, const void* weight, int out_features,
+                          void* out, int64_t ldo, const int32_t* out_row_map, const float* row_scale,
+                          int a_mode, int tile_n, void* stream);
+
+/* Bytes of workspace dyllm_swiglu_ffn needs for up to max_rows gathered rows. */
+size_t dyllm_swiglu_ffn_workspace_bytes(int max_rows, int inter);
+
+/* out[map[m]] = down( silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T) ) for the gathered rows: w_gate_up is
+ * [2 * inter, hidden] with the gate rows first, w_down is [hidden, inter].  The SiLU product is fused
+ * into the first GEMM's epilogue, the row scatter into the second's.  workspace: 1024-byte aligned,
+ * dyllm_swiglu_ffn_workspace_bytes(num_rows, inter) bytes.
+ * ref: dyllm/model_executor/models/llada.py:38-43,184-185 (gather + MLP),
+ *      dyllm/model_executor/layers/activations.py:9-14, dyllm/model_executor/layers/linear.py:76-93,195-220,
+ *      dyllm/model_executor/layers/mlp_cache_manage.py:24-40 (scatter into the FFN-output cache). */
+int dyllm_swiglu_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int32_t* idx, int num_rows,
+                     const int32_t* num_rows_dev, const void* w_gate_up, const void* w_down, int inter, void* out,
+                     int64_t ldo, const int32_t* out_row_map, void* workspace, size_t workspace_bytes, int a_mode,
+                     int tile_n, void* stream);
+
+/* dest_rows[m] = seq_starts[seq_ids[b]] + row_idx[m] - cu_seqlens[b] (the cache row that
+ * dyllm_cache_scatter_update would write) for m < min(num_rows, *num_rows_dev), -1 for the rest;
+ * feeds out_row_map of the GEMMs above.  ref: dyllm/csrc/cache/cache_kernels.cu:398-421. */
+int dyllm_cache_dest_rows(const int64_t* row_idx, const int32_t* cu_seqlens, const int64_t* seq_starts,
+                          const int64_t* seq_ids, int batch, int num_rows, const int32_t* num_rows_dev,
+                          int32_t* dest_rows, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

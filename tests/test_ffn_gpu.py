@@ -1,0 +1,121 @@
+"""Parity of the tcgen05 gathered GEMMs / SwiGLU FFN with the fp32 oracle.
+
+Tolerances follow the path's contract: bf16 outputs within max-abs 2e-2 and relative L2 1e-2.
+The a_mode 2 cases (vector-load gather) run before the a_mode 1 cases (TMA gather4).
+"""
+import pytest
+import torch
+
+from oracle import dyllm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, REL_L2 = 2e-2, 1e-2
+
+
+def _check(got, want, what):
+    got, want = got.float().cpu(), want.float().cpu()
+    # max-abs is stated for outputs of unit scale; larger outputs are compared relative to their peak
+    # (a bf16 ulp at |x| = 8 is already 0.03)
+    err = (got - want).abs().max().item() / max(1.0, want.abs().max().item())
+    rel = ((got - want).norm() / want.norm().clamp_min(1e-12)).item()
+    assert err <= MAX_ABS and rel <= REL_L2, f"{what}: scaled max-abs {err:.4g}, rel-L2 {rel:.4g}"
+
+
+def _status_ok():
+    from dyllm_b200 import _lib
+
+    assert _lib.load().dyllm_device_status() == 0
+
+
+@pytest.mark.parametrize("a_mode", [2, 1], ids=["mode2", "mode1"])
+@pytest.mark.parametrize("rows,k,n,tile_n", [(128, 64, 64, 64), (26, 256, 128, 128), (410, 4096, 1024, 0),
+                                              (300, 3584, 512, 64)])
+def test_gathered_linear(cuda_device, a_mode, rows, k, n, tile_n):
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + k)
+    total = max(rows * 3, 512)
+    x = torch.randn(total, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    idx = torch.sort(torch.randperm(total, generator=g)[:rows]).values.to(torch.int32)
+    want = x.float()[idx.long()] @ w.float().t()
+    got = ops.gathered_linear(x.to(cuda_device), w.to(cuda_device), idx.to(cuda_device), a_mode=a_mode, tile_n=tile_n)
+    _status_ok()
+    _check(got, want.bfloat16(), f"gathered_linear mode {a_mode}")
+
+
+@pytest.mark.parametrize("a_mode", [2, 1], ids=["mode2", "mode1"])
+def test_gathered_linear_scatter_scale_and_device_count(cuda_device, a_mode):
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(700, 512, generator=g).bfloat16()
+    w = (torch.randn(256, 512, generator=g) * 0.05).bfloat16()
+    idx = torch.sort(torch.randperm(700, generator=g)[:300]).values.to(torch.int32)
+    live = 211
+    dest = torch.randperm(400, generator=g)[:300].to(torch.int32)
+    dest[7] = -1  # dropped row
+    scale = torch.rand(300, generator=g)
+    out = torch.full((400, 256), 3.0).bfloat16().to(cuda_device)
+    ops.gathered_linear(x.to(cuda_device), w.to(cuda_device), idx.to(cuda_device),
+                        num_rows_dev=torch.tensor([live], dtype=torch.int32, device=cuda_device), out=out,
+                        out_row_map=dest.to(cuda_device), row_scale=scale.to(cuda_device), a_mode=a_mode)
+    _status_ok()
+    want = torch.full((400, 256), 3.0)
+    y = (x.float()[idx.long()] @ w.float().t()) * scale[:, None]
+    for m in range(live):
+        if dest[m] >= 0:
+            want[dest[m]] = y[m]
+    _check(out, want.bfloat16(), "scatter/scale")
+    untouched = torch.ones(400, dtype=torch.bool)
+    untouched[dest[:live][dest[:live] >= 0].long()] = False
+    assert bool((out.cpu()[untouched] == 3.0).all())
+
+
+@pytest.mark.parametrize("a_mode", [2, 1], ids=["mode2", "mode1"])
+@pytest.mark.parametrize("rows,hidden,inter,tile_n", [(26, 4096, 12288, 0), (410, 4096, 12288, 0), (130, 512, 1024, 64),
+                                                       (130, 512, 1024, 128), (1, 256, 128, 64)])
+def test_swiglu_ffn_matches_oracle(cuda_device, a_mode, rows, hidden, inter, tile_n):
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows)
+    total = max(2 * rows, 512)
+    x = torch.randn(total, hidden, generator=g).bfloat16()
+    w1 = (torch.randn(2 * inter, hidden, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn(hidden, inter, generator=g) * 0.02).bfloat16()
+    idx = torch.sort(torch.randperm(total, generator=g)[:rows]).values.to(torch.int32)
+    want = orc.swiglu_ffn(x[idx.long()], w1, w2)
+    got = ops.swiglu_ffn(x.to(cuda_device), w1.to(cuda_device), w2.to(cuda_device), idx.to(cuda_device),
+                         a_mode=a_mode, tile_n=tile_n)
+    _status_ok()
+    _check(got, want, f"swiglu_ffn mode {a_mode}")
+
+
+def test_swiglu_ffn_scatters_into_cache_rows(cuda_device):
+    """Fused path: rows of the FFN output land in the per-sequence cache rows that scatter_update would write."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(8)
+    batch, L, hidden, inter = 4, 128, 512, 1024
+    cu = (torch.arange(batch + 1) * L).to(torch.int32)
+    seq_ids = torch.tensor([9, 2, 5, 11])
+    seq_starts = torch.full((16,), -1, dtype=torch.int64)
+    for j, s in enumerate([2, 0, 3, 1]):
+        seq_starts[seq_ids[j]] = s * L
+    x = torch.randn(batch * L, hidden, generator=g).bfloat16()
+    w1 = (torch.randn(2 * inter, hidden, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn(hidden, inter, generator=g) * 0.02).bfloat16()
+    rows = torch.sort(torch.randperm(batch * L, generator=g)[:77]).values
+    cache = torch.randn(batch * L, hidden, generator=g).bfloat16()
+    d = lambda t: t.to(cuda_device)
+    dest = ops.cache_dest_rows(d(rows), d(cu), d(seq_starts), d(seq_ids))
+    dcache = d(cache)
+    ops.swiglu_ffn(d(x), d(w1), d(w2), d(rows.to(torch.int32)), out=dcache, out_row_map=dest)
+    _status_ok()
+    want = orc.cache_scatter_update(cache.clone(), orc.swiglu_ffn(x[rows], w1, w2).bfloat16(), rows, cu, seq_starts,
+                                    seq_ids)
+    _check(dcache, want, "ffn scatter")
+    touched = torch.zeros(batch * L, dtype=torch.bool)
+    touched[dest.cpu().long()] = True
+    assert torch.equal(dcache.cpu()[~touched], cache[~touched])
