@@ -36,6 +36,9 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_swiglu_ffn_workspace_bytes": (Z, [I, I]),
     "dyllm_swiglu_ffn": (I, [P, I, I, c_int64, P, I, P, P, P, I, P, c_int64, P, P, Z, I, I, P]),
     "dyllm_cache_dest_rows": (I, [P, P, P, P, I, I, P, P, P]),
+    "dyllm_attention_sparse_workspace_bytes": (Z, [I, I]),
+    "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, F, P, Z, I, P]),
+    "dyllm_attention_kernel_info": (I, [I, P]),
 }
 
 _lib = None

@@ -6,7 +6,108 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import call, ptr, stream_ptr
+from ._lib import call, load, ptr, stream_ptr
+
+_EMPTY = None
+_workspaces: dict = {}
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def _check_tensor(t, name, device, dtype, dim):
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be defined")
+    if not (t.is_cuda and t.device == device):
+        raise RuntimeError(f"{name} must be on {device}")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} has an invalid dtype")
+    if t.dim() != dim or not t.is_contiguous():
+        raise RuntimeError(f"{name} must be a contiguous {dim}D tensor")
+
+
+def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int,
+                            total_seqlen: int, cu_salientlens, idx_salient_row, cosine_stats, cosine_out,
+                            threshold: float = 0.0, is_q_pruned: bool = False, idx_salient_row_k=None,
+                            force_mask_v_rows: int = -1, v_mn_major: int = 1) -> torch.Tensor:
+    """ref: dyllm/csrc/attention/attention.cpp:64-179.
+
+    Same arguments, checks and return value (a fresh ``O`` shaped like ``Q``).  ``force_mask_v_rows``
+    is accepted and ignored (it switches between two load strategies of the reference kernel that
+    compute the same result).  ``V`` must be zero outside the listed salient key rows, as the
+    reference's caller builds it.
+    """
+    if not (isinstance(Q, torch.Tensor) and Q.is_cuda):
+        raise RuntimeError("Q must be CUDA")
+    dev, bf16, i32 = Q.device, torch.bfloat16, torch.int32
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (C, "C"), (o_sal, "o_sal")):
+        _check_tensor(t, n, dev, bf16, 3)
+    for t, n in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k"), (cu_salientlens, "cu_salientlens"),
+                 (idx_salient_row, "idx_salient_row")):
+        _check_tensor(t, n, dev, i32, 1)
+    _check_tensor(cosine_stats, "cosine_stats", dev, torch.float32, 2)
+    _check_tensor(cosine_out, "cosine_out", dev, torch.bool, 1)
+    if K.shape != V.shape:
+        raise RuntimeError("K and V must have the same shape")
+    if not (Q.size(0) > 0 and K.size(0) > 0):
+        raise RuntimeError("Q and K/V token dimensions must be non-empty")
+    if Q.size(2) != K.size(2):
+        raise RuntimeError("Q, K, and V must have the same head dimension")
+    if C.shape != Q.shape:
+        raise RuntimeError("C must have the same shape as Q")
+    if not (o_sal.size(0) == idx_salient_row.numel() and o_sal.size(1) == Q.size(1) and o_sal.size(2) == Q.size(2)):
+        raise RuntimeError("o_sal must be [idx_salient_row.numel(), Q.size(1), Q.size(2)]")
+    if not (Q.size(1) > 0 and K.size(1) > 0 and Q.size(1) % K.size(1) == 0):
+        raise RuntimeError(f"local TP query heads must be a positive multiple of local KV heads; got {Q.size(1)} "
+                           f"and {K.size(1)}")
+    if Q.size(2) != 128:
+        raise RuntimeError(f"supported head dimension is 128; got {Q.size(2)}")
+    if not (cu_seqlens_q.numel() >= 2 and cu_seqlens_q.numel() == cu_seqlens_k.numel() == cu_salientlens.numel()):
+        raise RuntimeError("cu_seqlens_q, cu_seqlens_k, and cu_salientlens must have the same B+1 length")
+    if total_seqlen != Q.size(0):
+        raise RuntimeError("total_seqlen must equal Q.size(0)")
+    if not (cosine_stats.size(0) == Q.size(0) and cosine_stats.size(1) == 3):
+        raise RuntimeError("cosine_stats must be [Q.size(0), 3]")
+    if cosine_out.numel() != Q.size(0):
+        raise RuntimeError("cosine_out must contain Q.size(0) elements")
+    if not (0 < max_seqlen_q <= Q.size(0) and 0 < max_seqlen_k <= K.size(0)):
+        raise RuntimeError("maximum sequence lengths must be positive and fit their packed token dimensions")
+    if idx_salient_row.numel() > Q.size(0):
+        raise RuntimeError("salient Q index count cannot exceed Q.size(0)")
+    if force_mask_v_rows not in (-1, 0, 1):
+        raise RuntimeError("force_mask_v_rows must be -1, 0, or 1")
+    idx_k = idx_salient_row
+    if is_q_pruned:
+        _check_tensor(idx_salient_row_k, "idx_salient_row_k", dev, i32, 1)
+        if idx_salient_row_k.numel() != idx_salient_row.numel():
+            raise RuntimeError("parallel Q/K pruning requires matching salient Q and K index counts")
+        if idx_salient_row_k.numel() > K.size(0):
+            raise RuntimeError("salient K index count cannot exceed K.size(0)")
+        idx_k = idx_salient_row_k
+
+    out = torch.empty_like(Q)
+    H = Q.size(1)
+    need = load().dyllm_attention_sparse_workspace_bytes(Q.size(0), H)
+    ws = _workspace(need, dev)
+    call("dyllm_attention_sparse_varlen", ptr(Q), ptr(K), ptr(V), ptr(C), ptr(o_sal), ptr(out), ptr(cu_seqlens_q),
+         ptr(cu_seqlens_k), cu_seqlens_q.numel() - 1, int(max_seqlen_q), int(max_seqlen_k), Q.size(0), K.size(0), H,
+         K.size(1), Q.size(2), ptr(cu_salientlens), ptr(idx_salient_row), ptr(idx_k), idx_salient_row.numel(),
+         ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_mn_major), stream_ptr(dev))
+    return out
+
+
+def attention_kernel_info(dim: int, mask_v_rows: bool = False) -> list[int]:
+    """ref: dyllm/csrc/attention/attention.cpp:184-208."""
+    import ctypes
+
+    buf = (ctypes.c_int64 * 10)()
+    call("dyllm_attention_kernel_info", int(dim), ctypes.cast(buf, ctypes.c_void_p))
+    return list(buf)
 
 
 def _check_i32_vector(t: torch.Tensor, name: str, device) -> None:
@@ -40,4 +141,4 @@ def fused_offset_launch(idxs, num_idxs, cu_promptlens, cu_salientlens, out_tenso
          cu_promptlens.numel() - 1, ptr(out_tensor), int(max_threads), stream_ptr(device))
 
 
-__all__ = ["fused_offset_launch"]
+__all__ = ["attention_sparse_varlen", "fused_offset_launch", "attention_kernel_info"]

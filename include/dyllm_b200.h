@@ -156,6 +156,42 @@ int dyllm_cache_dest_rows(const int64_t* row_idx, const int32_t* cu_seqlens, con
                           const int64_t* seq_ids, int batch, int num_rows, const int32_t* num_rows_dev,
                           int32_t* dest_rows, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Approximate (delta) attention of a sparse step, head_dim 128
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Bytes of scratch memory dyllm_attention_sparse_varlen needs (per-head partial statistics). */
+size_t dyllm_attention_sparse_workspace_bytes(int total_q, int num_heads);
+
+/* out[r] = bf16( c[r] + softmax(q_r K^T / sqrt(D)) V ) for all total_q query rows, where V is the
+ * delta-V tensor of the step: it must be zero on every key row that is not listed in
+ * idx_salient_row_k (the reference's caller builds it that way; only the listed rows are read).
+ * Rows listed in idx_salient_row_q are then replaced by o_sal, and
+ *   cosine_stats[r] += {dot(new, c), |new|^2, |c|^2}   (fp32 value before rounding; caller zero-fills)
+ *   cosine_stats[r]  = the same from the bf16 o_sal row for the replaced rows
+ *   cosine_out[r]    = cosine(cosine_stats[r]) < threshold
+ * q, c, out: [total_q, num_heads, 128]; k, v: [total_k, num_kv_heads, 128]; o_sal: [num_salient,
+ * num_heads, 128]; all bf16.  idx_salient_row_q (query space) and idx_salient_row_k (key space) hold
+ * num_salient ascending rows each, grouped by sequence through cu_salientlens; pass the same list
+ * twice when queries are not pruned.  The softmax scale is 1/sqrt(128).  Statistics are reduced over
+ * heads in a fixed order.  v_mn_major selects how the delta-V tile is fed to the tensor cores
+ * (1 = as gathered, MN-major descriptor; 0 = transposed while gathering); results are identical.
+ * ref: dyllm/csrc/attention/attention.cpp:64-179 (attention_sparse_varlen),
+ *      dyllm/csrc/attention/attention_ops_kernels_sm80.cu:44-590,
+ *      dyllm/csrc/attention/attention_aux_kernels.cu:10-110. */
+int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, const void* c, const void* o_sal,
+                                  void* out, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int batch,
+                                  int max_seqlen_q, int max_seqlen_k, int total_q, int total_k, int num_heads,
+                                  int num_kv_heads, int head_dim, const int32_t* cu_salientlens,
+                                  const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
+                                  int num_salient, float* cosine_stats, uint8_t* cosine_out, float threshold,
+                                  void* workspace, size_t workspace_bytes, int v_mn_major, void* stream);
+
+/* Launch resources of the main attention kernel: [registers, local bytes, static shared bytes,
+ * dynamic shared bytes, threads per block, resident blocks per SM, query rows per block, keys per
+ * tile, head-dim split, ok].  ref: dyllm/csrc/attention/attention.cpp:184-208. */
+int dyllm_attention_kernel_info(int dim, int64_t* info10);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,150 @@
+"""Parity of the tcgen05 approximate-attention kernel with the fp32 oracle.
+
+bf16 outputs: max-abs <= 2e-2 (unit-scale outputs) and relative L2 <= 1e-2; salient decisions
+bit-exact (the generators keep every cosine at least 1e-4 away from the threshold).
+"""
+import pytest
+import torch
+
+from oracle import dyllm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TAU = 0.99
+
+
+def make_case(batch, prompt, response, H, Hkv, response_only, sal_per_seq, seed, ragged=False):
+    """One sparse-step attention problem in the reference's calling convention."""
+    D = 128
+    g = torch.Generator().manual_seed(seed)
+    if ragged:
+        lens_k = [prompt + response - 17 * b for b in range(batch)]
+    else:
+        lens_k = [prompt + response] * batch
+    lens_q = [response if response_only else lk for lk in lens_k]
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32)
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    Tq, Tk = int(cu_q[-1]), int(cu_k[-1])
+    q = torch.randn(Tq, H, D, generator=g).bfloat16()
+    k = torch.randn(Tk, Hkv, D, generator=g).bfloat16()
+    c_old = torch.randn(Tq, H, D, generator=g).bfloat16()
+    # salient rows: response positions of each sequence
+    idx_q, idx_k, cu_sal = [], [], [0]
+    for b in range(batch):
+        n = sal_per_seq if isinstance(sal_per_seq, int) else sal_per_seq[b]
+        resp0 = lens_k[b] - response
+        pos = torch.sort(torch.randperm(response, generator=g)[:n]).values + resp0  # position inside the sequence
+        idx_k += (pos + int(cu_k[b])).tolist()
+        idx_q += ((pos - resp0 if response_only else pos) + int(cu_q[b])).tolist()
+        cu_sal.append(cu_sal[-1] + n)
+    idx_q = torch.tensor(idx_q, dtype=torch.int32)
+    idx_k = torch.tensor(idx_k, dtype=torch.int32)
+    cu_sal = torch.tensor(cu_sal, dtype=torch.int32)
+    dv = torch.zeros(Tk, Hkv, D)
+    dv[idx_k.long()] = torch.randn(idx_k.numel(), Hkv, D, generator=g) * 2.0
+    dv = dv.bfloat16()
+    o_sal = torch.randn(idx_q.numel(), H, D, generator=g).bfloat16()
+    return dict(q=q, k=k, dv=dv, c_old=c_old, o_sal=o_sal, cu_q=cu_q, cu_k=cu_k, cu_sal=cu_sal, idx_q=idx_q,
+                idx_k=idx_k, response_only=response_only, max_q=max(lens_q), max_k=max(lens_k))
+
+
+def run_gpu(case, dev, v_mn_major):
+    from dyllm_b200.attention_ops import attention_sparse_varlen
+
+    d = lambda t: t.to(dev)
+    Tq = case["q"].size(0)
+    stats = torch.zeros(Tq, 3, device=dev)
+    mask = torch.empty(Tq, dtype=torch.bool, device=dev)
+    out = attention_sparse_varlen(d(case["q"]), d(case["k"]), d(case["dv"]), d(case["c_old"]), d(case["o_sal"]),
+                                  d(case["cu_q"]), d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]),
+                                  d(case["idx_q"]), stats, mask, TAU, case["response_only"],
+                                  d(case["idx_k"]) if case["response_only"] else None, v_mn_major=v_mn_major)
+    from dyllm_b200 import _lib
+    assert _lib.load().dyllm_device_status() == 0
+    return out.cpu(), stats.cpu(), mask.cpu()
+
+
+def check(case, got):
+    out, stats, mask = got
+    want_o, want_stats, want_mask = orc.attention_sparse_varlen(
+        case["q"], case["k"], case["dv"], case["c_old"], case["o_sal"], case["cu_q"], case["cu_k"], case["cu_sal"],
+        case["idx_q"], TAU)
+    diff = (out.float() - want_o.float())
+    scale = max(1.0, want_o.float().abs().max().item())
+    assert diff.abs().max().item() / scale <= 2e-2
+    assert (diff.norm() / want_o.float().norm()).item() <= 1e-2
+    torch.testing.assert_close(stats, want_stats, rtol=2e-3, atol=2e-2)
+    # decisions: bit-exact wherever the oracle's cosine is at least 1e-4 away from the threshold
+    cosv = orc.cosine_values(want_stats)
+    clear = (cosv - TAU).abs() >= 1e-4
+    assert torch.equal(mask[clear], want_mask[clear])
+    assert clear.float().mean() > 0.99
+
+
+CASES = [
+    # batch, prompt, response, H, Hkv, response_only, salient per sequence
+    (1, 256, 256, 4, 4, False, 26),
+    (1, 256, 256, 4, 4, True, 26),
+    (2, 100, 156, 4, 2, False, 7),
+    (3, 64, 64, 2, 1, True, 64),
+    (2, 256, 256, 2, 2, False, 0),
+    (2, 128, 256, 2, 2, True, 200),   # more than one salient tile
+    (2, 300, 212, 4, 4, False, [1, 130]),
+]
+
+
+@pytest.mark.parametrize("v_mn_major", [0, 1], ids=["vT", "vMN"])
+@pytest.mark.parametrize("case_id", range(len(CASES)))
+def test_attention_sparse_varlen_matches_oracle(cuda_device, case_id, v_mn_major):
+    batch, prompt, response, H, Hkv, ro, sal = CASES[case_id]
+    case = make_case(batch, prompt, response, H, Hkv, ro, sal, seed=case_id)
+    check(case, run_gpu(case, cuda_device, v_mn_major))
+
+
+@pytest.mark.parametrize("v_mn_major", [0, 1], ids=["vT", "vMN"])
+def test_attention_ragged_lengths(cuda_device, v_mn_major):
+    case = make_case(4, 200, 180, 4, 2, False, [3, 0, 50, 140], seed=42, ragged=True)
+    check(case, run_gpu(case, cuda_device, v_mn_major))
+    case = make_case(4, 200, 180, 4, 2, True, [3, 0, 50, 140], seed=43, ragged=True)
+    check(case, run_gpu(case, cuda_device, v_mn_major))
+
+
+def test_attention_config_shape_and_determinism(cuda_device):
+    """LLaDA-8B layer shape (32 heads), batch 2; two runs give identical bits."""
+    case = make_case(2, 256, 256, 32, 32, False, 26, seed=7)
+    a = run_gpu(case, cuda_device, 1)
+    b = run_gpu(case, cuda_device, 1)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    check(case, a)
+
+
+def test_attention_delta_identity(cuda_device):
+    """Size-independent property: with dV = 0 the output equals C_old exactly and every cosine is 1."""
+    case = make_case(4, 256, 256, 8, 8, False, 0, seed=9)
+    out, stats, mask = run_gpu(case, cuda_device, 1)
+    assert torch.equal(out, case["c_old"])
+    assert not bool(mask.any())
+
+
+def test_attention_argument_errors(cuda_device):
+    from dyllm_b200.attention_ops import attention_kernel_info, attention_sparse_varlen
+
+    case = make_case(1, 64, 64, 2, 2, False, 4, seed=1)
+    d = lambda t: t.to(cuda_device)
+    Tq = case["q"].size(0)
+    stats = torch.zeros(Tq, 3, device=cuda_device)
+    mask = torch.empty(Tq, dtype=torch.bool, device=cuda_device)
+    args = [d(case["q"]), d(case["k"]), d(case["dv"]), d(case["c_old"]), d(case["o_sal"]), d(case["cu_q"]),
+            d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]), d(case["idx_q"]), stats, mask, TAU]
+    with pytest.raises(RuntimeError):
+        attention_sparse_varlen(*args[:9], Tq + 1, *args[10:])  # total_seqlen mismatch
+    bad = list(args)
+    bad[11] = d(case["idx_q"]).long()
+    with pytest.raises(RuntimeError):
+        attention_sparse_varlen(*bad)  # idx must be int32
+    bad = list(args)
+    bad[0] = d(case["q"])[:, :, :64].contiguous()
+    with pytest.raises(RuntimeError):
+        attention_sparse_varlen(*bad)
+    info = attention_kernel_info(128)
+    assert len(info) == 10 and info[9] == 1 and info[0] > 0 and info[5] >= 1
