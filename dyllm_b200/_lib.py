@@ -38,6 +38,7 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_cache_dest_rows": (I, [P, P, P, P, I, I, P, P, P]),
     "dyllm_attention_sparse_workspace_bytes": (Z, [I, I]),
     "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, F, P, Z, I, P]),
+    "dyllm_attention_salient_rows": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P]),
     "dyllm_attention_kernel_info": (I, [I, P]),
 }
 

@@ -141,4 +141,34 @@ def fused_offset_launch(idxs, num_idxs, cu_promptlens, cu_salientlens, out_tenso
          cu_promptlens.numel() - 1, ptr(out_tensor), int(max_threads), stream_ptr(device))
 
 
-__all__ = ["attention_sparse_varlen", "fused_offset_launch", "attention_kernel_info"]
+
+
+def attention_salient_rows(q, k, v, cu_seqlens_k, cu_salientlens, idx_salient_row, max_rows_per_seq: int,
+                           num_salient: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Exact non-causal attention of the salient query rows against the whole K / V of their sequence.
+
+    Replaces ``flash_attn_varlen_func(q[idx_salient_row], k, v_cache, cu_seqlens_q=cu_salientlens, ...)`` of
+    dyllm/model_executor/layers/attention.py:76-87 without materialising ``q[idx]``.  ``idx_salient_row`` is
+    int32 in Q space; rows past ``cu_salientlens[-1]`` of ``out`` are left untouched.
+    """
+    dev = q.device
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_tensor(t, n, dev, torch.bfloat16, 3)
+    for t, n in ((cu_seqlens_k, "cu_seqlens_k"), (cu_salientlens, "cu_salientlens"), (idx_salient_row, "idx_salient_row")):
+        _check_tensor(t, n, dev, torch.int32, 1)
+    if k.shape != v.shape:
+        raise RuntimeError("K and V must have the same shape")
+    if q.size(2) != 128 or k.size(2) != 128:
+        raise RuntimeError(f"supported head dimension is 128; got {q.size(2)}")
+    n = idx_salient_row.numel() if num_salient is None else num_salient
+    if out is None:
+        out = torch.empty((n, q.size(1), q.size(2)), dtype=q.dtype, device=dev)
+    if n == 0 or max_rows_per_seq == 0:
+        return out
+    call("dyllm_attention_salient_rows", ptr(q), ptr(k), ptr(v), ptr(out), ptr(cu_seqlens_k), cu_seqlens_k.numel() - 1,
+         int(max_rows_per_seq), q.size(0), k.size(0), q.size(1), k.size(1), q.size(2), ptr(cu_salientlens),
+         ptr(idx_salient_row), stream_ptr(dev))
+    return out
+
+
+__all__ = ["attention_sparse_varlen", "attention_salient_rows", "fused_offset_launch", "attention_kernel_info"]

@@ -33,6 +33,9 @@ constexpr uint32_t kAttnTmemCols = 256;          // S: columns 0..127, O: column
 constexpr float kNegBig = -1.0e30f;
 
 struct AttnParams {
+  const __nv_bfloat16* q;        // [Tq, H, D] (EXACT: rows gathered through idx_q)
+  const int32_t* idx_q;          // EXACT: salient query rows (Q space), grouped by sequence
+  __nv_bfloat16* o_sal;          // EXACT: [num_salient, H, D] output
   const __nv_bfloat16* k;        // [Tk, Hkv, D]
   const __nv_bfloat16* v;        // [Tk, Hkv, D] delta-V (non-zero on salient key rows only)
   const __nv_bfloat16* c_old;    // [Tq, H, D]
@@ -54,13 +57,22 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// EXACT = false: the delta attention described at the top of this file.
+// EXACT = true: plain softmax attention of the salient query rows against the full K / V of their
+// sequence, o_sal[i] = softmax(q[idx_q[i]] K^T / sqrt(D)) V: the query tile is gathered through idx_q,
+// pass B walks over all key tiles (K and V tiles by TMA; V is used as loaded, as an MN-major operand)
+// and the epilogue stores O / rowsum.
+template <bool EXACT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
-delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                       const AttnParams p) {
+attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   const int q_tile = blockIdx.x % p.n_qtiles;
   const int h = (blockIdx.x / p.n_qtiles) % p.H;
   const int b = blockIdx.x / (p.n_qtiles * p.H);
-  const int q_begin = p.cu_q[b], q_end = p.cu_q[b + 1];
+  const int sal_begin = p.cu_sal[b];
+  const int n_sal = p.cu_sal[b + 1] - sal_begin;
+  const int q_begin = EXACT ? 0 : p.cu_q[b];
+  const int q_end = EXACT ? n_sal : p.cu_q[b + 1];   // EXACT: rows are positions in the salient list
   const int q0 = q_begin + q_tile * kBQ;
   if (q0 >= q_end)
     return;
@@ -68,16 +80,15 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int len_k = k_end - k_begin;
   const int num_kt = (len_k + kBKeys - 1) / kBKeys;
   const int hk = h / (p.H / p.Hkv);
-  const int sal_begin = p.cu_sal[b];
-  const int n_sal = p.cu_sal[b + 1] - sal_begin;
-  const int num_st = (n_sal + kBKeys - 1) / kBKeys;
+  const int num_st = EXACT ? num_kt : (n_sal + kBKeys - 1) / kBKeys;   // tiles of pass B
+  const bool v_mn_major = EXACT ? true : (p.v_mn_major != 0);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;                      // Q tile
   uint8_t* kv_smem0 = smem + kTileBytes;       // K stage 0 / gathered Ksal, later P
   uint8_t* kv_smem1 = smem + 2 * kTileBytes;   // K stage 1 / gathered dV
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full, s_empty, b_full, p_full, pv_done;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full, s_empty, b_full, p_full, pv_done, a_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -86,19 +97,23 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(&q_full, 1);
+    mbar_init(&q_full, EXACT ? 128 : 1);
     mbar_init(&k_full[0], 1);
     mbar_init(&k_full[1], 1);
     mbar_init(&k_empty[0], 1);
     mbar_init(&k_empty[1], 1);
     mbar_init(&s_full, 1);
     mbar_init(&s_empty, 128);
-    mbar_init(&b_full, 128);
+    mbar_init(&b_full, EXACT ? 1 : 128);
     mbar_init(&p_full, 128);
     mbar_init(&pv_done, 1);
+    mbar_init(&a_done, 1);
     fence_mbar_init();
-    tma_prefetch_desc(&tmap_q);
+    if (!EXACT)
+      tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
+    if (EXACT)
+      tma_prefetch_desc(&tmap_v);
   }
   if (warp == 1) {
     tmem_alloc(&tmem_slot, kAttnTmemCols);
@@ -112,7 +127,7 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer: Q once, K tiles
-    if (lane == 0) {
+    if (!EXACT && lane == 0) {
       mbar_arrive_expect_tx(&q_full, kTileBytes);
       tma_load_2d(q_smem, &tmap_q, &q_full, h * kD, q0);
       tma_load_2d(q_smem + kHalfBytes, &tmap_q, &q_full, h * kD + 64, q0);
@@ -128,10 +143,27 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
       __syncwarp();
     }
+    if (EXACT) {
+      // pass B: K tile into buffer 0 and V tile into buffer 1 once both are free
+      for (int st = 0; st < num_st; ++st) {
+        if (st == 0)
+          mbar_wait(&a_done, 0, &abort_flag, p.status_word, 311);
+        else
+          mbar_wait(&pv_done, (st - 1) & 1, &abort_flag, p.status_word, 312);
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&b_full, 2 * kTileBytes);
+          tma_load_2d(kv_smem0, &tmap_k, &b_full, hk * kD, k_begin + st * kBKeys);
+          tma_load_2d(kv_smem0 + kHalfBytes, &tmap_k, &b_full, hk * kD + 64, k_begin + st * kBKeys);
+          tma_load_2d(kv_smem1, &tmap_v, &b_full, hk * kD, k_begin + st * kBKeys);
+          tma_load_2d(kv_smem1 + kHalfBytes, &tmap_v, &b_full, hk * kD + 64, k_begin + st * kBKeys);
+        }
+        __syncwarp();
+      }
+    }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
-    const uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, p.v_mn_major ? 1 : 0);
+    const uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, v_mn_major ? 1 : 0);
     const uint32_t q_addr = smem_u32(q_smem);
     mbar_wait(&q_full, 0, &abort_flag, p.status_word, 302);
     for (int t = 0; t < num_kt + num_st; ++t) {
@@ -161,6 +193,8 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (!sal_tile)
           umma_commit(&k_empty[t & 1]);
         umma_commit(&s_full);
+        if (EXACT && t == num_kt - 1)
+          umma_commit(&a_done);
       }
       __syncwarp();
       if (sal_tile) {
@@ -175,7 +209,7 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             const uint64_t a_desc =
                 umma_smem_desc_sw128(p_addr + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16, 1024);
             uint64_t b_desc;
-            if (p.v_mn_major)  // [keys][d]: 16 keys = 2048 bytes per step, d halves 16 KB apart
+            if (v_mn_major)  // [keys][d]: 16 keys = 2048 bytes per step, d halves 16 KB apart
               b_desc = umma_smem_desc_sw128(v_addr + kk * 2048, kHalfBytes, 1024);
             else               // [d][keys]: key halves 16 KB apart, 32 bytes per step inside a half
               b_desc = umma_smem_desc_sw128(v_addr + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16, 1024);
@@ -193,6 +227,21 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint32_t t_lane = static_cast<uint32_t>(qd * 32) << 16;
     const float c = p.scale_log2;
     float m = kNegBig, l = 0.f;
+
+    if (EXACT) {
+      // gather this thread's query row (or zeros past the list) into the swizzled Q tile
+      const bool have = q0 + row < q_end;
+      const int64_t qrow = have ? p.idx_q[sal_begin + q0 + row] : 0;
+      const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + (qrow * p.H + h) * kD);
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint4 qv = have ? __ldg(qsrc + ch) : zero;
+        *reinterpret_cast<uint4*>(q_smem + (ch >> 3) * kHalfBytes + sw128_offset(row, ch & 7)) = qv;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&q_full);
+    }
 
     // pass A: running maximum and sum over all keys
     for (int kt = 0; kt < num_kt; ++kt) {
@@ -231,15 +280,14 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const float mc = m * c;
     for (int st = 0; st < num_st; ++st) {
       const int t = num_kt + st;
-      if (st > 0)
+      // The buffers are free for tile 0 once the last Q K^T product is complete: s_full of the last
+      // key tile was observed above and is committed after every earlier MMA.  Later tiles wait for the
+      // previous P dV product.
+      if (!EXACT && st > 0)
         mbar_wait(&pv_done, (st - 1) & 1, &abort_flag, p.status_word, 308);
-      else if (num_kt > 0) {
-        // stage buffers are free once the last Q K^T products are complete; s_full of the last key
-        // tile was observed above, and it is committed after every earlier MMA
-      }
-      const int n_tile = min(kBKeys, n_sal - st * kBKeys);
+      const int n_tile = min(kBKeys, (EXACT ? len_k : n_sal) - st * kBKeys);
       // gather slot `row`: K row and dV row of one salient key, or zeros
-      {
+      if (!EXACT) {
         const bool have = row < n_tile;
         const int64_t krow = have ? p.idx_k[sal_begin + st * kBKeys + row] : 0;
         const uint4* ksrc = reinterpret_cast<const uint4*>(p.k + (krow * p.Hkv + hk) * kD);
@@ -250,7 +298,7 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           const uint4 kv = have ? __ldg(ksrc + ch) : zero;
           *reinterpret_cast<uint4*>(kv_smem0 + (ch >> 3) * kHalfBytes + sw128_offset(row, ch & 7)) = kv;
         }
-        if (p.v_mn_major) {
+        if (v_mn_major) {
 #pragma unroll
           for (int ch = 0; ch < 16; ++ch) {
             const uint4 vv = have ? __ldg(vsrc + ch) : zero;
@@ -315,9 +363,9 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int r = q0 + row;
     const bool live = r < q_end;
     const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-    const int64_t off = (static_cast<int64_t>(live ? r : q0) * p.H + h) * kD;
-    const __nv_bfloat16* cold = p.c_old + off;
-    __nv_bfloat16* dst = p.out + off;
+    const int64_t off = (static_cast<int64_t>((live ? r : q0) + (EXACT ? sal_begin : 0)) * p.H + h) * kD;
+    const __nv_bfloat16* cold = EXACT ? nullptr : p.c_old + off;
+    __nv_bfloat16* dst = (EXACT ? p.o_sal : p.out) + off;
     float dot = 0.f, nn = 0.f, no = 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < kD; c0 += 32) {
@@ -334,7 +382,7 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         uint4 oldv[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          oldv[j] = __ldg(reinterpret_cast<const uint4*>(cold + c0) + j);
+          oldv[j] = EXACT ? make_uint4(0, 0, 0, 0) : __ldg(reinterpret_cast<const uint4*>(cold + c0) + j);
         const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(oldv);
         uint32_t pk[16];
 #pragma unroll
@@ -356,7 +404,7 @@ delta_attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           reinterpret_cast<uint4*>(dst + c0)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
       }
     }
-    if (live) {
+    if (live && !EXACT) {
       float* ps = p.partial + (static_cast<int64_t>(h) * p.Tq + r) * 3;
       ps[0] = dot;
       ps[1] = nn;
@@ -467,7 +515,26 @@ attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, cons
   }
 }
 
-bool g_attn_smem_set[64] = {false};
+bool g_attn_smem_set[2][64] = {{false}, {false}};
+
+template <bool EXACT>
+int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+                     int64_t blocks, cudaStream_t s) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = (dev < 0 || dev >= 64) ? 0 : dev;
+  if (!g_attn_smem_set[EXACT ? 1 : 0][dev]) {
+    if (cudaFuncSetAttribute(attention_kernel<EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kAttnSmem)) != cudaSuccess)
+      return set_error(DYLLM_ERR_CUDA, "attention: cudaFuncSetAttribute failed: %s",
+                       cudaGetErrorString(cudaGetLastError()));
+    g_attn_smem_set[EXACT ? 1 : 0][dev] = true;
+  }
+  DYLLM_REQUIRE(blocks > 0 && blocks < (1ll << 31), DYLLM_ERR_UNSUPPORTED, "attention: grid of %lld blocks",
+                static_cast<long long>(blocks));
+  attention_kernel<EXACT><<<static_cast<unsigned>(blocks), kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+  return check_launch(EXACT ? "salient_attention" : "delta_attention");
+}
 
 }  // namespace
 }  // namespace dyllm
@@ -524,17 +591,6 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   if (rc != DYLLM_OK)
     return rc;
 
-  int dev = 0;
-  cudaGetDevice(&dev);
-  dev = (dev < 0 || dev >= 64) ? 0 : dev;
-  if (!g_attn_smem_set[dev]) {
-    if (cudaFuncSetAttribute(delta_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kAttnSmem)) != cudaSuccess)
-      return set_error(DYLLM_ERR_CUDA, "attention_sparse_varlen: cudaFuncSetAttribute failed: %s",
-                       cudaGetErrorString(cudaGetLastError()));
-    g_attn_smem_set[dev] = true;
-  }
-
   AttnParams p = {};
   p.k = static_cast<const __nv_bfloat16*>(k);
   p.v = static_cast<const __nv_bfloat16*>(v);
@@ -554,9 +610,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   p.v_mn_major = v_mn_major != 0;
   p.status_word = device_status_word();
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
-  DYLLM_REQUIRE(blocks < (1ll << 31), DYLLM_ERR_UNSUPPORTED, "attention_sparse_varlen: grid too large");
-  delta_attention_kernel<<<static_cast<unsigned>(blocks), kAttnThreads, kAttnSmem, s>>>(tq, tk, p);
-  rc = check_launch("delta_attention");
+  rc = launch_attention<false>(tq, tk, tk, p, blocks, s);
   if (rc != DYLLM_OK)
     return rc;
 
@@ -567,16 +621,64 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   return check_launch("attention_finalize");
 }
 
+int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, void* o_sal,
+                                 const int32_t* cu_seqlens_k, int batch, int max_rows_per_seq, int total_q,
+                                 int total_k, int num_heads, int num_kv_heads, int head_dim,
+                                 const int32_t* cu_salientlens, const int32_t* idx_salient_row_q, void* stream) {
+  DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "attention_salient_rows: head_dim %d (only 128 is built)",
+                head_dim);
+  DYLLM_REQUIRE(batch > 0 && total_q > 0 && total_k > 0 && max_rows_per_seq >= 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "attention_salient_rows: batch %d Tq %d Tk %d max rows %d", batch, total_q, total_k, max_rows_per_seq);
+  DYLLM_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "attention_salient_rows: query heads (%d) must be a positive multiple of KV heads (%d)", num_heads,
+                num_kv_heads);
+  if (max_rows_per_seq == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(q && k && v && o_sal && cu_seqlens_k && cu_salientlens && idx_salient_row_q,
+                DYLLM_ERR_INVALID_ARGUMENT, "attention_salient_rows: null pointer");
+  for (const void* ptr16 : {q, k, v, static_cast<const void*>(o_sal)})
+    DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(ptr16) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT,
+                  "attention_salient_rows: tensors must be 16-byte aligned");
+  CUtensorMap tk, tv;
+  int rc = encode_tmap_2d_bf16(&tk, k, total_k, static_cast<uint64_t>(num_kv_heads) * kD,
+                               static_cast<uint64_t>(num_kv_heads) * kD, kBKeys, 64, true);
+  if (rc != DYLLM_OK)
+    return rc;
+  rc = encode_tmap_2d_bf16(&tv, v, total_k, static_cast<uint64_t>(num_kv_heads) * kD,
+                           static_cast<uint64_t>(num_kv_heads) * kD, kBKeys, 64, true);
+  if (rc != DYLLM_OK)
+    return rc;
+  AttnParams p = {};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.idx_q = idx_salient_row_q;
+  p.o_sal = static_cast<__nv_bfloat16*>(o_sal);
+  p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  p.cu_q = cu_salientlens;
+  p.cu_k = cu_seqlens_k;
+  p.cu_sal = cu_salientlens;
+  p.H = num_heads;
+  p.Hkv = num_kv_heads;
+  p.Tq = total_q;
+  p.Tk = total_k;
+  p.n_qtiles = cdiv_i(max_rows_per_seq, kBQ);
+  p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
+  p.v_mn_major = 1;
+  p.status_word = device_status_word();
+  const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
+  return launch_attention<true>(tk, tk, tv, p, blocks, static_cast<cudaStream_t>(stream));
+}
+
 int dyllm_attention_kernel_info(int dim, int64_t* info10) {
   DYLLM_REQUIRE(info10, DYLLM_ERR_INVALID_ARGUMENT, "attention_kernel_info: null output");
   DYLLM_REQUIRE(dim == 128, DYLLM_ERR_UNSUPPORTED, "attention_kernel_info: head_dim %d (only 128 is built)", dim);
   cudaFuncAttributes attr;
-  if (cudaFuncGetAttributes(&attr, delta_attention_kernel) != cudaSuccess)
+  if (cudaFuncGetAttributes(&attr, attention_kernel<false>) != cudaSuccess)
     return set_error(DYLLM_ERR_CUDA, "attention_kernel_info: %s", cudaGetErrorString(cudaGetLastError()));
   int blocks_per_sm = 0;
-  cudaFuncSetAttribute(delta_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                        static_cast<int>(kAttnSmem));
-  const bool ok = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, delta_attention_kernel, kAttnThreads,
+  const bool ok = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, attention_kernel<false>, kAttnThreads,
                                                                 kAttnSmem) == cudaSuccess;
   info10[0] = attr.numRegs;
   info10[1] = static_cast<int64_t>(attr.localSizeBytes);

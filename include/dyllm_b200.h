@@ -187,6 +187,17 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   int num_salient, float* cosine_stats, uint8_t* cosine_out, float threshold,
                                   void* workspace, size_t workspace_bytes, int v_mn_major, void* stream);
 
+/* Exact attention of the salient query rows against the whole K / V of their sequence (non-causal):
+ * o_sal[i] = softmax(q[idx_salient_row_q[i]] K^T / sqrt(128)) V, i grouped by sequence through
+ * cu_salientlens.  q: [total_q, num_heads, 128], k, v: [total_k, num_kv_heads, 128], o_sal:
+ * [num_salient, num_heads, 128], bf16.  max_rows_per_seq is an upper bound of the salient rows of one
+ * sequence (it sizes the grid; the device-side counts decide the work).
+ * ref: dyllm/model_executor/layers/attention.py:76-87 (flash_attn_varlen_func on q[idx_salient_row]). */
+int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, void* o_sal,
+                                 const int32_t* cu_seqlens_k, int batch, int max_rows_per_seq, int total_q,
+                                 int total_k, int num_heads, int num_kv_heads, int head_dim,
+                                 const int32_t* cu_salientlens, const int32_t* idx_salient_row_q, void* stream);
+
 /* Launch resources of the main attention kernel: [registers, local bytes, static shared bytes,
  * dynamic shared bytes, threads per block, resident blocks per SM, query rows per block, keys per
  * tile, head-dim split, ok].  ref: dyllm/csrc/attention/attention.cpp:184-208. */

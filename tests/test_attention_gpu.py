@@ -148,3 +148,28 @@ def test_attention_argument_errors(cuda_device):
         attention_sparse_varlen(*bad)
     info = attention_kernel_info(128)
     assert len(info) == 10 and info[9] == 1 and info[0] > 0 and info[5] >= 1
+
+
+@pytest.mark.parametrize("case_id", range(len(CASES)))
+def test_attention_salient_rows_matches_exact_attention(cuda_device, case_id):
+    """Replacement of the flash-attn call on q[idx_salient_row]."""
+    from dyllm_b200 import _lib
+    from dyllm_b200.attention_ops import attention_salient_rows
+
+    batch, prompt, response, H, Hkv, ro, sal = CASES[case_id]
+    case = make_case(batch, prompt, response, H, Hkv, ro, sal, seed=100 + case_id)
+    g = torch.Generator().manual_seed(case_id)
+    v = torch.randn(case["k"].shape, generator=g).bfloat16()
+    d = lambda t: t.to(cuda_device)
+    n = case["idx_q"].numel()
+    out = torch.full((n + 3, H, 128), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    attention_salient_rows(d(case["q"]), d(case["k"]), d(v), d(case["cu_k"]), d(case["cu_sal"]), d(case["idx_q"]),
+                           max_rows_per_seq=case["max_q"], num_salient=n, out=out)
+    assert _lib.load().dyllm_device_status() == 0
+    want = orc.exact_attention_varlen(case["q"][case["idx_q"].long()], case["k"], v, case["cu_sal"], case["cu_k"])
+    got = out[:n].float().cpu()
+    if n:
+        diff = got - want
+        assert diff.abs().max().item() <= 2e-2
+        assert (diff.norm() / want.norm()).item() <= 1e-2
+    assert bool((out[n:] == 7.0).all())
