@@ -40,6 +40,7 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, F, P, Z, I, P]),
     "dyllm_attention_salient_rows": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P]),
     "dyllm_attention_kernel_info": (I, [I, P]),
+    "dyllm_delta_v_update": (I, [P, P, P, I, P, I, P, P]),
 }
 
 _lib = None

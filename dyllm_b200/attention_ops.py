@@ -34,25 +34,31 @@ def _check_tensor(t, name, device, dtype, dim):
 def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int,
                             total_seqlen: int, cu_salientlens, idx_salient_row, cosine_stats, cosine_out,
                             threshold: float = 0.0, is_q_pruned: bool = False, idx_salient_row_k=None,
-                            force_mask_v_rows: int = -1, v_mn_major: int = 1) -> torch.Tensor:
+                            force_mask_v_rows: int = -1, v_layout: int = 1) -> torch.Tensor:
     """ref: dyllm/csrc/attention/attention.cpp:64-179.
 
     Same arguments, checks and return value (a fresh ``O`` shaped like ``Q``).  ``force_mask_v_rows``
     is accepted and ignored (it switches between two load strategies of the reference kernel that
     compute the same result).  ``V`` must be zero outside the listed salient key rows, as the
-    reference's caller builds it.
+    reference's caller builds it.  ``v_layout`` (extension): bit 0 = feed the delta-V tile as an
+    MN-major operand, bit 1 = ``V`` is compact ``[num_salient, Hkv, D]`` (row i = key
+    ``idx_salient_row_k[i]``) instead of the zero-padded ``[T_k, Hkv, D]`` tensor.
     """
     if not (isinstance(Q, torch.Tensor) and Q.is_cuda):
         raise RuntimeError("Q must be CUDA")
     dev, bf16, i32 = Q.device, torch.bfloat16, torch.int32
     for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (C, "C"), (o_sal, "o_sal")):
         _check_tensor(t, n, dev, bf16, 3)
+    compact = bool(v_layout & 2)
     for t, n in ((cu_seqlens_q, "cu_seqlens_q"), (cu_seqlens_k, "cu_seqlens_k"), (cu_salientlens, "cu_salientlens"),
                  (idx_salient_row, "idx_salient_row")):
         _check_tensor(t, n, dev, i32, 1)
     _check_tensor(cosine_stats, "cosine_stats", dev, torch.float32, 2)
     _check_tensor(cosine_out, "cosine_out", dev, torch.bool, 1)
-    if K.shape != V.shape:
+    if compact:
+        if V.shape != (idx_salient_row.numel(), K.size(1), K.size(2)):
+            raise RuntimeError("compact V must be [idx_salient_row.numel(), K.size(1), K.size(2)]")
+    elif K.shape != V.shape:
         raise RuntimeError("K and V must have the same shape")
     if not (Q.size(0) > 0 and K.size(0) > 0):
         raise RuntimeError("Q and K/V token dimensions must be non-empty")
@@ -97,7 +103,7 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     call("dyllm_attention_sparse_varlen", ptr(Q), ptr(K), ptr(V), ptr(C), ptr(o_sal), ptr(out), ptr(cu_seqlens_q),
          ptr(cu_seqlens_k), cu_seqlens_q.numel() - 1, int(max_seqlen_q), int(max_seqlen_k), Q.size(0), K.size(0), H,
          K.size(1), Q.size(2), ptr(cu_salientlens), ptr(idx_salient_row), ptr(idx_k), idx_salient_row.numel(),
-         ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_mn_major), stream_ptr(dev))
+         ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_layout), stream_ptr(dev))
     return out
 
 

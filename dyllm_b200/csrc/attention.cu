@@ -48,6 +48,7 @@ struct AttnParams {
   int H, Hkv, Tq, Tk, n_qtiles;
   float scale_log2;              // log2(e) / sqrt(D)
   int v_mn_major;                // 1: dV tile kept [keys][d] (MN-major operand); 0: transposed while gathering
+  int v_compact;                 // 1: v holds one row per salient key, in list order; 0: v is [Tk, Hkv, D]
   int* status_word;
 };
 
@@ -291,7 +292,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const bool have = row < n_tile;
         const int64_t krow = have ? p.idx_k[sal_begin + st * kBKeys + row] : 0;
         const uint4* ksrc = reinterpret_cast<const uint4*>(p.k + (krow * p.Hkv + hk) * kD);
-        const uint4* vsrc = reinterpret_cast<const uint4*>(p.v + (krow * p.Hkv + hk) * kD);
+        const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + st * kBKeys + (have ? row : 0)) : krow;
+        const uint4* vsrc = reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD);
         const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int ch = 0; ch < 16; ++ch) {
@@ -555,7 +557,9 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   int num_kv_heads, int head_dim, const int32_t* cu_salientlens,
                                   const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
                                   int num_salient, float* cosine_stats, uint8_t* cosine_out, float threshold,
-                                  void* workspace, size_t workspace_bytes, int v_mn_major, void* stream) {
+                                  void* workspace, size_t workspace_bytes, int v_layout, void* stream) {
+  const int v_mn_major = (v_layout & 1) ? 1 : 0;
+  const int v_compact = (v_layout & 2) ? 1 : 0;
   DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "attention_sparse_varlen: head_dim %d (only 128 is built)",
                 head_dim);
   DYLLM_REQUIRE(batch > 0 && total_q > 0 && total_k > 0, DYLLM_ERR_INVALID_ARGUMENT,
@@ -607,7 +611,8 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   p.Tk = total_k;
   p.n_qtiles = cdiv_i(max_seqlen_q, kBQ);
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
-  p.v_mn_major = v_mn_major != 0;
+  p.v_mn_major = v_mn_major;
+  p.v_compact = v_compact;
   p.status_word = device_status_word();
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
   rc = launch_attention<false>(tq, tk, tk, p, blocks, s);

@@ -83,6 +83,39 @@ scatter_rows_kernel(uint4* __restrict__ cache, const uint4* __restrict__ new_row
   }
 }
 
+// dv[i] = v_new[i] - cache[rows[i]]; cache[rows[i]] = v_new[i]; one warp per row.
+__global__ void __launch_bounds__(kCopyWarps * 32)
+delta_v_update_kernel(const uint4* __restrict__ v_new, uint4* __restrict__ cache, const int32_t* __restrict__ rows,
+                      int num_rows, const int32_t* __restrict__ num_rows_dev, int vecs, uint4* __restrict__ dv) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
+  for (int i = blockIdx.x * kCopyWarps + warp; i < n; i += gridDim.x * kCopyWarps) {
+    const int64_t r = rows[i];
+    if (r < 0)
+      continue;
+    uint4* crow = cache + r * vecs;
+    const uint4* nrow = v_new + static_cast<int64_t>(i) * vecs;
+    uint4* drow = dv + static_cast<int64_t>(i) * vecs;
+    for (int v = lane; v < vecs; v += 32) {
+      const uint4 nv = __ldg(nrow + v);
+      const uint4 ov = crow[v];
+      uint4 out;
+      const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nv);
+      const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+      __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(n2[j]);
+        const float2 b = __bfloat1622float2(o2[j]);
+        d2[j] = __floats2bfloat162_rn(a.x - b.x, a.y - b.y);
+      }
+      drow[v] = out;
+      crow[v] = nv;
+    }
+  }
+}
+
 int check_common(const char* name, const void* cache, const void* other, const int64_t* seq_starts,
                  const void* cu, const int64_t* seq_ids, int batch, int rows, int width, int elem_bytes) {
   DYLLM_REQUIRE(batch >= 0 && rows >= 0 && width > 0 && elem_bytes > 0, DYLLM_ERR_INVALID_ARGUMENT,
@@ -150,6 +183,24 @@ int dyllm_cache_reset_block(void* cache, const void* in, const int64_t* seq_star
                 "cache_reset_block: null cu_seqlens_k");
   return launch_rows<true>("cache_reset_block", cache, const_cast<void*>(in), seq_starts, cu_seqlens_q,
                            cu_seqlens_k, seq_ids, batch, total_rows, width, elem_bytes, stream);
+}
+
+int dyllm_delta_v_update(const void* v_new, void* cache, const int32_t* rows, int num_rows,
+                         const int32_t* num_rows_dev, int width, void* dv, void* stream) {
+  DYLLM_REQUIRE(num_rows >= 0 && width > 0, DYLLM_ERR_INVALID_ARGUMENT, "delta_v_update: rows %d width %d", num_rows,
+                width);
+  DYLLM_REQUIRE(width % 8 == 0, DYLLM_ERR_UNSUPPORTED, "delta_v_update: width %d is not a multiple of 8", width);
+  if (num_rows == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(v_new && cache && rows && dv, DYLLM_ERR_INVALID_ARGUMENT, "delta_v_update: null pointer");
+  DYLLM_REQUIRE(((reinterpret_cast<uintptr_t>(v_new) | reinterpret_cast<uintptr_t>(cache) |
+                  reinterpret_cast<uintptr_t>(dv)) & 15) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "delta_v_update: buffers must be 16-byte aligned");
+  const int blocks = min(cdiv_i(num_rows, kCopyWarps), sm_count() * 8);
+  delta_v_update_kernel<<<blocks, kCopyWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(v_new), static_cast<uint4*>(cache), rows, num_rows, num_rows_dev, width / 8,
+      static_cast<uint4*>(dv));
+  return check_launch("delta_v_update");
 }
 
 int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t* row_idx, const void* cu_seqlens,

@@ -1,0 +1,360 @@
+"""Host-side mirror of the reference's ``model_executor`` layer interfaces for the saliency path.
+
+Same class names, constructor arguments and ``forward`` signatures as the reference
+(ref: dyllm/model_executor/layers/{attention,linear,layernorm,rotary_embedding,activations,mlp_cache_manage}.py,
+dyllm/distributed/parallel_state.py, dyllm/model_executor/models/llada.py); the bodies call the sm_100a
+kernels through the C ABI instead of flash-attn / cuBLAS-on-gathered-copies / the reference's extension.
+Projections that run on every row (q_proj, o_proj, lm_head) stay ``F.linear``.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch import nn
+
+from . import ops
+from .attention_ops import attention_salient_rows, attention_sparse_varlen
+from .cache_manager import CacheManager
+from .context import get_context, get_metadata
+
+
+# --------------------------------------------------------------------------------------------------
+# distributed helpers (ref: dyllm/distributed/parallel_state.py)
+# --------------------------------------------------------------------------------------------------
+def _world_size() -> int:
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+def _rank() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.Tensor:
+    """SUM all-reduce of the 12-byte-per-token statistics, then ``cosine < threshold``.
+
+    ref: dyllm/distributed/parallel_state.py:52-66.  The decision itself runs in the mask kernel when the
+    statistics live on a GPU.
+    """
+    if _world_size() > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+    if stats.is_cuda and stats.dim() == 2:
+        return ops.cosine_mask(stats, threshold)
+    dot = stats[..., 0]
+    a = stats[..., 1].clamp_min(1e-8)
+    b = stats[..., 2].clamp_min(1e-8)
+    return dot * torch.rsqrt(a) * torch.rsqrt(b) < threshold
+
+
+def divide(numerator: int, denominator: int) -> int:
+    assert numerator % denominator == 0
+    return numerator // denominator
+
+
+# --------------------------------------------------------------------------------------------------
+# linear layers (ref: dyllm/model_executor/layers/linear.py)
+# --------------------------------------------------------------------------------------------------
+class LinearBase(nn.Module):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False, tp_dim: int | None = None):
+        super().__init__()
+        self.tp_dim = tp_dim
+        self.tp_rank = _rank()
+        self.tp_size = _world_size()
+        self.weight = nn.Parameter(torch.empty(output_size, input_size))
+        self.weight.weight_loader = self.weight_loader
+        if bias:
+            self.bias = nn.Parameter(torch.empty(output_size))
+            self.bias.weight_loader = self.weight_loader
+        else:
+            self.register_parameter("bias", None)
+
+
+class ReplicatedLinear(LinearBase):
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        param.data.copy_(loaded_weight)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.weight, self.bias)
+
+
+class ColumnParallelLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False):
+        super().__init__(input_size, divide(output_size, _world_size()), bias, 0)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        shard = param.data.size(self.tp_dim)
+        param.data.copy_(loaded_weight.narrow(self.tp_dim, self.tp_rank * shard, shard))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.weight, self.bias)
+
+    def forward_gathered(self, x: torch.Tensor, idx32: torch.Tensor, num_rows: int) -> torch.Tensor:
+        """``self(x[idx])`` without materialising the gathered copy (tcgen05 GEMM, rows by TMA gather)."""
+        y = ops.gathered_linear(x, self.weight, idx32, num_rows=num_rows)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
+
+
+class MergedColumnParallelLinear(ColumnParallelLinear):
+    def __init__(self, input_size: int, output_sizes: list[int], bias: bool = False):
+        self.output_sizes = output_sizes
+        super().__init__(input_size, sum(output_sizes), bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: int):
+        offset = sum(self.output_sizes[:loaded_shard_id]) // self.tp_size
+        size = self.output_sizes[loaded_shard_id] // self.tp_size
+        dst = param.data.narrow(self.tp_dim, offset, size)
+        dst.copy_(loaded_weight.chunk(self.tp_size, self.tp_dim)[self.tp_rank])
+
+
+class KVParallelLinear(ColumnParallelLinear):
+    def __init__(self, hidden_size: int, head_size: int, total_num_kv_heads: int, bias: bool = False):
+        self.head_size = head_size
+        self.num_kv_heads = divide(total_num_kv_heads, _world_size())
+        super().__init__(hidden_size, 2 * total_num_kv_heads * head_size, bias)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor, loaded_shard_id: str):
+        assert loaded_shard_id in ("k", "v")
+        size = self.num_kv_heads * self.head_size
+        offset = 0 if loaded_shard_id == "k" else size
+        dst = param.data.narrow(self.tp_dim, offset, size)
+        dst.copy_(loaded_weight.chunk(self.tp_size, self.tp_dim)[self.tp_rank])
+
+
+class RowParallelLinear(LinearBase):
+    def __init__(self, input_size: int, output_size: int, bias: bool = False):
+        super().__init__(divide(input_size, _world_size()), output_size, bias, 1)
+
+    def weight_loader(self, param: nn.Parameter, loaded_weight: torch.Tensor):
+        if param.dim() == 1:
+            param.data.copy_(loaded_weight)
+            return
+        shard = param.data.size(self.tp_dim)
+        param.data.copy_(loaded_weight.narrow(self.tp_dim, self.tp_rank * shard, shard))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
+        if self.tp_size > 1:
+            dist.all_reduce(y)
+        return y
+
+
+# --------------------------------------------------------------------------------------------------
+# norm, rotary embedding, activation (ref: layernorm.py:6-53, rotary_embedding.py:8-67, activations.py)
+# --------------------------------------------------------------------------------------------------
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size: int, eps: float = 1e-6) -> None:
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
+        orig = x.dtype
+        xf = x.float()
+        if residual is not None:
+            xf = xf + residual.float()
+            residual = xf.to(orig)
+        var = xf.pow(2).mean(dim=-1, keepdim=True)
+        y = (xf * torch.rsqrt(var + self.eps)).to(orig) * self.weight
+        return y if residual is None else (y, residual)
+
+
+def apply_rotary_emb(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    x1, x2 = torch.chunk(x.float(), 2, dim=-1)
+    return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
+
+
+class RotaryEmbedding(nn.Module):
+    def __init__(self, head_size: int, rotary_dim: int, max_position_embeddings: int, base: float) -> None:
+        super().__init__()
+        assert rotary_dim == head_size
+        inv_freq = 1.0 / (base ** (torch.arange(0, rotary_dim, 2, dtype=torch.float) / rotary_dim))
+        t = torch.arange(max_position_embeddings, dtype=torch.float)
+        freqs = torch.einsum("i,j -> ij", t, inv_freq)
+        # kept out of the module's buffers: the table stays fp32 when the model is cast to bf16
+        self._cos_sin_cache = torch.cat((freqs.cos(), freqs.sin()), dim=-1).unsqueeze_(1)
+
+    @property
+    def cos_sin_cache(self) -> torch.Tensor:
+        return self._cos_sin_cache
+
+    def rotate(self, positions: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        if self._cos_sin_cache.device != x.device:
+            self._cos_sin_cache = self._cos_sin_cache.to(x.device)
+        positions = torch.clamp(positions, 0, self._cos_sin_cache.size(0) - 1)
+        cos, sin = self._cos_sin_cache[positions].chunk(2, dim=-1)
+        return apply_rotary_emb(x, cos, sin)
+
+    def forward(self, positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor):
+        return self.rotate(positions, query), self.rotate(positions, key)
+
+
+class SiluAndMul(nn.Module):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        a, b = x.chunk(2, -1)
+        return F.silu(a) * b
+
+
+# --------------------------------------------------------------------------------------------------
+# FFN-output cache (ref: dyllm/model_executor/layers/mlp_cache_manage.py)
+# --------------------------------------------------------------------------------------------------
+class MLPcache(nn.Module):
+    def __init__(self, hidden_dim: int = 0):
+        super().__init__()
+        self.cache_manager = CacheManager(hidden_dim=hidden_dim)
+
+    def result(self) -> torch.Tensor:
+        """The full ``[T_q, hidden]`` activation of the step after the cache has been updated."""
+        ctx, md = get_context(), get_metadata()
+        if not ctx.is_full and ctx.idx_salient_row_k is not None:
+            return self.cache_manager.get_seqs_block(md.running_seqs_tensor)
+        return self.cache_manager.get_seqs(md.running_seqs_tensor, allow_view=True, seq_ids_list=md.running_seqs)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        ctx, md = get_context(), get_metadata()
+        if ctx.is_full:
+            self.cache_manager.reset_full(x, md.running_seqs_tensor, seq_ids_list=md.running_seqs)
+        else:
+            rows = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
+            self.cache_manager.scatter_update(md.running_seqs_tensor, rows, x)
+        self.cache_manager.finish(md.finished_seqs)
+        return self.result()
+
+
+class LLaDAMLP(nn.Module):
+    """ref: dyllm/model_executor/models/llada.py:26-43."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int) -> None:
+        super().__init__()
+        self.gate_up_proj = MergedColumnParallelLinear(hidden_size, [intermediate_size] * 2, bias=False)
+        self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=False)
+        self.act_fn = SiluAndMul()
+        self.cache_update = MLPcache(hidden_size)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Reference calling convention: ``x`` holds the rows to process (all rows of a dense step, the
+        gathered salient rows of a sparse step)."""
+        y = ops.swiglu_ffn(x, self.gate_up_proj.weight, self.down_proj.weight)
+        if self.down_proj.tp_size > 1:
+            dist.all_reduce(y)
+        return self.cache_update(y)
+
+    def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Sparse step on the full ``[T_q, hidden]`` activation: rows are fetched by TMA gather through the
+        step's salient index list and the down projection scatters straight into the FFN-output cache
+        (replaces gather_rows_2D + MLP + scatter_update, dyllm/model_executor/models/llada.py:184-186)."""
+        ctx, md = get_context(), get_metadata()
+        n = ctx.idx_salient_row.numel()
+        cm = self.cache_update.cache_manager
+        if n:
+            rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
+            if self.down_proj.tp_size > 1:
+                y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
+                                   num_rows=n)
+                dist.all_reduce(y)
+                cm.scatter_update(md.running_seqs_tensor, rows_k, y)
+            else:
+                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor)
+                ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
+                               num_rows=n, out=cm.cache, out_row_map=dest)
+        cm.finish(md.finished_seqs)
+        return self.cache_update.result()
+
+
+# --------------------------------------------------------------------------------------------------
+# attention (ref: dyllm/model_executor/layers/attention.py)
+# --------------------------------------------------------------------------------------------------
+def _dense_attention(q, k, v, ctx, scale):
+    """Non-causal varlen attention of a dense step (library call; outside the saliency path)."""
+    H, Hkv = q.size(1), k.size(1)
+    lens = ctx.context_lens_cpu
+    if len(set(lens)) == 1:
+        B, L = len(lens), lens[0]
+        o = F.scaled_dot_product_attention(
+            q.view(B, L, H, -1).transpose(1, 2), k.view(B, L, Hkv, -1).transpose(1, 2),
+            v.view(B, L, Hkv, -1).transpose(1, 2), scale=scale, enable_gqa=H != Hkv)
+        return o.transpose(1, 2).reshape(B * L, H, -1)
+    outs, pos = [], 0
+    for L in lens:
+        o = F.scaled_dot_product_attention(
+            q[pos : pos + L].transpose(0, 1)[None], k[pos : pos + L].transpose(0, 1)[None],
+            v[pos : pos + L].transpose(0, 1)[None], scale=scale, enable_gqa=H != Hkv)
+        outs.append(o[0].transpose(0, 1))
+        pos += L
+    return torch.cat(outs, dim=0)
+
+
+class Attention(nn.Module):
+    def __init__(self, num_heads, head_dim, scale, num_kv_heads, threshold: float = 0.99):
+        super().__init__()
+        self.num_heads = num_heads
+        self.head_dim = head_dim
+        self.scale = scale
+        self.num_kv_heads = num_kv_heads
+        self.threshold = threshold
+        self.context_cache = CacheManager(self.num_heads * self.head_dim)
+        self.v_cache = CacheManager(self.num_kv_heads * self.head_dim)
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """Dense step: q, k, v hold every row.  Sparse step: ``q`` every query row, ``k`` the packed full
+        key tensor, ``v`` the new value rows of the step's salient tokens (reference convention)."""
+        ctx, md = get_context(), get_metadata()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        seq_t = md.running_seqs_tensor
+
+        if ctx.is_full:
+            o = _dense_attention(q, k, v, ctx, self.scale)
+            self.context_cache.reset_full(o.flatten(-2, -1).contiguous(), seq_t, seq_ids_list=md.running_seqs)
+            self.v_cache.reset_full(v.flatten(-2, -1), seq_t, seq_ids_list=md.running_seqs)
+            self.context_cache.finish(md.finished_seqs)
+            self.v_cache.finish(md.finished_seqs)
+            return o
+
+        is_q_pruned = ctx.idx_salient_row_k is not None
+        rows_k = ctx.idx_salient_row_k if is_q_pruned else ctx.idx_salient_row
+        idx_q32 = ctx.idx_salient_row32
+        n_sal = idx_q32.numel()
+        H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+
+        # delta-V and value-cache update in one pass over the salient rows (attention.py:67-74,89-96)
+        dv = torch.empty((n_sal, Hkv, D), dtype=v.dtype, device=v.device)
+        if n_sal:
+            dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, self.v_cache.seq_start_gpu, seq_t)
+            ops.delta_v_update(v.view(n_sal, Hkv * D), self.v_cache.cache, dest, dv.view(n_sal, Hkv * D))
+        v_full = self.v_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs).view(-1, Hkv, D)
+
+        # exact attention of the salient query rows (attention.py:76-87)
+        o_sal = attention_salient_rows(q, k, v_full, ctx.cu_seqlens_k, ctx.cu_salientlens, idx_q32,
+                                       max_rows_per_seq=max(ctx.max_salient_per_seq, 1), num_salient=n_sal)
+
+        stats = torch.zeros((ctx.total_seqlen, 3), dtype=torch.float32, device=q.device)
+        mask = torch.empty((ctx.total_seqlen,), dtype=torch.bool, device=q.device)
+        c_old = (self.context_cache.get_seqs_block(seq_t) if is_q_pruned
+                 else self.context_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs))
+        c_old = c_old.view(-1, H, D)
+        rows_k32 = rows_k.to(torch.int32) if is_q_pruned else None
+        new_c = attention_sparse_varlen(q, k, dv, c_old, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
+                                        ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens, idx_q32, stats, mask,
+                                        self.threshold, is_q_pruned, rows_k32, v_layout=3)
+
+        # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch
+        if _world_size() > 1:
+            dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+        sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q, ctx.cu_promptlens if is_q_pruned else None)
+        num_valid = int(sel.count.item())
+
+        if is_q_pruned:
+            self.context_cache.reset_block(new_c.flatten(-2, -1), seq_t)
+            ctx.idx_salient_row_k = sel.idx_k[:num_valid]
+        else:
+            self.context_cache.reset_full(new_c.flatten(-2, -1), seq_t, seq_ids_list=md.running_seqs)
+        ctx.idx_salient_row = sel.idx[:num_valid]
+        ctx.idx_salient_row32 = sel.idx32[:num_valid]
+        ctx.cu_salientlens = sel.cu_salientlens
+        ctx.max_salient_per_seq = min(num_valid, ctx.max_seqlen_q)
+
+        self.v_cache.finish(md.finished_seqs)
+        self.context_cache.finish(md.finished_seqs)
+        return new_c.view(-1, H, D)

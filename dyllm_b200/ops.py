@@ -170,3 +170,19 @@ def swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, i
          ptr(w_gate_up), ptr(w_down), inter, ptr(out), out.stride(0), ptr(out_row_map), ptr(ws), ws.numel(), a_mode,
          tile_n, stream_ptr(x.device))
     return out
+
+
+def delta_v_update(v_new: torch.Tensor, cache: torch.Tensor, rows: torch.Tensor, dv: torch.Tensor | None = None,
+                   num_rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """``dv[i] = v_new[i] - cache[rows[i]]; cache[rows[i]] = v_new[i]`` in one pass (bf16).
+
+    ref: dyllm/model_executor/layers/attention.py:67-74,89-96.
+    """
+    require_cuda(v_new, "v_new", torch.bfloat16, 2)
+    require_cuda(cache, "cache", torch.bfloat16, 2)
+    require_cuda(rows, "rows", torch.int32, 1)
+    if dv is None:
+        dv = torch.empty_like(v_new)
+    call("dyllm_delta_v_update", ptr(v_new), ptr(cache), ptr(rows), v_new.size(0), ptr(num_rows_dev), v_new.size(1),
+         ptr(dv), stream_ptr(v_new.device))
+    return dv

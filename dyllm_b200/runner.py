@@ -1,0 +1,187 @@
+"""Minimal step driver for the saliency path: builds the per-step ``Context`` exactly as the reference's
+``ModelRunner.prepare_full`` / ``prepare_sparse`` do (ref: dyllm/engine/model_runner.py:140-298), runs the
+model, and unmasks tokens with the confidence rule of the reference's sampler
+(ref: dyllm/model_executor/layers/sampler.py:244-315) for batches of equal-length sequences.
+
+It exists so that the path can be measured and tested end to end; request scheduling, tokenisation
+and multi-process control of the reference engine are outside this package.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List
+
+import torch
+
+from .context import get_context, get_metadata, set_context, set_metadata
+
+
+@dataclass
+class Sequence:
+    """The per-request state the step preparation reads (ref: dyllm/engine/sequence.py:15-82)."""
+
+    seq_id: int
+    token_ids: List[int]
+    num_prompt_tokens: int
+    max_new_tokens: int
+    processed_steps: int = 0
+    last_token_pos: List[int] = field(default_factory=list)
+    last_tokens: List[int] = field(default_factory=list)
+
+    def __len__(self) -> int:
+        return len(self.token_ids)
+
+
+def _dev(values, dtype, device):
+    return torch.tensor(values, dtype=dtype).pin_memory().to(device, non_blocking=True) if device.type == "cuda" \
+        else torch.tensor(values, dtype=dtype, device=device)
+
+
+def prepare_full(seqs: List[Sequence], device: torch.device):
+    """ref: dyllm/engine/model_runner.py:140-184."""
+    input_ids, positions, cu = [], [], [0]
+    lens, seq_ids = [], []
+    for seq in seqs:
+        n = len(seq)
+        input_ids.extend(seq.token_ids)
+        positions.extend(range(n))
+        cu.append(cu[-1] + n)
+        lens.append(n)
+        seq_ids.append(seq.seq_id)
+    md = get_metadata()
+    md.running_seqs = seq_ids
+    md.running_seqs_tensor = _dev(seq_ids, torch.long, device)
+    cu_t = _dev(cu, torch.int32, device)
+    set_context(True, cu_seqlens_q=cu_t, cu_seqlens_q_cpu=cu, cu_seqlens_k=cu_t, max_seqlen_q=max(lens),
+                max_seqlen_k=max(lens), context_lens=_dev(lens, torch.int32, device), context_lens_cpu=lens,
+                total_seqlen=cu[-1], total_seqlen_k=cu[-1])
+    return _dev(input_ids, torch.int64, device), _dev(positions, torch.int64, device)
+
+
+def prepare_sparse(seqs: List[Sequence], device: torch.device, refresh_period: int = 4):
+    """ref: dyllm/engine/model_runner.py:186-298.  ``refresh_period`` is the reference's hard-coded 4:
+    a step with ``processed_steps > period and processed_steps % period != 0`` uses response-only
+    queries, every other sparse step the full sequence."""
+    input_ids, positions, positions_k = [], [], []
+    idx_q, idx_k, idx_upd = [], [], []
+    cu_q, cu_k, cu_p, cu_sal = [0], [0], [0], [0]
+    lens, seq_ids = [], []
+    pruned_flags = []
+    for seq in seqs:
+        n = len(seq)
+        cu_p.append(seq.num_prompt_tokens + cu_p[-1])
+        answer_start = n - seq.max_new_tokens
+        kept = [p for p in seq.last_token_pos if p >= answer_start]
+        pruned = seq.processed_steps > refresh_period and seq.processed_steps % refresh_period != 0
+        pruned_flags.append(pruned)
+        if pruned:
+            input_ids.extend(seq.token_ids[-seq.max_new_tokens:])
+            positions.extend(range(answer_start, n))
+            idx_q.extend(p - seq.num_prompt_tokens + cu_q[-1] for p in kept)
+            idx_k.extend(p + cu_k[-1] for p in kept)
+            lq = seq.max_new_tokens
+        else:
+            input_ids.extend(seq.token_ids)
+            positions.extend(range(n))
+            idx_q.extend(p + cu_q[-1] for p in kept)
+            lq = n
+        positions_k.extend(kept)
+        idx_upd.extend(p + cu_k[-1] for p in kept)
+        cu_sal.append(len(kept) + cu_sal[-1])
+        seq_ids.append(seq.seq_id)
+        cu_q.append(cu_q[-1] + lq)
+        cu_k.append(cu_k[-1] + n)
+        lens.append(n)
+    any_pruned = any(pruned_flags)
+    if any_pruned and not all(pruned_flags):
+        raise RuntimeError("sequences of one batch must be at the same refresh phase")
+    md = get_metadata()
+    md.running_seqs = seq_ids
+    md.running_seqs_tensor = _dev(seq_ids, torch.long, device)
+    max_sal = max((cu_sal[i + 1] - cu_sal[i] for i in range(len(seqs))), default=0)
+    set_context(
+        False, cu_seqlens_q=_dev(cu_q, torch.int32, device), cu_seqlens_q_cpu=cu_q,
+        cu_seqlens_k=_dev(cu_k, torch.int32, device), cu_promptlens=_dev(cu_p, torch.int32, device),
+        cu_updatedlens=_dev(cu_sal, torch.int32, device), cu_salientlens=_dev(cu_sal, torch.int32, device),
+        max_seqlen_q=max(cu_q[i + 1] - cu_q[i] for i in range(len(seqs))), max_seqlen_k=max(lens),
+        idx_updated_row=_dev(idx_upd, torch.int32, device), idx_salient_row=_dev(idx_q, torch.int64, device),
+        idx_salient_row_k=_dev(idx_k, torch.int64, device) if any_pruned else None,
+        idx_salient_row32=_dev(idx_q, torch.int32, device), max_salient_per_seq=max_sal,
+        context_lens=_dev(lens, torch.int32, device), context_lens_cpu=lens, total_seqlen_k=cu_k[-1],
+        total_seqlen=cu_q[-1], positions_k=_dev(positions_k, torch.int64, device))
+    return _dev(input_ids, torch.int64, device), _dev(positions, torch.int64, device)
+
+
+class StepRunner:
+    """Runs denoising steps of a fixed batch: ``num_full_steps`` dense steps, then sparse steps."""
+
+    def __init__(self, model, mask_id: int, block_length: int = 32, steps: int = 256, num_full_steps: int = 8,
+                 refresh_period: int = 4):
+        self.model = model
+        self.mask_id = mask_id
+        self.block_length = block_length
+        self.steps = steps
+        self.num_full_steps = num_full_steps
+        self.refresh_period = refresh_period
+        self.device = next(model.parameters()).device
+        self.salient_counts: list[int] = []
+
+    def new_batch(self, prompts: List[List[int]], max_new_tokens: int, first_seq_id: int = 0) -> List[Sequence]:
+        seqs = []
+        for i, p in enumerate(prompts):
+            seqs.append(Sequence(first_seq_id + i, list(p) + [self.mask_id] * max_new_tokens, len(p), max_new_tokens))
+        set_metadata([s.seq_id for s in seqs], [s.seq_id for s in seqs], [])
+        return seqs
+
+    @torch.inference_mode()
+    def step(self, seqs: List[Sequence]) -> int:
+        """One denoising step of every sequence; returns the number of tokens unmasked."""
+        is_full = seqs[0].processed_steps < self.num_full_steps
+        if is_full:
+            input_ids, positions = prepare_full(seqs, self.device)
+        else:
+            input_ids, positions = prepare_sparse(seqs, self.device, self.refresh_period)
+        ctx = get_context()
+        hidden = self.model(input_ids, positions)
+        logits = self.model.compute_logits(hidden)
+        return self._unmask(seqs, logits, ctx)
+
+    def _unmask(self, seqs: List[Sequence], logits: torch.Tensor, ctx) -> int:
+        B = len(seqs)
+        gen = seqs[0].max_new_tokens
+        steps_per_block = max(1, self.steps * self.block_length // gen)
+        num_transfer = max(1, self.block_length // steps_per_block)
+        cu_q = ctx.cu_seqlens_q_cpu
+        rows, cand_pos = [], []
+        for b, seq in enumerate(seqs):
+            blk = min(seq.processed_steps // steps_per_block, gen // self.block_length - 1)
+            start = seq.num_prompt_tokens + blk * self.block_length
+            lq = cu_q[b + 1] - cu_q[b]
+            off = start - (len(seq) - lq)  # position -> row inside this sequence's query rows
+            rows.append(torch.arange(off, off + self.block_length) + cu_q[b])
+            cand_pos.append(list(range(start, start + self.block_length)))
+        rows_t = torch.stack(rows).to(self.device)
+        cand = logits.index_select(0, rows_t.flatten()).float().view(B, self.block_length, -1)
+        probs = torch.softmax(cand, dim=-1)
+        conf, tok = probs.max(dim=-1)
+        still_masked = torch.tensor(
+            [[seq.token_ids[p] == self.mask_id for p in cand_pos[b]] for b, seq in enumerate(seqs)], device=self.device)
+        conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
+        top_conf, top_i = conf.topk(num_transfer, dim=-1)
+        picked = torch.stack([top_i, tok.gather(1, top_i), (top_conf >= 0).long()], dim=-1).cpu()  # one D2H per step
+        n_unmasked = 0
+        for b, seq in enumerate(seqs):
+            chosen = []
+            for j in range(num_transfer):
+                i, t, ok = picked[b, j].tolist()
+                if ok:
+                    chosen.append((cand_pos[b][i], int(t)))
+            chosen.sort()  # the kernels expect ascending row lists
+            for p, t in chosen:
+                seq.token_ids[p] = t
+            seq.last_token_pos = [p for p, _ in chosen]
+            seq.last_tokens = [t for _, t in chosen]
+            n_unmasked += len(chosen)
+            seq.processed_steps += 1
+        return n_unmasked

@@ -174,8 +174,10 @@ size_t dyllm_attention_sparse_workspace_bytes(int total_q, int num_heads);
  * num_heads, 128]; all bf16.  idx_salient_row_q (query space) and idx_salient_row_k (key space) hold
  * num_salient ascending rows each, grouped by sequence through cu_salientlens; pass the same list
  * twice when queries are not pruned.  The softmax scale is 1/sqrt(128).  Statistics are reduced over
- * heads in a fixed order.  v_mn_major selects how the delta-V tile is fed to the tensor cores
- * (1 = as gathered, MN-major descriptor; 0 = transposed while gathering); results are identical.
+ * heads in a fixed order.  v_layout is a bit set: bit 0 selects how the delta-V tile is fed to the
+ * tensor cores (1 = as gathered, MN-major descriptor; 0 = transposed while gathering; results are
+ * identical); bit 1 set means v is compact, [num_salient, num_kv_heads, 128] with row i belonging to
+ * key idx_salient_row_k[i], instead of the zero-padded [total_k, ...] tensor (no memset, no scatter).
  * ref: dyllm/csrc/attention/attention.cpp:64-179 (attention_sparse_varlen),
  *      dyllm/csrc/attention/attention_ops_kernels_sm80.cu:44-590,
  *      dyllm/csrc/attention/attention_aux_kernels.cu:10-110. */
@@ -185,7 +187,15 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   int num_kv_heads, int head_dim, const int32_t* cu_salientlens,
                                   const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
                                   int num_salient, float* cosine_stats, uint8_t* cosine_out, float threshold,
-                                  void* workspace, size_t workspace_bytes, int v_mn_major, void* stream);
+                                  void* workspace, size_t workspace_bytes, int v_layout, void* stream);
+
+
+/* Delta-V of the step and value-cache update in one pass over the salient rows:
+ *   dv[i] = v_new[i] - cache[rows[i]];  cache[rows[i]] = v_new[i]       i < min(num_rows, *num_rows_dev)
+ * (bf16, the difference rounded once).  rows are int32 row numbers of `cache`; width % 8 == 0.
+ * ref: dyllm/model_executor/layers/attention.py:67-74,89-96 (v_delta, cache update, v_delta_sparse). */
+int dyllm_delta_v_update(const void* v_new, void* cache, const int32_t* rows, int num_rows,
+                         const int32_t* num_rows_dev, int width, void* dv, void* stream);
 
 /* Exact attention of the salient query rows against the whole K / V of their sequence (non-causal):
  * o_sal[i] = softmax(q[idx_salient_row_q[i]] K^T / sqrt(128)) V, i grouped by sequence through

@@ -1,0 +1,186 @@
+"""Generates tests/golden/llada_layer_small.pt by running the REFERENCE's own Python
+(`LLaDADecoderLayer`, `Attention`, `CacheManager`, `MLPcache`, `tensor_parallel_cosine_mask`, ...) on the CPU with
+bf16 modules and caches (as the reference runs them on a GPU; in fp32 its in-place RMSNorm would alias
+the residual), with the three native modules it imports replaced by the oracle's fp32 restatements.
+
+Run in the development container only (it needs the reference checkout):
+
+    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py /path/to/reference
+
+The fixture holds seeds, shapes and outputs; weights and inputs are regenerated from the seeds by
+`golden_inputs()` below, which the tests import.
+"""
+import os
+import sys
+import types
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+SHAPE = dict(hidden=256, heads=2, kv_heads=2, head_dim=128, inter=512, eps=1e-5, theta=500000.0, max_pos=512)
+BATCH, PROMPT, RESP = 2, 24, 40
+TAU = 0.99
+
+
+def golden_inputs(seed=1234):
+    """Weights N(0, 0.02) (a larger scale for the value/FFN paths keeps cosines spread around the
+    threshold) and three hidden-state inputs, all from one CPU generator."""
+    g = torch.Generator().manual_seed(seed)
+    h, H, Hkv, D, I = SHAPE["hidden"], SHAPE["heads"], SHAPE["kv_heads"], SHAPE["head_dim"], SHAPE["inter"]
+    w = {
+        "q_proj": torch.randn(H * D, h, generator=g) * 0.05,
+        "kv_proj": torch.randn(2 * Hkv * D, h, generator=g) * 0.05,
+        "o_proj": torch.randn(h, H * D, generator=g) * 0.05,
+        "gate_up_proj": torch.randn(2 * I, h, generator=g) * 0.05,
+        "down_proj": torch.randn(h, I, generator=g) * 0.05,
+    }
+    w = {k: v.bfloat16().float() for k, v in w.items()}
+    L = PROMPT + RESP
+    x0 = torch.randn(BATCH * L, h, generator=g).bfloat16().float()
+    # later steps: small perturbations of the same hidden states, large ones on the rows the step lists
+    # as salient (their tokens changed) and medium ones on a few more response rows
+    xs = [x0]
+    for step in (1, 2):
+        bump = torch.zeros(BATCH * L, 1)
+        for b in range(BATCH):
+            bump[b * L + PROMPT + torch.randperm(RESP, generator=g)[:5]] = 0.05
+            for p in step_layout(step)[2][b]:
+                bump[b * L + p] = 0.6
+        xs.append((xs[-1] + (0.003 + bump) * torch.randn(BATCH * L, h, generator=g)).bfloat16().float())
+    return w, xs
+
+
+def step_layout(step):
+    """(is_full, response_only, initial salient positions per sequence) of the three recorded steps."""
+    if step == 0:
+        return True, False, None
+    if step == 1:
+        return False, False, [[PROMPT + 1, PROMPT + 7, PROMPT + 20], [PROMPT + 3, PROMPT + 33]]
+    return False, True, [[PROMPT + 2, PROMPT + 9], [PROMPT + 5, PROMPT + 30, PROMPT + 31]]
+
+
+def main(ref_root):
+    os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+    import torch.distributed as dist
+    from oracle import dyllm_oracle as orc
+
+    # --- stand-ins for the reference's three native modules ------------------------------------
+    pkg = types.ModuleType("dyllm")
+    pkg.__path__ = [os.path.join(ref_root, "dyllm")]
+    sys.modules["dyllm"] = pkg
+    cache_mod = types.ModuleType("dyllm.cache")
+    cache_mod.get_seqs_cuda = lambda cache, ss, cu, ids, total: orc.cache_get_seqs(cache, ss, cu, ids, total)
+    cache_mod.get_block_cuda = lambda cache, ss, cu, cuq, ids, total: orc.cache_get_block(cache, ss, cu, cuq, ids, total)
+    cache_mod.reset_full_cuda = lambda cache, inp, ss, cu, ids, total: orc.cache_reset_full(cache, inp, ss, cu, ids)
+    cache_mod.reset_block_cuda = lambda cache, inp, ss, cu, cuq, ids, total: orc.cache_reset_block(cache, inp, ss, cu, cuq, ids)
+    cache_mod.scatter_update_cuda = lambda cache, new, rows, cu, ss, ids: orc.cache_scatter_update(cache, new, rows, cu, ss, ids)
+    sys.modules["dyllm.cache"] = cache_mod
+
+    def attention_sparse_varlen(Q, K, V, C, o_sal, cu_q, cu_k, max_q, max_k, total, cu_sal, idx, stats, mask_out,
+                                threshold=0.0, is_q_pruned=False, idx_k=None, force=-1):
+        O, st, mask = orc.attention_sparse_varlen(Q, K, V, C, o_sal, cu_q, cu_k, cu_sal, idx, threshold,
+                                                  round_p_bf16=False, stats_in=stats)
+        stats.copy_(st)
+        mask_out.copy_(mask)
+        return O.to(Q.dtype)
+
+    def fused_offset_launch(idxs, num_idxs, cu_p, cu_sal, out, max_threads):
+        n = int(num_idxs.item())
+        out[:n] = orc.fused_offset(idxs[:n], cu_p, cu_sal)
+
+    ops_mod = types.ModuleType("dyllm.attention_ops")
+    ops_mod.attention_sparse_varlen = attention_sparse_varlen
+    ops_mod.fused_offset_launch = fused_offset_launch
+    sys.modules["dyllm.attention_ops"] = ops_mod
+    fa = types.ModuleType("flash_attn")
+    fa.flash_attn_varlen_func = lambda q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, dropout_p, softmax_scale, causal: \
+        orc.exact_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, softmax_scale).to(q.dtype)
+    sys.modules["flash_attn"] = fa
+    torch.cuda.nvtx.range_pop = lambda: None
+
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1)
+    import dyllm.engine.cache_manager as cm
+
+    cm.CacheManager.__init__.__defaults__ = (16384, torch.bfloat16, torch.device("cpu"))
+    import dyllm.distributed as ddist
+    import dyllm.model_executor.layers.attention as ref_attn
+
+    seen_stats = []
+    real_mask = ddist.tensor_parallel_cosine_mask
+
+    def recording_mask(stats, threshold):
+        seen_stats.append(stats.clone())
+        return real_mask(stats, threshold)
+
+    ref_attn.tensor_parallel_cosine_mask = recording_mask
+    from dyllm.model_executor.models.llada import LLaDADecoderLayer
+    from dyllm.utils.context import get_context, set_context
+    from dyllm.utils.metadata import get_metadata, set_metadata
+
+    cfg = types.SimpleNamespace(hidden_size=SHAPE["hidden"], num_attention_heads=SHAPE["heads"], n_kv_heads=SHAPE["kv_heads"],
+                                max_sequence_length=SHAPE["max_pos"], rms_norm_eps=SHAPE["eps"], head_dim=SHAPE["head_dim"],
+                                rope_theta=SHAPE["theta"], mlp_hidden_size=SHAPE["inter"])
+    layer = LLaDADecoderLayer(cfg, TAU).bfloat16()
+    w, xs = golden_inputs()
+    with torch.no_grad():
+        layer.self_attn.q_proj.weight.copy_(w["q_proj"])
+        layer.self_attn.kv_proj.weight.copy_(w["kv_proj"])
+        layer.self_attn.o_proj.weight.copy_(w["o_proj"])
+        layer.mlp.gate_up_proj.weight.copy_(w["gate_up_proj"])
+        layer.mlp.down_proj.weight.copy_(w["down_proj"])
+        layer.input_layernorm.weight.fill_(1.0)
+        layer.post_attention_layernorm.weight.fill_(1.0)
+
+    L = PROMPT + RESP
+    seq_ids = [5, 3]
+    record = {"shape": SHAPE, "batch": BATCH, "prompt": PROMPT, "resp": RESP, "tau": TAU, "seq_ids": seq_ids, "steps": []}
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    for step in range(3):
+        is_full, ro, sal = step_layout(step)
+        set_metadata(seq_ids, seq_ids, [])
+        get_metadata().running_seqs_tensor = torch.tensor(seq_ids, dtype=torch.long)
+        cu_k = [b * L for b in range(BATCH + 1)]
+        if is_full:
+            positions = torch.arange(L).repeat(BATCH)
+            set_context(True, cu_seqlens_q=i32(cu_k), cu_seqlens_q_cpu=cu_k, cu_seqlens_k=i32(cu_k), max_seqlen_q=L,
+                        max_seqlen_k=L, context_lens=i32([L] * BATCH), context_lens_cpu=[L] * BATCH, total_seqlen=BATCH * L)
+            x = xs[step]
+        else:
+            lq = RESP if ro else L
+            cu_q = [b * lq for b in range(BATCH + 1)]
+            idx_q, idx_k, cu_sal = [], [], [0]
+            for b in range(BATCH):
+                for p in sal[b]:
+                    idx_q.append((p - PROMPT if ro else p) + cu_q[b])
+                    idx_k.append(p + cu_k[b])
+                cu_sal.append(len(idx_q))
+            positions = (torch.arange(PROMPT, L) if ro else torch.arange(L)).repeat(BATCH)
+            set_context(False, cu_seqlens_q=i32(cu_q), cu_seqlens_q_cpu=cu_q, cu_seqlens_k=i32(cu_k),
+                        cu_promptlens=i32([b * PROMPT for b in range(BATCH + 1)]), cu_salientlens=i32(cu_sal),
+                        max_seqlen_q=lq, max_seqlen_k=L, idx_salient_row=torch.tensor(idx_q, dtype=torch.long),
+                        idx_salient_row_k=torch.tensor(idx_k, dtype=torch.long) if ro else None,
+                        context_lens=i32([L] * BATCH), context_lens_cpu=[L] * BATCH, total_seqlen_k=BATCH * L,
+                        total_seqlen=BATCH * lq)
+            x = xs[step].view(BATCH, L, -1)[:, PROMPT:].reshape(BATCH * RESP, -1) if ro else xs[step]
+        with torch.no_grad():
+            out, residual = layer(positions, x.clone().bfloat16(), None)
+        ctx = get_context()
+        rec = {"out": out.float().clone(), "residual": residual.float().clone()}
+        if not is_full:
+            rec["cosine"] = orc.cosine_values(seen_stats[-1]).float()
+            print("   min |cos - tau| =", float((rec["cosine"] - TAU).abs().min()))
+            rec["idx_salient_row"] = ctx.idx_salient_row.clone()
+            rec["cu_salientlens"] = ctx.cu_salientlens.clone()
+            if ro:
+                rec["idx_salient_row_k"] = ctx.idx_salient_row_k.clone()
+        record["steps"].append(rec)
+        print("step", step, "out", tuple(out.shape), "salient", None if is_full else ctx.idx_salient_row.tolist())
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "llada_layer_small.pt")
+    torch.save(record, path)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -58,7 +58,7 @@ def run_gpu(case, dev, v_mn_major):
     out = attention_sparse_varlen(d(case["q"]), d(case["k"]), d(case["dv"]), d(case["c_old"]), d(case["o_sal"]),
                                   d(case["cu_q"]), d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]),
                                   d(case["idx_q"]), stats, mask, TAU, case["response_only"],
-                                  d(case["idx_k"]) if case["response_only"] else None, v_mn_major=v_mn_major)
+                                  d(case["idx_k"]) if case["response_only"] else None, v_layout=v_mn_major)
     from dyllm_b200 import _lib
     assert _lib.load().dyllm_device_status() == 0
     return out.cpu(), stats.cpu(), mask.cpu()
@@ -173,3 +173,22 @@ def test_attention_salient_rows_matches_exact_attention(cuda_device, case_id):
         assert diff.abs().max().item() <= 2e-2
         assert (diff.norm() / want.norm()).item() <= 1e-2
     assert bool((out[n:] == 7.0).all())
+
+
+@pytest.mark.parametrize("case_id", [0, 1, 3, 5])
+def test_attention_compact_delta_v_equals_padded(cuda_device, case_id):
+    """The compact delta-V layout (no zero-padded tensor) gives bit-identical results."""
+    from dyllm_b200.attention_ops import attention_sparse_varlen
+
+    batch, prompt, response, H, Hkv, ro, sal = CASES[case_id]
+    case = make_case(batch, prompt, response, H, Hkv, ro, sal, seed=50 + case_id)
+    ref = run_gpu(case, cuda_device, 1)
+    d = lambda t: t.to(cuda_device)
+    Tq = case["q"].size(0)
+    stats = torch.zeros(Tq, 3, device=cuda_device)
+    mask = torch.empty(Tq, dtype=torch.bool, device=cuda_device)
+    dv_compact = case["dv"][case["idx_k"].long()].contiguous()
+    out = attention_sparse_varlen(d(case["q"]), d(case["k"]), d(dv_compact), d(case["c_old"]), d(case["o_sal"]),
+                                  d(case["cu_q"]), d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]),
+                                  d(case["idx_q"]), stats, mask, TAU, ro, d(case["idx_k"]) if ro else None, v_layout=3)
+    assert torch.equal(out.cpu(), ref[0]) and torch.equal(stats.cpu(), ref[1]) and torch.equal(mask.cpu(), ref[2])

@@ -107,3 +107,21 @@ def test_swiglu_and_moe_consistency():
     assert torch.allclose(out, orc.swiglu_ffn(x, w1[0], w2[0], round_bf16=False), atol=1e-5)
     w, i = orc.moe_gate(x, torch.randn(4, 32, generator=g), 2)
     assert w.shape == (5, 2) and i.dtype == torch.int32 and bool((w[:, 0] >= w[:, 1]).all())
+
+
+def test_oracle_selection_reproduces_reference_layer_outputs():
+    """Golden fixture (reference Python run on CPU, tests/golden/make_golden.py): the oracle's mask ->
+    compaction -> K-space offsets reproduce the index lists the reference layer published."""
+    import os
+
+    fx = torch.load(os.path.join(os.path.dirname(__file__), "golden", "llada_layer_small.pt"))
+    B, P, R = fx["batch"], fx["prompt"], fx["resp"]
+    for step, response_only in ((1, False), (2, True)):
+        rec = fx["steps"][step]
+        cu_q, cu_k, cu_p = orc.make_batch_layout(B, P, R, response_only)
+        mask = rec["cosine"] < fx["tau"]
+        idx, cu_sal = orc.compact(mask, cu_q)
+        assert torch.equal(idx, rec["idx_salient_row"])
+        assert torch.equal(cu_sal, rec["cu_salientlens"])
+        if response_only:
+            assert torch.equal(orc.fused_offset(idx, cu_p, cu_sal), rec["idx_salient_row_k"])
