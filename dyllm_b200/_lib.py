@@ -43,6 +43,15 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_delta_v_update": (I, [P, P, P, I, P, I, P, P]),
 }
 
+# kernels of this library launched by one call of each entry point (for launch accounting)
+KERNELS_PER_CALL = {
+    "dyllm_context_stats": 1, "dyllm_cosine_mask": 1, "dyllm_salient_select": 1, "dyllm_fused_offset": 1,
+    "dyllm_cache_get_seqs": 1, "dyllm_cache_get_block": 1, "dyllm_cache_reset_full": 1, "dyllm_cache_reset_block": 1,
+    "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 1, "dyllm_swiglu_ffn": 2, "dyllm_cache_dest_rows": 1,
+    "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 1, "dyllm_delta_v_update": 1,
+}
+launch_count = 0
+
 _lib = None
 
 
@@ -77,8 +86,10 @@ def stream_ptr(device: torch.device | None = None) -> int:
 
 def call(name: str, *args) -> None:
     """Calls a status-returning entry point and raises RuntimeError on failure."""
+    global launch_count
     lib = load()
     rc = getattr(lib, name)(*args)
+    launch_count += KERNELS_PER_CALL.get(name, 0)
     if rc != 0:
         msg = lib.dyllm_last_error().decode(errors="replace")
         raise RuntimeError(f"{name} failed with status {rc}: {msg}")

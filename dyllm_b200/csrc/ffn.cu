@@ -183,8 +183,8 @@ int dyllm_swiglu_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const i
   DYLLM_REQUIRE(workspace_bytes >= dyllm_swiglu_ffn_workspace_bytes(num_rows, inter), DYLLM_ERR_WORKSPACE,
                 "swiglu_ffn: workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
                 dyllm_swiglu_ffn_workspace_bytes(num_rows, inter));
-  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023) == 0, DYLLM_ERR_INVALID_ARGUMENT,
-                "swiglu_ffn: workspace must be 1024-byte aligned");
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "swiglu_ffn: workspace must be 16-byte aligned");
   if (a_mode < 0)
     a_mode = 1;
   DYLLM_REQUIRE(a_mode == 1 || a_mode == 2, DYLLM_ERR_INVALID_ARGUMENT, "swiglu_ffn: a_mode %d (1 = TMA gather4, "

@@ -14,7 +14,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 from torch import nn
 
-from . import ops
+from . import ops, profiling
 from .attention_ops import attention_salient_rows, attention_sparse_varlen
 from .cache_manager import CacheManager
 from .context import get_context, get_metadata
@@ -257,8 +257,10 @@ class LLaDAMLP(nn.Module):
                 cm.scatter_update(md.running_seqs_tensor, rows_k, y)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor)
-                ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
-                               num_rows=n, out=cm.cache, out_row_map=dest)
+                flops = 6.0 * n * hidden.size(1) * self.down_proj.weight.size(1)
+                with profiling.region("swiglu_ffn", flops):
+                    ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
+                                   num_rows=n, out=cm.cache, out_row_map=dest)
         cm.finish(md.finished_seqs)
         return self.cache_update.result()
 
@@ -326,8 +328,9 @@ class Attention(nn.Module):
         v_full = self.v_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs).view(-1, Hkv, D)
 
         # exact attention of the salient query rows (attention.py:76-87)
-        o_sal = attention_salient_rows(q, k, v_full, ctx.cu_seqlens_k, ctx.cu_salientlens, idx_q32,
-                                       max_rows_per_seq=max(ctx.max_salient_per_seq, 1), num_salient=n_sal)
+        with profiling.region("salient_attention", 4.0 * n_sal * ctx.max_seqlen_k * H * D):
+            o_sal = attention_salient_rows(q, k, v_full, ctx.cu_seqlens_k, ctx.cu_salientlens, idx_q32,
+                                           max_rows_per_seq=max(ctx.max_salient_per_seq, 1), num_salient=n_sal)
 
         stats = torch.zeros((ctx.total_seqlen, 3), dtype=torch.float32, device=q.device)
         mask = torch.empty((ctx.total_seqlen,), dtype=torch.bool, device=q.device)
@@ -335,15 +338,21 @@ class Attention(nn.Module):
                  else self.context_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs))
         c_old = c_old.view(-1, H, D)
         rows_k32 = rows_k.to(torch.int32) if is_q_pruned else None
-        new_c = attention_sparse_varlen(q, k, dv, c_old, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q,
-                                        ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens, idx_q32, stats, mask,
-                                        self.threshold, is_q_pruned, rows_k32, v_layout=3)
+        # algorithmic flops: Q K^T over all keys (sum over sequences of len_q * len_k, equal lengths here)
+        flops = 2.0 * ctx.total_seqlen * ctx.max_seqlen_k * H * D
+        with profiling.region("delta_attention", flops):
+            new_c = attention_sparse_varlen(q, k, dv, c_old, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
+                                            ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens,
+                                            idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=3)
 
         # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch
         if _world_size() > 1:
             dist.all_reduce(stats, op=dist.ReduceOp.SUM)
-        sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q, ctx.cu_promptlens if is_q_pruned else None)
+        with profiling.region("salient_select", 12.0 * ctx.total_seqlen):
+            sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,
+                                     ctx.cu_promptlens if is_q_pruned else None)
         num_valid = int(sel.count.item())
+        profiling.count("salient_rows", num_valid)
 
         if is_q_pruned:
             self.context_cache.reset_block(new_c.flatten(-2, -1), seq_t)

@@ -1,0 +1,213 @@
+"""Per-kernel timing of the saliency path at the LLaDA-8B layer shape (batch 16, 512 tokens per sequence).
+
+    python -m dyllm_b200.microbench [--kernel NAME ...] [--rows S] [--iters N] [--no-flush]
+
+Each kernel is warmed up, then timed launch by launch with CUDA events on the current stream; L2 is
+flushed between launches by writing a 256 MiB buffer.  The report gives the median launch time and the
+achieved fraction of the roofline that bounds the kernel (HBM GB/s from algorithmic bytes, or bf16
+TFLOP/s), against MEASURED_PEAKS.json at the repository root when present.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+from . import ops
+from .attention_ops import attention_salient_rows, attention_sparse_varlen
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+B, P, R, H, D, HID, INTER = 16, 256, 256, 32, 128, 4096, 12288
+L = P + R
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def time_launches(fn, iters, flush):
+    dev = torch.device("cuda")
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(iters):
+        if scratch is not None:
+            scratch.fill_(1)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return statistics.median(times)
+
+
+def salient_lists(rows_total, dev, response_only=False, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    per = max(1, rows_total // B)
+    lq = R if response_only else L
+    idx_q, idx_k = [], []
+    for b in range(B):
+        pos = torch.sort(torch.randperm(R, generator=g)[:per]).values + P
+        idx_k.append(pos + b * L)
+        idx_q.append((pos - P if response_only else pos) + b * lq)
+    cu_sal = (torch.arange(B + 1) * per).to(torch.int32)
+    return torch.cat(idx_q).to(dev), torch.cat(idx_k).to(dev), cu_sal.to(dev), per
+
+
+def bench_stats(args):
+    dev = torch.device("cuda")
+    rows = B * L
+    a = torch.randn(rows, H * D, device=dev).bfloat16()
+    b = torch.randn(rows, H * D, device=dev).bfloat16()
+    out = torch.empty(rows, 3, device=dev)
+    ms = time_launches(lambda: ops.context_stats(a, b, out=out), args.iters, args.flush)
+    return ms, rows * (2 * H * D * 2 + 12), "B"
+
+
+def bench_select(args):
+    dev = torch.device("cuda")
+    rows = args.select_rows
+    stats = torch.ones(rows, 3, device=dev)
+    stats[:, 0] = torch.where(torch.rand(rows, device=dev) < 0.1, 0.5, 0.999)
+    cu = torch.arange(0, rows + 1, L, dtype=torch.int32, device=dev)
+    ms = time_launches(lambda: ops.salient_select(stats, 0.99, cu), args.iters, args.flush)
+    n = int((stats[:, 0] < 0.9).sum())
+    return ms, 12 * rows + 12 * n + 4 * cu.numel(), "B"
+
+
+def bench_scatter(args):
+    from . import cache as C
+
+    dev = torch.device("cuda")
+    rows = B * L
+    cache = torch.randn(rows, HID, device=dev).bfloat16()
+    idx_q, _, _, _ = salient_lists(args.rows, dev)
+    new = torch.randn(idx_q.numel(), HID, device=dev).bfloat16()
+    cu = torch.arange(0, rows + 1, L, dtype=torch.int32, device=dev)
+    ss = torch.arange(B, device=dev) * L
+    ids = torch.arange(B, device=dev)
+    ms = time_launches(lambda: C.scatter_update_cuda(cache, new, idx_q, cu, ss, ids), args.iters, args.flush)
+    return ms, idx_q.numel() * (2 * HID * 2 + 8), "B"
+
+
+def bench_get_seqs(args):
+    from . import cache as C
+
+    dev = torch.device("cuda")
+    rows = B * L
+    cache = torch.randn(rows, HID, device=dev).bfloat16()
+    cu = torch.arange(0, rows + 1, L, dtype=torch.int32, device=dev)
+    ss = torch.arange(B, device=dev) * L
+    ids = torch.arange(B, device=dev)
+    ms = time_launches(lambda: C.get_seqs_cuda(cache, ss, cu, ids, rows), args.iters, args.flush)
+    return ms, rows * 2 * HID * 2, "B"
+
+
+def bench_ffn(args):
+    dev = torch.device("cuda")
+    x = torch.randn(B * L, HID, device=dev).bfloat16()
+    w1 = (torch.randn(2 * INTER, HID, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(HID, INTER, device=dev) * 0.02).bfloat16()
+    idx_q, _, _, _ = salient_lists(args.rows, dev)
+    idx32 = idx_q.to(torch.int32)
+    out = torch.empty(idx32.numel(), HID, device=dev, dtype=torch.bfloat16)
+    ms = time_launches(lambda: ops.swiglu_ffn(x, w1, w2, idx32, out=out, a_mode=args.a_mode, tile_n=args.tile_n),
+                       args.iters, args.flush)
+    s = idx32.numel()
+    flops = 6.0 * s * HID * INTER
+    wbytes = 3.0 * HID * INTER * 2 + s * HID * 2 * 2 + 2.0 * s * INTER * 2
+    # the bound is whichever roofline gives the longer time
+    hbm, tf, _ = peaks()
+    if flops / (tf * 1e12) >= wbytes / (hbm * 1e9):
+        return ms, flops, "F"
+    return ms, wbytes, "B"
+
+
+def bench_kv_proj(args):
+    dev = torch.device("cuda")
+    x = torch.randn(B * L, HID, device=dev).bfloat16()
+    w = (torch.randn(2 * H * D, HID, device=dev) * 0.02).bfloat16()
+    idx_q, _, _, _ = salient_lists(args.rows, dev)
+    idx32 = idx_q.to(torch.int32)
+    ms = time_launches(lambda: ops.gathered_linear(x, w, idx32, a_mode=args.a_mode, tile_n=args.tile_n), args.iters,
+                       args.flush)
+    s = idx32.numel()
+    return ms, 2.0 * HID * 2 * H * D + s * HID * 2 + s * 2 * H * D * 2, "B"
+
+
+def _attention_inputs(args, response_only):
+    dev = torch.device("cuda")
+    lq = R if response_only else L
+    q = torch.randn(B * lq, H, D, device=dev).bfloat16()
+    k = torch.randn(B * L, H, D, device=dev).bfloat16()
+    c = torch.randn(B * lq, H, D, device=dev).bfloat16()
+    idx_q, idx_k, cu_sal, per = salient_lists(args.rows, dev, response_only)
+    dv = torch.randn(idx_q.numel(), H, D, device=dev).bfloat16()
+    o_sal = torch.randn(idx_q.numel(), H, D, device=dev).bfloat16()
+    cu_q = torch.arange(0, B * lq + 1, lq, dtype=torch.int32, device=dev)
+    cu_k = torch.arange(0, B * L + 1, L, dtype=torch.int32, device=dev)
+    return q, k, c, dv, o_sal, cu_q, cu_k, cu_sal, idx_q.to(torch.int32), idx_k.to(torch.int32), per, lq
+
+
+def bench_attention(args):
+    q, k, c, dv, o_sal, cu_q, cu_k, cu_sal, iq, ik, per, lq = _attention_inputs(args, args.response_only)
+    tq = q.size(0)
+    stats = torch.zeros(tq, 3, device=q.device)
+    mask = torch.empty(tq, dtype=torch.bool, device=q.device)
+
+    def fn():
+        stats.zero_()
+        attention_sparse_varlen(q, k, dv, c, o_sal, cu_q, cu_k, lq, L, tq, cu_sal, iq, stats, mask, 0.99,
+                                args.response_only, ik if args.response_only else None, v_layout=3)
+
+    ms = time_launches(fn, args.iters, args.flush)
+    return ms, 2.0 * tq * L * H * D + 4.0 * tq * per * H * D, "F"
+
+
+def bench_salient_attention(args):
+    q, k, c, dv, o_sal, cu_q, cu_k, cu_sal, iq, ik, per, lq = _attention_inputs(args, False)
+    v = torch.randn_like(k)
+    ms = time_launches(lambda: attention_salient_rows(q, k, v, cu_k, cu_sal, iq, max_rows_per_seq=per, out=o_sal),
+                       args.iters, args.flush)
+    return ms, 2.0 * k.numel() * 2 + 2.0 * iq.numel() * H * D * 2, "B"
+
+
+KERNELS = {"stats": bench_stats, "select": bench_select, "scatter": bench_scatter, "get_seqs": bench_get_seqs,
+           "ffn": bench_ffn, "kv_proj": bench_kv_proj, "attention": bench_attention,
+           "salient_attention": bench_salient_attention}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", nargs="*", default=list(KERNELS))
+    ap.add_argument("--rows", type=int, default=416, help="salient rows in the batch (multiple of 16)")
+    ap.add_argument("--select-rows", type=int, default=8 << 20)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", dest="flush", action="store_false")
+    ap.add_argument("--a-mode", type=int, default=-1)
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--response-only", action="store_true")
+    args = ap.parse_args()
+    hbm, tf, src = peaks()
+    for name in args.kernel:
+        ms, work, kind = KERNELS[name](args)
+        if kind == "B":
+            ach, peak, unit = work / ms / 1e6, hbm, "GB/s"
+        else:
+            ach, peak, unit = work / ms / 1e9, tf, "TFLOP/s"
+        print(json.dumps({"kernel": name, "salient_rows": args.rows, "median_ms": round(ms, 4), "achieved": round(ach, 1),
+                          "unit": unit, "peak": peak, "frac": round(ach / peak, 3), "peak_source": src}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,9 +33,13 @@ class Sequence:
         return len(self.token_ids)
 
 
+io_bytes = {"h2d": 0, "d2h": 0}  # host<->device traffic of the step driver, counted from the tensors copied
+
+
 def _dev(values, dtype, device):
-    return torch.tensor(values, dtype=dtype).pin_memory().to(device, non_blocking=True) if device.type == "cuda" \
-        else torch.tensor(values, dtype=dtype, device=device)
+    t = torch.tensor(values, dtype=dtype)
+    io_bytes["h2d"] += t.numel() * t.element_size()
+    return t.pin_memory().to(device, non_blocking=True) if device.type == "cuda" else t.to(device)
 
 
 def prepare_full(seqs: List[Sequence], device: torch.device):
@@ -147,6 +151,13 @@ class StepRunner:
         logits = self.model.compute_logits(hidden)
         return self._unmask(seqs, logits, ctx)
 
+    def generate(self, prompts: List[List[int]], max_new_tokens: int) -> List[List[int]]:
+        """Runs all denoising steps of one batch and returns the generated token ids (host lists)."""
+        seqs = self.new_batch(prompts, max_new_tokens)
+        for _ in range(self.steps):
+            self.step(seqs)
+        return [s.token_ids[s.num_prompt_tokens:] for s in seqs]
+
     def _unmask(self, seqs: List[Sequence], logits: torch.Tensor, ctx) -> int:
         B = len(seqs)
         gen = seqs[0].max_new_tokens
@@ -161,15 +172,20 @@ class StepRunner:
             off = start - (len(seq) - lq)  # position -> row inside this sequence's query rows
             rows.append(torch.arange(off, off + self.block_length) + cu_q[b])
             cand_pos.append(list(range(start, start + self.block_length)))
-        rows_t = torch.stack(rows).to(self.device)
+        rows_t = torch.stack(rows)
+        io_bytes["h2d"] += rows_t.numel() * rows_t.element_size()
+        rows_t = rows_t.to(self.device)
         cand = logits.index_select(0, rows_t.flatten()).float().view(B, self.block_length, -1)
         probs = torch.softmax(cand, dim=-1)
         conf, tok = probs.max(dim=-1)
         still_masked = torch.tensor(
-            [[seq.token_ids[p] == self.mask_id for p in cand_pos[b]] for b, seq in enumerate(seqs)], device=self.device)
+            [[seq.token_ids[p] == self.mask_id for p in cand_pos[b]] for b, seq in enumerate(seqs)])
+        io_bytes["h2d"] += still_masked.numel()
+        still_masked = still_masked.to(self.device)
         conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
         top_conf, top_i = conf.topk(num_transfer, dim=-1)
         picked = torch.stack([top_i, tok.gather(1, top_i), (top_conf >= 0).long()], dim=-1).cpu()  # one D2H per step
+        io_bytes["d2h"] += picked.numel() * picked.element_size()
         n_unmasked = 0
         for b, seq in enumerate(seqs):
             chosen = []

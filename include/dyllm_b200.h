@@ -139,7 +139,7 @@ size_t dyllm_swiglu_ffn_workspace_bytes(int max_rows, int inter);
 
 /* out[map[m]] = down( silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T) ) for the gathered rows: w_gate_up is
  * [2 * inter, hidden] with the gate rows first, w_down is [hidden, inter].  The SiLU product is fused
- * into the first GEMM's epilogue, the row scatter into the second's.  workspace: 1024-byte aligned,
+ * into the first GEMM's epilogue, the row scatter into the second's.  workspace: 16-byte aligned,
  * dyllm_swiglu_ffn_workspace_bytes(num_rows, inter) bytes.
  * ref: dyllm/model_executor/models/llada.py:38-43,184-185 (gather + MLP),
  *      dyllm/model_executor/layers/activations.py:9-14, dyllm/model_executor/layers/linear.py:76-93,195-220,
