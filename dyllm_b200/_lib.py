@@ -26,6 +26,8 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_cosine_mask": (I, [P, P, I, F, P]),
     "dyllm_salient_select_workspace_bytes": (Z, [I]),
     "dyllm_salient_select": (I, [P, I, F, P, I, P, P, P, P, P, P, P, P, Z, P]),
+    "dyllm_salient_select_static": (I, [P, I, F, P, I, P, P, P, P, P, P, P, P]),
+    "dyllm_salient_select_static_max_rows": (I, []),
     "dyllm_fused_offset": (I, [P, P, P, P, I, P, I, P]),
     "dyllm_cache_get_seqs": (I, [P, P, P, P, P, I, I, I, I, P]),
     "dyllm_cache_get_block": (I, [P, P, P, P, P, P, I, I, I, I, P]),
@@ -45,7 +47,8 @@ SIGNATURES: dict[str, tuple] = {
 
 # kernels of this library launched by one call of each entry point (for launch accounting)
 KERNELS_PER_CALL = {
-    "dyllm_context_stats": 1, "dyllm_cosine_mask": 1, "dyllm_salient_select": 1, "dyllm_fused_offset": 1,
+    "dyllm_context_stats": 1, "dyllm_cosine_mask": 1, "dyllm_salient_select": 1, "dyllm_salient_select_static": 1,
+    "dyllm_fused_offset": 1,
     "dyllm_cache_get_seqs": 1, "dyllm_cache_get_block": 1, "dyllm_cache_reset_full": 1, "dyllm_cache_reset_block": 1,
     "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 1, "dyllm_swiglu_ffn": 2, "dyllm_cache_dest_rows": 1,
     "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 1, "dyllm_delta_v_update": 1,

@@ -311,6 +311,41 @@ int launch_salient_select(const float* stats, int rows, float threshold, const i
   return check_launch("salient_select");
 }
 
+// ----------------------------------------------------------------------------------------------
+// Selection without any caller- or library-allocated scratch memory.
+//
+// The look-back descriptors of salient_select live in this fixed array, which every device that loads
+// the library holds until the process exits (kStaticSelectMaxRows / 2048 descriptors of 8 bytes plus
+// the ticket: about 16 KB).  In host code the array's name is only a handle for the runtime, not a
+// device address; its address on the current device is looked up once per device with
+// cudaGetSymbolAddress and that pointer is what the kernel receives.
+// ----------------------------------------------------------------------------------------------
+constexpr int kStaticSelectMaxRows = 4 * 1024 * 1024;
+constexpr size_t kStaticSelectBytes =
+    sizeof(unsigned int) * 2 + sizeof(unsigned long long) * (kStaticSelectMaxRows / kSelTileRows);
+static __device__ __align__(256) unsigned char g_static_select_scratch[kStaticSelectBytes];
+
+namespace {
+void* g_static_select_ptr[64] = {nullptr};
+}
+
+// Returns the device address of the static scratch array on the current device (set up on first use).
+int static_select_scratch(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return set_error(DYLLM_ERR_CUDA, "salient_select_static: no usable current device");
+  if (!g_static_select_ptr[dev]) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_select_scratch);
+    if (err != cudaSuccess || !ptr)
+      return set_error(DYLLM_ERR_CUDA, "salient_select_static: cudaGetSymbolAddress failed: %s",
+                       cudaGetErrorString(err));
+    g_static_select_ptr[dev] = ptr;
+  }
+  *out = g_static_select_ptr[dev];
+  return DYLLM_OK;
+}
+
 }  // namespace dyllm
 
 using namespace dyllm;
@@ -361,6 +396,34 @@ int dyllm_salient_select(const float* stats, int rows, float threshold, const in
                 "salient_select: workspace must be 8-byte aligned");
   return launch_salient_select(stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out,
                                idx_k_out, cu_salientlens_out, count_out, mask_out, workspace,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int dyllm_salient_select_static_max_rows(void) { return kStaticSelectMaxRows; }
+
+int dyllm_salient_select_static(const float* stats, int rows, float threshold, const int32_t* cu_seqlens_q, int batch,
+                                const int32_t* cu_promptlens, int64_t* idx_out, int32_t* idx32_out,
+                                int64_t* idx_k_out, int32_t* cu_salientlens_out, int32_t* count_out,
+                                uint8_t* mask_out, void* stream) {
+  DYLLM_REQUIRE(rows >= 0 && batch >= 0, DYLLM_ERR_INVALID_ARGUMENT, "salient_select_static: rows %d batch %d", rows,
+                batch);
+  DYLLM_REQUIRE(rows <= kStaticSelectMaxRows, DYLLM_ERR_UNSUPPORTED,
+                "salient_select_static: %d rows exceed the built-in scratch capacity of %d rows; use "
+                "dyllm_salient_select with a caller-provided workspace",
+                rows, kStaticSelectMaxRows);
+  DYLLM_REQUIRE(cu_seqlens_q && cu_salientlens_out && count_out, DYLLM_ERR_INVALID_ARGUMENT,
+                "salient_select_static: null pointer");
+  DYLLM_REQUIRE(rows == 0 || (stats && idx_out), DYLLM_ERR_INVALID_ARGUMENT, "salient_select_static: null pointer");
+  DYLLM_REQUIRE(!idx_k_out || cu_promptlens, DYLLM_ERR_INVALID_ARGUMENT,
+                "salient_select_static: idx_k_out needs cu_promptlens");
+  void* scratch = nullptr;
+  const int rc = static_select_scratch(&scratch);
+  if (rc != DYLLM_OK)
+    return rc;
+  // launch_salient_select clears the descriptors it is going to use (the array keeps the previous
+  // call's content) before the kernel starts, on the same stream
+  return launch_salient_select(stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out,
+                               idx_k_out, cu_salientlens_out, count_out, mask_out, scratch,
                                static_cast<cudaStream_t>(stream));
 }
 

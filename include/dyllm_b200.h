@@ -77,6 +77,28 @@ int dyllm_salient_select(const float* stats, int rows, float threshold, const in
                          int64_t* idx_k_out, int32_t* cu_salientlens_out, int32_t* count_out,
                          uint8_t* mask_out, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Selection for callers that may not allocate.  Same inputs, outputs and results as
+ * dyllm_salient_select, but the scratch memory is a fixed array inside the library (about 16 KB, held
+ * by every GPU that loads the library until the process exits), so the caller passes no workspace and
+ * neither this call nor anything it uses calls cudaMalloc, cudaFree or another allocating routine.
+ * It is meant for hosts that have handed all device memory to a pool of their own before serving
+ * starts, or whose steady-state step must not touch the CUDA allocator because an allocation there
+ * would stall every stream of the device.  This entry point has no counterpart in the reference.
+ *   - rows may be at most dyllm_salient_select_static_max_rows() (4 Mi rows); larger inputs are
+ *     rejected with DYLLM_ERR_UNSUPPORTED and an error text that names the limit.
+ *   - The first call on a device looks up the array's device address (once per device, with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's content; each call
+ *     clears the part it uses on its stream before its kernel runs.  Two calls whose kernels can overlap
+ *     on the GPU (different streams without an ordering between them) race on the array and give
+ *     undefined results: issue them on one stream or order them with events. */
+int dyllm_salient_select_static(const float* stats, int rows, float threshold, const int32_t* cu_seqlens_q,
+                                int batch, const int32_t* cu_promptlens, int64_t* idx_out, int32_t* idx32_out,
+                                int64_t* idx_k_out, int32_t* cu_salientlens_out, int32_t* count_out,
+                                uint8_t* mask_out, void* stream);
+/* Largest `rows` dyllm_salient_select_static accepts. */
+int dyllm_salient_select_static_max_rows(void);
+
 /* out[t] = idxs[t] + cu_promptlens[g + 1] for t < *num_idxs, g = group with
  * cu_salientlens[g] <= t < cu_salientlens[g + 1]; at most max_threads entries are written.
  * ref: dyllm/csrc/attention/attention_aux_kernels.cu:112-128,173-200 (fused_offset_launch). */
