@@ -214,7 +214,7 @@ def run_ours(args):
     torch.set_default_dtype(torch.float32)
     init_weights_(model, seed=0)
     model.eval()
-    sr = runner.StepRunner(model, shape.mask_token_id, BLOCK, args.denoise_steps, FULL_STEPS, REFRESH)
+    sr = runner.StepRunner(model, shape.mask_token_id, BLOCK, args.denoise_steps, args.full_steps, REFRESH)
     g = torch.Generator().manual_seed(1)
     prompts = torch.randint(0, shape.vocab_size - 1024, (BATCH, PROMPT), generator=g).tolist()
 
@@ -314,7 +314,7 @@ def run_ours(args):
         "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels,
         "salient_rows_per_layer": {"mean": (sum(sal) / len(sal)) if sal else None, "max": max(sal) if sal else None},
     }
-    if args.layers != 32 or args.denoise_steps != DSTEPS:
+    if args.layers != 32 or args.denoise_steps != DSTEPS or args.full_steps != FULL_STEPS:
         line["invalid_reduced_config"] = True
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -329,6 +329,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers marks the line invalid")
     ap.add_argument("--denoise-steps", type=int, default=DSTEPS, help="debug only")
+    ap.add_argument("--full-steps", type=int, default=FULL_STEPS, help="debug only: dense steps per generation")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

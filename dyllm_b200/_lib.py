@@ -43,6 +43,8 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_attention_salient_rows": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P]),
     "dyllm_attention_kernel_info": (I, [I, P]),
     "dyllm_delta_v_update": (I, [P, P, P, I, P, I, P, P]),
+    "dyllm_add_rms_norm": (I, [P, P, P, F, P, P, I, I, P]),
+    "dyllm_rope_neox": (I, [P, P, P, P, I, P, I, I, I, P]),
 }
 
 # kernels of this library launched by one call of each entry point (for launch accounting)
@@ -52,6 +54,7 @@ KERNELS_PER_CALL = {
     "dyllm_cache_get_seqs": 1, "dyllm_cache_get_block": 1, "dyllm_cache_reset_full": 1, "dyllm_cache_reset_block": 1,
     "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 1, "dyllm_swiglu_ffn": 2, "dyllm_cache_dest_rows": 1,
     "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 1, "dyllm_delta_v_update": 1,
+    "dyllm_add_rms_norm": 1, "dyllm_rope_neox": 1,
 }
 launch_count = 0
 

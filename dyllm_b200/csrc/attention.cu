@@ -572,11 +572,11 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                 DYLLM_ERR_INVALID_ARGUMENT, "attention_sparse_varlen: maximum sequence lengths must be positive and fit");
   DYLLM_REQUIRE(num_salient >= 0 && num_salient <= total_q && num_salient <= total_k, DYLLM_ERR_INVALID_ARGUMENT,
                 "attention_sparse_varlen: salient index count %d out of range", num_salient);
-  DYLLM_REQUIRE(q && k && v && c && out && cu_seqlens_q && cu_seqlens_k && cu_salientlens && cosine_stats &&
+  DYLLM_REQUIRE(q && k && c && out && cu_seqlens_q && cu_seqlens_k && cu_salientlens && cosine_stats &&
                     cosine_out && workspace,
                 DYLLM_ERR_INVALID_ARGUMENT, "attention_sparse_varlen: null pointer");
-  DYLLM_REQUIRE(num_salient == 0 || (o_sal && idx_salient_row_q && idx_salient_row_k), DYLLM_ERR_INVALID_ARGUMENT,
-                "attention_sparse_varlen: salient rows without o_sal / index lists");
+  DYLLM_REQUIRE(num_salient == 0 || (v && o_sal && idx_salient_row_q && idx_salient_row_k), DYLLM_ERR_INVALID_ARGUMENT,
+                "attention_sparse_varlen: salient rows without delta-V / o_sal / index lists");
   DYLLM_REQUIRE(workspace_bytes >= dyllm_attention_sparse_workspace_bytes(total_q, num_heads), DYLLM_ERR_WORKSPACE,
                 "attention_sparse_varlen: workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
                 dyllm_attention_sparse_workspace_bytes(total_q, num_heads));

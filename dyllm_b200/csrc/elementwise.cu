@@ -1,0 +1,177 @@
+// Row-wise kernels that surround the saliency path in a decoder layer: RMSNorm with the residual add
+// fused in, and the NeoX-style rotary embedding.  Both are HBM-bound: each element is read once and
+// written once.
+#include "common.cuh"
+
+namespace dyllm {
+namespace {
+
+constexpr int kNormThreads = 256;
+
+// y = bf16( bf16((x + r) * rsqrt(mean((x + r)^2) + eps)) * w ), r_out = bf16(x + r); fp32 statistics.
+// One block per row; VPT 16-byte vectors per thread are kept in registers between the two passes.
+template <int VPT>
+__global__ void __launch_bounds__(kNormThreads)
+add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
+                    uint4* __restrict__ y, uint4* __restrict__ res_out, int vecs, float inv_width, float eps) {
+  const int64_t row = blockIdx.x;
+  const uint4* xr = x + row * vecs;
+  const uint4* rr = res_in ? res_in + row * vecs : nullptr;
+  float vals[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < vecs) {
+      const uint4 xv = __ldg(xr + v);
+      const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      uint4 rv = make_uint4(0, 0, 0, 0);
+      if (rr)
+        rv = __ldg(rr + v);
+      const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+      uint4 ro;
+      __nv_bfloat162* ro2 = reinterpret_cast<__nv_bfloat162*>(&ro);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(x2[i]);
+        const float2 b = __bfloat1622float2(r2[i]);
+        const float s0 = a.x + b.x, s1 = a.y + b.y;
+        vals[j][2 * i] = s0;
+        vals[j][2 * i + 1] = s1;
+        ss = fmaf(s0, s0, ss);
+        ss = fmaf(s1, s1, ss);
+        ro2[i] = __floats2bfloat162_rn(s0, s1);
+      }
+      if (res_out)
+        res_out[row * vecs + v] = ro;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+    ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  __shared__ float red[kNormThreads / 32];
+  __shared__ float s_scale;
+  if ((threadIdx.x & 31) == 0)
+    red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < kNormThreads / 32; ++i)
+      t += red[i];
+    s_scale = rsqrtf(t * inv_width + eps);
+  }
+  __syncthreads();
+  const float scale = s_scale;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int v = threadIdx.x + j * kNormThreads;
+    if (v < vecs) {
+      const uint4 wv = __ldg(w + v);
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      uint4 o;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        // two roundings, as the bf16 module does: normalise -> bf16, times weight -> bf16
+        const __nv_bfloat162 n = __floats2bfloat162_rn(vals[j][2 * i] * scale, vals[j][2 * i + 1] * scale);
+        o2[i] = __hmul2(n, w2[i]);
+      }
+      y[row * vecs + v] = o;
+    }
+  }
+}
+
+// x[r, h, :] rotated in place by the angle table row of positions[pos_idx ? pos_idx[r] : r]:
+// (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), halves of 64; 8 threads per (row, head).
+__global__ void __launch_bounds__(256)
+rope_neox_kernel(uint4* __restrict__ x, const int64_t* __restrict__ positions, const int64_t* __restrict__ pos_idx,
+                 const float* __restrict__ cos_sin, int rows, int heads, int max_pos,
+                 const int32_t* __restrict__ num_rows_dev) {
+  const int n = num_rows_dev ? min(rows, *num_rows_dev) : rows;
+  const int64_t total = static_cast<int64_t>(n) * heads * 8;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int part = static_cast<int>(t & 7);          // which 8 of the 64 rotation pairs
+    const int64_t rh = t >> 3;
+    const int r = static_cast<int>(rh / heads);
+    int64_t pos = positions[pos_idx ? pos_idx[r] : r];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + pos * 128;
+    uint4* base = x + rh * 16;                          // 128 bf16 = 16 vectors
+    const uint4 a = base[part], b = base[part + 8];
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+    uint4 oa, ob;
+    __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+    __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x1 = __bfloat1622float2(a2[i]);
+      const float2 x2 = __bfloat1622float2(b2[i]);
+      const int d = part * 8 + 2 * i;
+      const float c0 = __ldg(cs + d), c1 = __ldg(cs + d + 1), s0 = __ldg(cs + 64 + d), s1 = __ldg(cs + 64 + d + 1);
+      oa2[i] = __floats2bfloat162_rn(x1.x * c0 - x2.x * s0, x1.y * c1 - x2.y * s1);
+      ob2[i] = __floats2bfloat162_rn(x2.x * c0 + x1.x * s0, x2.y * c1 + x1.y * s1);
+    }
+    base[part] = oa;
+    base[part + 8] = ob;
+  }
+}
+
+}  // namespace
+}  // namespace dyllm
+
+using namespace dyllm;
+
+extern "C" {
+
+int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weight, float eps, void* y,
+                       void* residual_out, int rows, int width, void* stream) {
+  DYLLM_REQUIRE(rows >= 0 && width > 0, DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm: rows %d width %d", rows, width);
+  DYLLM_REQUIRE(width % 8 == 0 && width <= 8 * kNormThreads * 4, DYLLM_ERR_UNSUPPORTED,
+                "add_rms_norm: width %d must be a multiple of 8 and at most %d", width, 8 * kNormThreads * 4);
+  if (rows == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(x && weight && y, DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm: null pointer");
+  DYLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual_in) |
+                  reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y) |
+                  reinterpret_cast<uintptr_t>(residual_out)) & 15) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm: buffers must be 16-byte aligned");
+  const int vecs = width / 8;
+  const int vpt = cdiv_i(vecs, kNormThreads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint4* xp = static_cast<const uint4*>(x);
+  const uint4* rp = static_cast<const uint4*>(residual_in);
+  const uint4* wp = static_cast<const uint4*>(weight);
+  uint4* yp = static_cast<uint4*>(y);
+  uint4* rop = static_cast<uint4*>(residual_out);
+  const float inv = 1.0f / static_cast<float>(width);
+  switch (vpt) {
+    case 1: add_rms_norm_kernel<1><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
+    case 2: add_rms_norm_kernel<2><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
+    case 3: add_rms_norm_kernel<3><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
+    default: add_rms_norm_kernel<4><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
+  }
+  return check_launch("add_rms_norm");
+}
+
+int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, const float* cos_sin, int rows,
+                    const int32_t* num_rows_dev, int heads, int head_dim, int max_pos, void* stream) {
+  DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "rope_neox: head_dim %d (only 128 is built)", head_dim);
+  DYLLM_REQUIRE(rows >= 0 && heads > 0 && max_pos > 0, DYLLM_ERR_INVALID_ARGUMENT, "rope_neox: rows %d heads %d", rows,
+                heads);
+  if (rows == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(x && positions && cos_sin, DYLLM_ERR_INVALID_ARGUMENT, "rope_neox: null pointer");
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "rope_neox: x must be 16-byte aligned");
+  const int64_t total = static_cast<int64_t>(rows) * heads * 8;
+  int64_t want = cdiv_l(total, 256);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  const int blocks = static_cast<int>(want < cap ? want : cap);
+  rope_neox_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(x), positions, pos_idx,
+                                                                        cos_sin, rows, heads, max_pos, num_rows_dev);
+  return check_launch("rope_neox");
+}
+
+}  // extern "C"

@@ -186,3 +186,36 @@ def delta_v_update(v_new: torch.Tensor, cache: torch.Tensor, rows: torch.Tensor,
     call("dyllm_delta_v_update", ptr(v_new), ptr(cache), ptr(rows), v_new.size(0), ptr(num_rows_dev), v_new.size(1),
          ptr(dv), stream_ptr(v_new.device))
     return dv
+
+
+def add_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
+    """RMSNorm with the residual add fused in; returns ``y`` or ``(y, new_residual)``.
+
+    ref: dyllm/model_executor/layers/layernorm.py:17-53.
+    """
+    require_cuda(x, "x", torch.bfloat16, 2)
+    require_cuda(weight, "weight", torch.bfloat16, 1)
+    y = torch.empty_like(x)
+    res_out = None
+    if residual is not None:
+        require_cuda(residual, "residual", torch.bfloat16, 2)
+        res_out = torch.empty_like(x)
+    call("dyllm_add_rms_norm", ptr(x), ptr(residual), ptr(weight), float(eps), ptr(y), ptr(res_out), x.size(0),
+         x.size(1), stream_ptr(x.device))
+    return y if residual is None else (y, res_out)
+
+
+def rope_neox_(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, pos_idx: torch.Tensor | None = None,
+               num_rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """In-place NeoX rotary embedding of ``x [rows, heads, 128]``.
+
+    ref: dyllm/model_executor/layers/rotary_embedding.py:8-54.
+    """
+    require_cuda(x, "x", torch.bfloat16, 3)
+    require_cuda(positions, "positions", torch.int64, 1)
+    require_cuda(cos_sin, "cos_sin", torch.float32)
+    if pos_idx is not None:
+        require_cuda(pos_idx, "pos_idx", torch.int64, 1)
+    call("dyllm_rope_neox", ptr(x), ptr(positions), ptr(pos_idx), ptr(cos_sin), x.size(0), ptr(num_rows_dev), x.size(1),
+         x.size(2), cos_sin.size(0), stream_ptr(x.device))
+    return x

@@ -235,6 +235,25 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
  * tile, head-dim split, ok].  ref: dyllm/csrc/attention/attention.cpp:184-208. */
 int dyllm_attention_kernel_info(int dim, int64_t* info10);
 
+/* ------------------------------------------------------------------------------------------------
+ * Row-wise kernels around the path (every query row, HBM-bound)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* RMSNorm with the residual add fused in (bf16 in / out, fp32 statistics):
+ *   s = x + residual_in (residual_in null = 0);  residual_out = bf16(s) (nullable);
+ *   y = bf16( bf16(s * rsqrt(mean(s^2) + eps)) * weight ).
+ * width % 8 == 0, width <= 8192.  y may alias x, residual_out may alias residual_in.
+ * ref: dyllm/model_executor/layers/layernorm.py:17-53 (RMSNorm.rms_forward / add_rms_forward). */
+int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weight, float eps, void* y,
+                       void* residual_out, int rows, int width, void* stream);
+
+/* NeoX-style rotary embedding applied in place to x [rows, heads, 128] (bf16): row r uses the angle
+ * table row of positions[pos_idx ? pos_idx[r] : r], clamped to [0, max_pos); cos_sin is fp32
+ * [max_pos, 128] = cos(64) | sin(64).  num_rows_dev (nullable) bounds the rows on the device.
+ * ref: dyllm/model_executor/layers/rotary_embedding.py:8-54. */
+int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, const float* cos_sin, int rows,
+                    const int32_t* num_rows_dev, int heads, int head_dim, int max_pos, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -192,3 +192,19 @@ def test_attention_compact_delta_v_equals_padded(cuda_device, case_id):
                                   d(case["cu_q"]), d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]),
                                   d(case["idx_q"]), stats, mask, TAU, ro, d(case["idx_k"]) if ro else None, v_layout=3)
     assert torch.equal(out.cpu(), ref[0]) and torch.equal(stats.cpu(), ref[1]) and torch.equal(mask.cpu(), ref[2])
+
+
+def test_attention_no_salient_rows_with_empty_compact_delta_v(cuda_device):
+    """A layer may publish an empty salient set; the next layer then passes empty lists and tensors."""
+    from dyllm_b200.attention_ops import attention_sparse_varlen
+
+    case = make_case(2, 128, 128, 2, 2, False, 0, seed=77)
+    d = lambda t: t.to(cuda_device)
+    Tq = case["q"].size(0)
+    stats = torch.zeros(Tq, 3, device=cuda_device)
+    mask = torch.ones(Tq, dtype=torch.bool, device=cuda_device)
+    empty_dv = torch.empty(0, 2, 128, dtype=torch.bfloat16, device=cuda_device)
+    out = attention_sparse_varlen(d(case["q"]), d(case["k"]), empty_dv, d(case["c_old"]), d(case["o_sal"]),
+                                  d(case["cu_q"]), d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]),
+                                  d(case["idx_q"]), stats, mask, TAU, v_layout=3)
+    assert torch.equal(out.cpu(), case["c_old"]) and not bool(mask.any())
