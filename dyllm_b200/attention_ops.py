@@ -34,7 +34,7 @@ def _check_tensor(t, name, device, dtype, dim):
 def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int,
                             total_seqlen: int, cu_salientlens, idx_salient_row, cosine_stats, cosine_out,
                             threshold: float = 0.0, is_q_pruned: bool = False, idx_salient_row_k=None,
-                            force_mask_v_rows: int = -1, v_layout: int = 1) -> torch.Tensor:
+                            force_mask_v_rows: int = -1, v_layout: int = 1, num_salient_dev=None) -> torch.Tensor:
     """ref: dyllm/csrc/attention/attention.cpp:64-179.
 
     Same arguments, checks and return value (a fresh ``O`` shaped like ``Q``).  ``force_mask_v_rows``
@@ -42,7 +42,9 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     compute the same result).  ``V`` must be zero outside the listed salient key rows, as the
     reference's caller builds it.  ``v_layout`` (extension): bit 0 = feed the delta-V tile as an
     MN-major operand, bit 1 = ``V`` is compact ``[num_salient, Hkv, D]`` (row i = key
-    ``idx_salient_row_k[i]``) instead of the zero-padded ``[T_k, Hkv, D]`` tensor.
+    ``idx_salient_row_k[i]``) instead of the zero-padded ``[T_k, Hkv, D]`` tensor.  ``num_salient_dev``
+    (extension): device int32 scalar with the live length of the index lists, whose tensors are then
+    only capacity-sized.
     """
     if not (isinstance(Q, torch.Tensor) and Q.is_cuda):
         raise RuntimeError("Q must be CUDA")
@@ -103,7 +105,7 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     call("dyllm_attention_sparse_varlen", ptr(Q), ptr(K), ptr(V), ptr(C), ptr(o_sal), ptr(out), ptr(cu_seqlens_q),
          ptr(cu_seqlens_k), cu_seqlens_q.numel() - 1, int(max_seqlen_q), int(max_seqlen_k), Q.size(0), K.size(0), H,
          K.size(1), Q.size(2), ptr(cu_salientlens), ptr(idx_salient_row), ptr(idx_k), idx_salient_row.numel(),
-         ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_layout), stream_ptr(dev))
+         ptr(num_salient_dev), ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_layout), stream_ptr(dev))
     return out
 
 

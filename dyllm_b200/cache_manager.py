@@ -167,9 +167,10 @@ class CacheManager:
         reset_block_cuda(self.cache, c, self.seq_start_gpu, ctx.cu_seqlens_k, ctx.cu_seqlens_q, seq_ids,
                          ctx.total_seqlen)
 
-    def scatter_update(self, seq_ids: torch.Tensor, row_idx: torch.Tensor, new: torch.Tensor) -> None:
+    def scatter_update(self, seq_ids: torch.Tensor, row_idx: torch.Tensor, new: torch.Tensor,
+                       num_rows_dev: Optional[torch.Tensor] = None) -> None:
         ctx = get_context()
-        scatter_update_cuda(self.cache, new, row_idx, ctx.cu_seqlens_k, self.seq_start_gpu, seq_ids)
+        scatter_update_cuda(self.cache, new, row_idx, ctx.cu_seqlens_k, self.seq_start_gpu, seq_ids, num_rows_dev)
 
     def finish(self, finished_seq_ids: List[int]) -> bool:
         if len(finished_seq_ids) == 0:

@@ -35,6 +35,19 @@ class Context:
     positions_k: Optional[torch.Tensor] = None
     idx_salient_row32: Optional[torch.Tensor] = None
     max_salient_per_seq: int = 0
+    # Device-resident selection: when num_salient_dev is set, the idx_salient_row* tensors are
+    # capacity-sized buffers whose first *num_salient_dev entries are live; salient_hint is the host's
+    # estimate of that count (used only to shape launches).
+    num_salient_dev: Optional[torch.Tensor] = None
+    salient_hint: int = 0
+
+    def salient_rows(self):
+        """(idx_salient_row, idx_salient_row_k or None) trimmed to the live length (synchronises)."""
+        if self.num_salient_dev is None:
+            return self.idx_salient_row, self.idx_salient_row_k
+        n = int(self.num_salient_dev.item())
+        k = self.idx_salient_row_k[:n] if self.idx_salient_row_k is not None else None
+        return self.idx_salient_row[:n], k
 
 
 _CONTEXT = Context()

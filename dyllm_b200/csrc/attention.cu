@@ -436,7 +436,9 @@ attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, cons
                           int num_salient, const __nv_bfloat16* __restrict__ c_old,
                           const __nv_bfloat16* __restrict__ o_sal, __nv_bfloat16* __restrict__ out,
                           float* __restrict__ stats, uint8_t* __restrict__ mask, float threshold, int width,
-                          int row_blocks) {
+                          int row_blocks, const int32_t* __restrict__ num_salient_dev) {
+  if (num_salient_dev)
+    num_salient = min(num_salient, *num_salient_dev);
   if (static_cast<int>(blockIdx.x) < row_blocks) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= Tq)
@@ -466,6 +468,8 @@ attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, cons
     return;
   }
   const int i = blockIdx.x - row_blocks;
+  if (i >= num_salient)
+    return;
   const int r = idx_q[i];
   const uint4* old_row = reinterpret_cast<const uint4*>(c_old + static_cast<int64_t>(r) * width);
   const uint4* new_row = reinterpret_cast<const uint4*>(o_sal + static_cast<int64_t>(i) * width);
@@ -556,8 +560,9 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   int max_seqlen_q, int max_seqlen_k, int total_q, int total_k, int num_heads,
                                   int num_kv_heads, int head_dim, const int32_t* cu_salientlens,
                                   const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
-                                  int num_salient, float* cosine_stats, uint8_t* cosine_out, float threshold,
-                                  void* workspace, size_t workspace_bytes, int v_layout, void* stream) {
+                                  int num_salient, const int32_t* num_salient_dev, float* cosine_stats,
+                                  uint8_t* cosine_out, float threshold, void* workspace, size_t workspace_bytes,
+                                  int v_layout, void* stream) {
   const int v_mn_major = (v_layout & 1) ? 1 : 0;
   const int v_compact = (v_layout & 2) ? 1 : 0;
   DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "attention_sparse_varlen: head_dim %d (only 128 is built)",
@@ -622,7 +627,8 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   const int row_blocks = cdiv_i(total_q, 256);
   attention_finalize_kernel<<<row_blocks + num_salient, 256, 0, s>>>(
       p.partial, num_heads, total_q, idx_salient_row_q, num_salient, p.c_old,
-      static_cast<const __nv_bfloat16*>(o_sal), p.out, cosine_stats, cosine_out, threshold, num_heads * kD, row_blocks);
+      static_cast<const __nv_bfloat16*>(o_sal), p.out, cosine_stats, cosine_out, threshold, num_heads * kD, row_blocks,
+      num_salient_dev);
   return check_launch("attention_finalize");
 }
 

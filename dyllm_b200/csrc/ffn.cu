@@ -1,14 +1,21 @@
-// Gathered SwiGLU FFN on salient rows:  out[map[m]] = down( silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T) ).
-// Two launches of the tcgen05 GEMM in gemm.cuh: gate/up with the activation fused in the epilogue, then
-// the down projection whose epilogue scatters rows to their destination.
+// Gathered linear layers and the SwiGLU FFN on salient rows:
+//   out[map[m]] = down( silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T) )
+// built from the tcgen05 GEMM in gemm.cuh: gate/up with the activation fused in the epilogue, then the
+// down projection whose epilogue scatters rows to their destination.  Activation rows reach the GEMM
+// either through a small staging copy (rows gathered once into a compact buffer, then plain TMA boxes)
+// or directly by TMA gather4.  Launch shapes are chosen from a row-count hint; the live row count is
+// read on the device, so no host synchronisation is needed.
 #include "gemm.cuh"
 
 namespace dyllm {
 
+constexpr int kSplitRows = 512;   // split-K partial sums are kept for at most this many live rows
+constexpr int kMaxSplits = 4;
+
 namespace {
 
 template <int BNH, bool SWIGLU, int A_MODE, int STAGES>
-int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int n_tiles, cudaStream_t stream) {
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BNH, SWIGLU, STAGES>;
   auto kernel = gathered_gemm_kernel<BNH, SWIGLU, A_MODE, STAGES>;
   // one flag per kernel instantiation and device: the opt-in shared-memory size is a per-function attribute
@@ -23,71 +30,113 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
                        cudaGetErrorString(cudaGetLastError()));
     smem_set[dev] = true;
   }
-  dim3 grid(cdiv_i(p.M, kGemmBM), n_tiles);
   kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
   return check_launch("gathered_gemm");
 }
 
 template <int BNH, bool SWIGLU, int STAGES>
-int launch_mode(int a_mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int n_tiles,
+int launch_mode(int a_mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid,
                 cudaStream_t stream) {
-  switch (a_mode) {
-    case 0: return launch_one<BNH, SWIGLU, 0, STAGES>(ta, tb, p, n_tiles, stream);
-    case 1: return launch_one<BNH, SWIGLU, 1, STAGES>(ta, tb, p, n_tiles, stream);
-    default: return launch_one<BNH, SWIGLU, 2, STAGES>(ta, tb, p, n_tiles, stream);
-  }
-}
-
-}  // namespace
-
-// a_mode: 0 = rows m0..m0+127 of A by one TMA box (requires a_idx == null), 1 = TMA gather4, 2 = gather
-// with 16-byte loads by the epilogue warps.  n is the number of output columns per weight block
-// (the intermediate size for SWIGLU).  tile_n: 64 or 128 (0 = choose).
-int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& p_in, const void* b,
-                         int64_t b_total_rows, int n, cudaStream_t stream) {
-  GemmParams p = p_in;
-  DYLLM_REQUIRE(p.K > 0 && p.K % kGemmBK == 0, DYLLM_ERR_UNSUPPORTED, "gemm: K = %d is not a multiple of 64", p.K);
-  DYLLM_REQUIRE(n > 0 && n % 64 == 0, DYLLM_ERR_UNSUPPORTED, "gemm: N = %d is not a multiple of 64", n);
-  DYLLM_REQUIRE(p.lda % 8 == 0 && p.ldc % 8 == 0, DYLLM_ERR_UNSUPPORTED, "gemm: row pitches must be multiples of 8");
-  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
-                    (reinterpret_cast<uintptr_t>(p.out) & 15) == 0,
-                DYLLM_ERR_INVALID_ARGUMENT, "gemm: operands must be 16-byte aligned");
-  DYLLM_REQUIRE(a_mode >= 0 && a_mode <= 2, DYLLM_ERR_INVALID_ARGUMENT, "gemm: a_mode %d", a_mode);
-  DYLLM_REQUIRE(!(a_mode == 0 && p.a_idx), DYLLM_ERR_INVALID_ARGUMENT, "gemm: a_mode 0 cannot gather");
-  if (p.M <= 0)
-    return DYLLM_OK;
-  if (tile_n == 0) {
-    const int tiles128 = cdiv_i(p.M, kGemmBM) * (n / 128);
-    tile_n = (n % 128 == 0 && tiles128 >= sm_count() * 3 / 4) ? 128 : 64;
-  }
-  DYLLM_REQUIRE((tile_n == 64 || tile_n == 128) && n % tile_n == 0, DYLLM_ERR_UNSUPPORTED,
-                "gemm: tile_n %d does not divide N = %d", tile_n, n);
-  p.status_word = device_status_word();
-
-  CUtensorMap ta, tb;
-  int rc;
   if (a_mode == 0)
-    rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, p.lda, kGemmBM, kGemmBK, true);
-  else
-    rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, p.lda, 1, kGemmBK, true);
-  if (rc != DYLLM_OK)
-    return rc;
-  rc = encode_tmap_2d_bf16(&tb, b, b_total_rows, p.K, p.K, tile_n, kGemmBK, true);
-  if (rc != DYLLM_OK)
-    return rc;
-
-  const int n_tiles = n / tile_n;
-  if (swiglu) {
-    if (tile_n == 128)
-      return launch_mode<128, true, 4>(a_mode, ta, tb, p, n_tiles, stream);
-    return launch_mode<64, true, 6>(a_mode, ta, tb, p, n_tiles, stream);
-  }
-  if (tile_n == 128)
-    return launch_mode<128, false, 6>(a_mode, ta, tb, p, n_tiles, stream);
-  return launch_mode<64, false, 8>(a_mode, ta, tb, p, n_tiles, stream);
+    return launch_one<BNH, SWIGLU, 0, STAGES>(ta, tb, p, grid, stream);
+  return launch_one<BNH, SWIGLU, 1, STAGES>(ta, tb, p, grid, stream);
 }
 
-namespace {
+// compact[m] = x[idx[m]] for the live rows; one warp per row, 16-byte accesses.
+__global__ void __launch_bounds__(256)
+stage_rows_kernel(const uint4* __restrict__ x, int64_t x_pitch_vecs, const int32_t* __restrict__ idx, int x_rows,
+                  uint4* __restrict__ compact, int vecs, int num_rows, const int32_t* __restrict__ num_rows_dev) {
+  const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int m = blockIdx.x * 8 + warp; m < n; m += gridDim.x * 8) {
+    const int r = min(max(idx[m], 0), x_rows - 1);
+    const uint4* src = x + static_cast<int64_t>(r) * x_pitch_vecs;
+    uint4* dst = compact + static_cast<int64_t>(m) * vecs;
+    int v = lane;
+    for (; v + 96 < vecs; v += 128) {
+      const uint4 a = __ldg(src + v), b = __ldg(src + v + 32), c = __ldg(src + v + 64), d = __ldg(src + v + 96);
+      dst[v] = a;
+      dst[v + 32] = b;
+      dst[v + 64] = c;
+      dst[v + 96] = d;
+    }
+    for (; v < vecs; v += 32)
+      dst[v] = __ldg(src + v);
+  }
+}
+
+// out[map[m]][n] = bf16(scale[m] * sum_z partial[z][m][n]) in split order (deterministic).
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, int splits, int split_rows, int n_total, int M,
+                     const int32_t* __restrict__ m_count_dev, __nv_bfloat16* __restrict__ out, int64_t ldc,
+                     const int32_t* __restrict__ out_row_map, const float* __restrict__ row_scale,
+                     __nv_bfloat16* __restrict__ out2, int64_t ldc2, int split_col) {
+  const int m_count = m_count_dev ? min(*m_count_dev, M) : M;
+  if (m_count > split_rows)
+    return;  // the GEMM wrote its results directly
+  const int m = blockIdx.y;
+  if (m >= m_count)
+    return;
+  const int n = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (n >= n_total)
+    return;
+  const int out_row = out_row_map ? out_row_map[m] : m;
+  if (out_row < 0)
+    return;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int z = 0; z < splits; ++z) {
+    const float4* src =
+        reinterpret_cast<const float4*>(partial + (static_cast<int64_t>(z) * split_rows + m) * n_total + n);
+    const float4 a = __ldg(src), b = __ldg(src + 1);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  const float scale = row_scale ? row_scale[m] : 1.0f;
+  uint4 o = make_uint4(pack_bf16x2(acc[0] * scale, acc[1] * scale), pack_bf16x2(acc[2] * scale, acc[3] * scale),
+                       pack_bf16x2(acc[4] * scale, acc[5] * scale), pack_bf16x2(acc[6] * scale, acc[7] * scale));
+  __nv_bfloat16* dst = (out2 && n >= split_col) ? out2 + static_cast<int64_t>(out_row) * ldc2 + (n - split_col)
+                                                : out + static_cast<int64_t>(out_row) * ldc + n;
+  *reinterpret_cast<uint4*>(dst) = o;
+}
+
+struct Plan {
+  int tile_n;
+  int splits;
+  dim3 grid;
+};
+
+// Launch shape from the row-count hint: tile width so that the expected tiles fill the SMs, split-K
+// when even the narrow tiles leave most SMs idle, one grid row per expected row tile.
+Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_split) {
+  const int sms = sm_count();
+  const int h = (hint > 0 && hint < M) ? hint : M;
+  const int mt_h = cdiv_i(h, kGemmBM);
+  Plan plan;
+  if (tile_n == 0)
+    tile_n = (n % 128 == 0 && mt_h * (n / 128) >= sms * 3 / 4) ? 128 : 64;
+  plan.tile_n = tile_n;
+  const int n_tiles = n / tile_n;
+  plan.splits = 1;
+  if (!swiglu && can_split && h <= kSplitRows) {
+    const int ctas = mt_h * n_tiles;
+    if (ctas * 2 <= sms) {
+      int s = sms / ctas;
+      s = s > kMaxSplits ? kMaxSplits : s;
+      const int num_kt = K / kGemmBK;
+      s = s > num_kt ? num_kt : s;
+      plan.splits = s < 1 ? 1 : s;
+    }
+  }
+  int m_groups = mt_h;
+  const int mt_all = cdiv_i(M, kGemmBM);
+  m_groups = m_groups > mt_all ? mt_all : m_groups;
+  plan.grid = dim3(n_tiles, m_groups < 1 ? 1 : m_groups, plan.splits);
+  return plan;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t padded_rows(int rows) { return static_cast<size_t>(cdiv_i(rows, kGemmBM)) * kGemmBM; }
 
 // dest[m] = seq_starts[seq_ids[b]] + (row_idx[m] - cu[b]) for m < n, -1 beyond the live rows.
 __global__ void cache_dest_rows_kernel(const int64_t* __restrict__ row_idx, const int32_t* __restrict__ cu,
@@ -115,17 +164,96 @@ __global__ void cache_dest_rows_kernel(const int64_t* __restrict__ row_idx, cons
 }
 
 }  // namespace
+
+// a_mode: 0 = A rows m0..m0+127 by one TMA box (A dense or already staged), 1 = TMA gather4 through
+// p.a_idx.  n is the number of output columns per weight block (the intermediate size for SWIGLU).
+// tile_n: 64 or 128 (0 = choose).  `partial` enables split-K for the non-SwiGLU GEMM.
+int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& p_in, int64_t lda, const void* b,
+                         int64_t b_total_rows, int n, int rows_hint, float* partial, cudaStream_t stream) {
+  GemmParams p = p_in;
+  DYLLM_REQUIRE(p.K > 0 && p.K % kGemmBK == 0, DYLLM_ERR_UNSUPPORTED, "gemm: K = %d is not a multiple of 64", p.K);
+  DYLLM_REQUIRE(n > 0 && n % 64 == 0, DYLLM_ERR_UNSUPPORTED, "gemm: N = %d is not a multiple of 64", n);
+  DYLLM_REQUIRE(lda % 8 == 0 && p.ldc % 8 == 0 && p.ldc2 % 8 == 0, DYLLM_ERR_UNSUPPORTED,
+                "gemm: row pitches must be multiples of 8");
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.out2) & 15) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "gemm: operands must be 16-byte aligned");
+  DYLLM_REQUIRE(a_mode == 0 || a_mode == 1, DYLLM_ERR_INVALID_ARGUMENT, "gemm: a_mode %d", a_mode);
+  DYLLM_REQUIRE(!(a_mode == 0 && p.a_idx), DYLLM_ERR_INVALID_ARGUMENT, "gemm: a_mode 0 cannot gather");
+  DYLLM_REQUIRE(!p.out2 || (p.split_col > 0 && p.split_col % 128 == 0 && p.split_col < n), DYLLM_ERR_INVALID_ARGUMENT,
+                "gemm: split column %d must be a multiple of 128 inside (0, %d)", p.split_col, n);
+  if (p.M <= 0)
+    return DYLLM_OK;
+  const Plan plan = make_plan(swiglu, p.M, rows_hint, n, p.K, tile_n, partial != nullptr);
+  DYLLM_REQUIRE((plan.tile_n == 64 || plan.tile_n == 128) && n % plan.tile_n == 0, DYLLM_ERR_UNSUPPORTED,
+                "gemm: tile_n %d does not divide N = %d", plan.tile_n, n);
+  p.status_word = device_status_word();
+  p.n_total = n;
+  p.partial = plan.splits > 1 ? partial : nullptr;
+  p.split_rows = kSplitRows;
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mode == 0)
+    rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, lda, kGemmBM, kGemmBK, true);
+  else
+    rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, lda, 1, kGemmBK, true);
+  if (rc != DYLLM_OK)
+    return rc;
+  rc = encode_tmap_2d_bf16(&tb, b, b_total_rows, p.K, p.K, plan.tile_n, kGemmBK, true);
+  if (rc != DYLLM_OK)
+    return rc;
+
+  if (swiglu) {
+    if (plan.tile_n == 128)
+      rc = launch_mode<128, true, 4>(a_mode, ta, tb, p, plan.grid, stream);
+    else
+      rc = launch_mode<64, true, 6>(a_mode, ta, tb, p, plan.grid, stream);
+  } else if (plan.tile_n == 128) {
+    rc = launch_mode<128, false, 6>(a_mode, ta, tb, p, plan.grid, stream);
+  } else {
+    rc = launch_mode<64, false, 8>(a_mode, ta, tb, p, plan.grid, stream);
+  }
+  if (rc != DYLLM_OK || plan.splits == 1)
+    return rc;
+  const int rows = p.M < kSplitRows ? p.M : kSplitRows;
+  dim3 rgrid(cdiv_i(n, 256 * 8), rows);
+  splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(partial, plan.splits, kSplitRows, n, p.M, p.m_count_dev, p.out, p.ldc,
+                                                  p.out_row_map, p.row_scale, p.out2, p.ldc2, p.split_col);
+  return check_launch("splitk_reduce");
+}
+
+int stage_rows(const void* x, int64_t ldx, const int32_t* idx, int x_rows, void* compact, int width, int num_rows,
+               const int32_t* num_rows_dev, int rows_hint, cudaStream_t stream) {
+  const int h = (rows_hint > 0 && rows_hint < num_rows) ? rows_hint : num_rows;
+  int blocks = cdiv_i(h, 8);
+  const int cap = sm_count() * 8;
+  blocks = blocks > cap ? cap : (blocks < 1 ? 1 : blocks);
+  stage_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), ldx / 8, idx, x_rows,
+                                               static_cast<uint4*>(compact), width / 8, num_rows, num_rows_dev);
+  return check_launch("stage_rows");
+}
+
 }  // namespace dyllm
 
 using namespace dyllm;
 
 extern "C" {
 
-size_t dyllm_swiglu_ffn_workspace_bytes(int max_rows, int inter) {
-  if (max_rows <= 0 || inter <= 0)
+size_t dyllm_gathered_linear_workspace_bytes(int max_rows, int in_features, int out_features) {
+  if (max_rows <= 0 || in_features <= 0 || out_features <= 0)
     return 0;
-  const size_t padded = static_cast<size_t>(cdiv_i(max_rows, kGemmBM)) * kGemmBM;
-  return padded * static_cast<size_t>(inter) * 2;
+  return align_up(padded_rows(max_rows) * static_cast<size_t>(in_features) * 2, 1024) +
+         static_cast<size_t>(kMaxSplits) * kSplitRows * out_features * sizeof(float);
+}
+
+size_t dyllm_swiglu_ffn_workspace_bytes(int max_rows, int hidden, int inter) {
+  if (max_rows <= 0 || inter <= 0 || hidden <= 0)
+    return 0;
+  const size_t padded = padded_rows(max_rows);
+  return align_up(padded * static_cast<size_t>(hidden) * 2, 1024) +
+         align_up(padded * static_cast<size_t>(inter) * 2, 1024) +
+         static_cast<size_t>(kMaxSplits) * kSplitRows * hidden * sizeof(float);
 }
 
 int dyllm_cache_dest_rows(const int64_t* row_idx, const int32_t* cu_seqlens, const int64_t* seq_starts,
@@ -144,82 +272,127 @@ int dyllm_cache_dest_rows(const int64_t* row_idx, const int32_t* cu_seqlens, con
 }
 
 int dyllm_gathered_linear(const void* x, int x_rows, int in_features, int64_t ldx, const int32_t* idx, int num_rows,
-                          const int32_t* num_rows_dev, const void* weight, int out_features, void* out, int64_t ldo,
-                          const int32_t* out_row_map, const float* row_scale, int a_mode, int tile_n, void* stream) {
+                          const int32_t* num_rows_dev, int rows_hint, const void* weight, int out_features, void* out,
+                          int64_t ldo, void* out2, int64_t ldo2, int split_col, const int32_t* out_row_map,
+                          const float* row_scale, void* workspace, size_t workspace_bytes, int a_mode, int tile_n,
+                          void* stream) {
   DYLLM_REQUIRE(x_rows >= 0 && in_features > 0 && out_features > 0 && num_rows >= 0, DYLLM_ERR_INVALID_ARGUMENT,
                 "gathered_linear: x_rows %d in %d out %d num_rows %d", x_rows, in_features, out_features, num_rows);
   if (num_rows == 0 || x_rows == 0)
     return DYLLM_OK;
   DYLLM_REQUIRE(x && weight && out, DYLLM_ERR_INVALID_ARGUMENT, "gathered_linear: null pointer");
   if (a_mode < 0)
-    a_mode = 1;
-  DYLLM_REQUIRE(a_mode == 1 || a_mode == 2, DYLLM_ERR_INVALID_ARGUMENT, "gathered_linear: a_mode %d", a_mode);
+    a_mode = 0;
+  DYLLM_REQUIRE(a_mode == 0 || a_mode == 1, DYLLM_ERR_INVALID_ARGUMENT,
+                "gathered_linear: a_mode %d (0 = staged rows + TMA boxes, 1 = TMA gather4)", a_mode);
+  DYLLM_REQUIRE(in_features % 8 == 0 && ldx % 8 == 0, DYLLM_ERR_UNSUPPORTED,
+                "gathered_linear: pitches must be multiples of 8");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t stage_bytes = align_up(padded_rows(num_rows) * static_cast<size_t>(in_features) * 2, 1024);
+  const size_t need = dyllm_gathered_linear_workspace_bytes(num_rows, in_features, out_features);
+  const bool have_ws = workspace && workspace_bytes >= need && (reinterpret_cast<uintptr_t>(workspace) & 15) == 0;
+  DYLLM_REQUIRE(have_ws || a_mode == 1 || !idx, DYLLM_ERR_WORKSPACE,
+                "gathered_linear: staging the gathered rows needs a 16-byte aligned workspace of %zu bytes (got %zu)",
+                need, workspace_bytes);
+
   GemmParams g = {};
   g.a = static_cast<const __nv_bfloat16*>(x);
-  g.a_idx = idx;
+  g.a_rows = x_rows;
+  int64_t lda = ldx;
+  int mode = a_mode;
+  if (idx && a_mode == 0) {
+    int rc = stage_rows(x, ldx, idx, x_rows, workspace, in_features, num_rows, num_rows_dev, rows_hint, s);
+    if (rc != DYLLM_OK)
+      return rc;
+    g.a = static_cast<const __nv_bfloat16*>(workspace);
+    g.a_rows = static_cast<int>(padded_rows(num_rows));
+    lda = in_features;
+  } else if (idx) {
+    g.a_idx = idx;
+  } else {
+    mode = 0;
+  }
   g.m_count_dev = num_rows_dev;
   g.M = num_rows;
   g.K = in_features;
-  g.a_rows = x_rows;
-  g.lda = ldx;
   g.b_rows_per_expert = out_features;
   g.out = static_cast<__nv_bfloat16*>(out);
   g.ldc = ldo;
+  g.out2 = static_cast<__nv_bfloat16*>(out2);
+  g.ldc2 = out2 ? ldo2 : 0;
+  g.split_col = out2 ? split_col : 0;
   g.out_row_map = out_row_map;
   g.row_scale = row_scale;
-  return launch_gathered_gemm(false, a_mode, tile_n, g, weight, out_features, out_features,
-                              static_cast<cudaStream_t>(stream));
+  float* partial = have_ws ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + stage_bytes) : nullptr;
+  return launch_gathered_gemm(false, mode, tile_n, g, lda, weight, out_features, out_features, rows_hint, partial, s);
 }
 
 int dyllm_swiglu_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int32_t* idx, int num_rows,
-                     const int32_t* num_rows_dev, const void* w_gate_up, const void* w_down, int inter, void* out,
-                     int64_t ldo, const int32_t* out_row_map, void* workspace, size_t workspace_bytes, int a_mode,
-                     int tile_n, void* stream) {
+                     const int32_t* num_rows_dev, int rows_hint, const void* w_gate_up, const void* w_down, int inter,
+                     void* out, int64_t ldo, const int32_t* out_row_map, void* workspace, size_t workspace_bytes,
+                     int a_mode, int tile_n, void* stream) {
   DYLLM_REQUIRE(x_rows >= 0 && hidden > 0 && inter > 0 && num_rows >= 0, DYLLM_ERR_INVALID_ARGUMENT,
                 "swiglu_ffn: x_rows %d hidden %d inter %d num_rows %d", x_rows, hidden, inter, num_rows);
   if (num_rows == 0 || x_rows == 0)
     return DYLLM_OK;
   DYLLM_REQUIRE(x && w_gate_up && w_down && out && workspace, DYLLM_ERR_INVALID_ARGUMENT, "swiglu_ffn: null pointer");
-  DYLLM_REQUIRE(workspace_bytes >= dyllm_swiglu_ffn_workspace_bytes(num_rows, inter), DYLLM_ERR_WORKSPACE,
+  DYLLM_REQUIRE(workspace_bytes >= dyllm_swiglu_ffn_workspace_bytes(num_rows, hidden, inter), DYLLM_ERR_WORKSPACE,
                 "swiglu_ffn: workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
-                dyllm_swiglu_ffn_workspace_bytes(num_rows, inter));
+                dyllm_swiglu_ffn_workspace_bytes(num_rows, hidden, inter));
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT,
                 "swiglu_ffn: workspace must be 16-byte aligned");
+  DYLLM_REQUIRE(hidden % 8 == 0 && ldx % 8 == 0, DYLLM_ERR_UNSUPPORTED, "swiglu_ffn: pitches must be multiples of 8");
   if (a_mode < 0)
-    a_mode = 1;
-  DYLLM_REQUIRE(a_mode == 1 || a_mode == 2, DYLLM_ERR_INVALID_ARGUMENT, "swiglu_ffn: a_mode %d (1 = TMA gather4, "
-                "2 = vector-load gather)", a_mode);
+    a_mode = 0;
+  DYLLM_REQUIRE(a_mode == 0 || a_mode == 1, DYLLM_ERR_INVALID_ARGUMENT,
+                "swiglu_ffn: a_mode %d (0 = staged rows + TMA boxes, 1 = TMA gather4)", a_mode);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int padded = cdiv_i(num_rows, kGemmBM) * kGemmBM;
+  const size_t padded = padded_rows(num_rows);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* staged = ws;
+  uint8_t* inter_buf = ws + align_up(padded * static_cast<size_t>(hidden) * 2, 1024);
+  float* partial = reinterpret_cast<float*>(inter_buf + align_up(padded * static_cast<size_t>(inter) * 2, 1024));
 
   GemmParams g1 = {};
   g1.a = static_cast<const __nv_bfloat16*>(x);
-  g1.a_idx = idx;
+  g1.a_rows = x_rows;
+  int64_t lda = ldx;
+  int mode = a_mode;
+  if (idx && a_mode == 0) {
+    int rc = stage_rows(x, ldx, idx, x_rows, staged, hidden, num_rows, num_rows_dev, rows_hint, s);
+    if (rc != DYLLM_OK)
+      return rc;
+    g1.a = static_cast<const __nv_bfloat16*>(staged);
+    g1.a_rows = static_cast<int>(padded);
+    lda = hidden;
+  } else if (idx) {
+    g1.a_idx = idx;
+  } else {
+    mode = 0;
+  }
   g1.m_count_dev = num_rows_dev;
   g1.M = num_rows;
   g1.K = hidden;
-  g1.a_rows = x_rows;
-  g1.lda = ldx;
   g1.b_rows_per_expert = 2 * inter;
   g1.up_row_offset = inter;
-  g1.out = static_cast<__nv_bfloat16*>(workspace);
+  g1.out = reinterpret_cast<__nv_bfloat16*>(inter_buf);
   g1.ldc = inter;
-  int rc = launch_gathered_gemm(true, a_mode, tile_n, g1, w_gate_up, 2 * static_cast<int64_t>(inter), inter, s);
+  int rc = launch_gathered_gemm(true, mode, tile_n, g1, lda, w_gate_up, 2 * static_cast<int64_t>(inter), inter,
+                                rows_hint, nullptr, s);
   if (rc != DYLLM_OK)
     return rc;
 
   GemmParams g2 = {};
-  g2.a = static_cast<const __nv_bfloat16*>(workspace);
+  g2.a = reinterpret_cast<const __nv_bfloat16*>(inter_buf);
   g2.m_count_dev = num_rows_dev;
   g2.M = num_rows;
   g2.K = inter;
-  g2.a_rows = padded;
-  g2.lda = inter;
+  g2.a_rows = static_cast<int>(padded);
   g2.b_rows_per_expert = hidden;
   g2.out = static_cast<__nv_bfloat16*>(out);
   g2.ldc = ldo;
   g2.out_row_map = out_row_map;
-  return launch_gathered_gemm(false, 0, tile_n, g2, w_down, hidden, hidden, s);
+  return launch_gathered_gemm(false, 0, tile_n, g2, inter, w_down, hidden, hidden, rows_hint, partial, s);
 }
 
 }  // extern "C"

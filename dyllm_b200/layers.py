@@ -89,12 +89,23 @@ class ColumnParallelLinear(LinearBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return F.linear(x, self.weight, self.bias)
 
-    def forward_gathered(self, x: torch.Tensor, idx32: torch.Tensor, num_rows: int) -> torch.Tensor:
-        """``self(x[idx])`` without materialising the gathered copy (tcgen05 GEMM, rows by TMA gather)."""
-        y = ops.gathered_linear(x, self.weight, idx32, num_rows=num_rows)
+    def forward_gathered(self, x: torch.Tensor, idx32: torch.Tensor, num_rows: int, num_rows_dev=None,
+                         rows_hint: int = 0, split_col: int = 0):
+        """``self(x[idx])`` on the tcgen05 GEMM; ``num_rows`` may be a capacity with the live count on the
+        device.  With ``split_col`` the output columns are returned as two tensors (K and V halves)."""
+        n_out = self.weight.size(0)
+        if split_col:
+            out = torch.empty((num_rows, split_col), dtype=x.dtype, device=x.device)
+            out2 = torch.empty((num_rows, n_out - split_col), dtype=x.dtype, device=x.device)
+        else:
+            out, out2 = torch.empty((num_rows, n_out), dtype=x.dtype, device=x.device), None
+        ops.gathered_linear(x, self.weight, idx32, num_rows=num_rows, num_rows_dev=num_rows_dev, rows_hint=rows_hint,
+                            out=out, out2=out2, split_col=split_col)
         if self.bias is not None:
-            y = y + self.bias
-        return y
+            out += self.bias[: out.size(1)]
+            if out2 is not None:
+                out2 += self.bias[out.size(1):]
+        return (out, out2) if split_col else out
 
 
 class MergedColumnParallelLinear(ColumnParallelLinear):
@@ -151,6 +162,8 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size))
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and self.weight.dtype == torch.bfloat16:
+            return ops.add_rms_norm(x.contiguous(), self.weight, self.eps, residual)
         orig = x.dtype
         xf = x.float()
         if residual is not None:
@@ -183,6 +196,9 @@ class RotaryEmbedding(nn.Module):
     def rotate(self, positions: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         if self._cos_sin_cache.device != x.device:
             self._cos_sin_cache = self._cos_sin_cache.to(x.device)
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and x.size(2) == 128 and x.is_contiguous():
+            # in place on the freshly projected tensor
+            return ops.rope_neox_(x, positions, self._cos_sin_cache.view(-1, 128))
         positions = torch.clamp(positions, 0, self._cos_sin_cache.size(0) - 1)
         cos, sin = self._cos_sin_cache[positions].chunk(2, dim=-1)
         return apply_rotary_emb(x, cos, sin)
@@ -242,25 +258,27 @@ class LLaDAMLP(nn.Module):
         return self.cache_update(y)
 
     def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
-        """Sparse step on the full ``[T_q, hidden]`` activation: rows are fetched by TMA gather through the
-        step's salient index list and the down projection scatters straight into the FFN-output cache
-        (replaces gather_rows_2D + MLP + scatter_update, dyllm/model_executor/models/llada.py:184-186)."""
+        """Sparse step on the full ``[T_q, hidden]`` activation: the salient rows are read through the step's
+        index list (live count on the device) and the down projection scatters straight into the
+        FFN-output cache (replaces gather_rows_2D + MLP + scatter_update,
+        dyllm/model_executor/models/llada.py:184-186)."""
         ctx, md = get_context(), get_metadata()
-        n = ctx.idx_salient_row.numel()
+        cap = ctx.idx_salient_row.numel()
+        n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
         cm = self.cache_update.cache_manager
-        if n:
+        if cap:
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
             if self.down_proj.tp_size > 1:
                 y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
-                                   num_rows=n)
+                                   num_rows=cap, num_rows_dev=n_dev, rows_hint=hint)
                 dist.all_reduce(y)
-                cm.scatter_update(md.running_seqs_tensor, rows_k, y)
+                cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
             else:
-                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor)
-                flops = 6.0 * n * hidden.size(1) * self.down_proj.weight.size(1)
+                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
+                flops = 6.0 * (hint or cap) * hidden.size(1) * self.down_proj.weight.size(1)
                 with profiling.region("swiglu_ffn", flops):
                     ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
-                                   num_rows=n, out=cm.cache, out_row_map=dest)
+                                   num_rows=cap, num_rows_dev=n_dev, rows_hint=hint, out=cm.cache, out_row_map=dest)
         cm.finish(md.finished_seqs)
         return self.cache_update.result()
 
@@ -298,6 +316,25 @@ class Attention(nn.Module):
         self.threshold = threshold
         self.context_cache = CacheManager(self.num_heads * self.head_dim)
         self.v_cache = CacheManager(self.num_kv_heads * self.head_dim)
+        self._hint_host = None      # pinned int32[1]: this layer's salient count, copied back without waiting
+        self._hint_event = None
+        self._hint = 0
+
+    def _next_hint(self, count_dev: torch.Tensor, capacity: int) -> int:
+        """Estimate of the salient count this layer has just produced: its value from the previous step
+        (read back asynchronously, never waited for), or the capacity when none has arrived yet.  The
+        estimate only shapes launches; kernels take the true count from the device."""
+        if self._hint_host is None:
+            self._hint_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._hint_event = torch.cuda.Event()
+        elif self._hint_event.query():
+            self._hint = int(self._hint_host[0])
+            profiling.count("salient_rows", self._hint)
+        else:
+            return min(self._hint, capacity) if self._hint else capacity
+        self._hint_host.copy_(count_dev, non_blocking=True)
+        self._hint_event.record()
+        return min(self._hint, capacity) if self._hint else capacity
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         """Dense step: q, k, v hold every row.  Sparse step: ``q`` every query row, ``k`` the packed full
@@ -317,20 +354,22 @@ class Attention(nn.Module):
         is_q_pruned = ctx.idx_salient_row_k is not None
         rows_k = ctx.idx_salient_row_k if is_q_pruned else ctx.idx_salient_row
         idx_q32 = ctx.idx_salient_row32
-        n_sal = idx_q32.numel()
+        cap = idx_q32.numel()            # capacity of the salient lists; the live count may be on the device
+        n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
 
         # delta-V and value-cache update in one pass over the salient rows (attention.py:67-74,89-96)
-        dv = torch.empty((n_sal, Hkv, D), dtype=v.dtype, device=v.device)
-        if n_sal:
-            dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, self.v_cache.seq_start_gpu, seq_t)
-            ops.delta_v_update(v.view(n_sal, Hkv * D), self.v_cache.cache, dest, dv.view(n_sal, Hkv * D))
+        dv = torch.empty((cap, Hkv, D), dtype=v.dtype, device=v.device)
+        if cap:
+            dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, self.v_cache.seq_start_gpu, seq_t, n_dev)
+            ops.delta_v_update(v.view(cap, Hkv * D), self.v_cache.cache, dest, dv.view(cap, Hkv * D), n_dev)
         v_full = self.v_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs).view(-1, Hkv, D)
 
         # exact attention of the salient query rows (attention.py:76-87)
-        with profiling.region("salient_attention", 4.0 * n_sal * ctx.max_seqlen_k * H * D):
+        max_rows = max(min(ctx.max_salient_per_seq, ctx.max_seqlen_q), 1)
+        with profiling.region("salient_attention", 4.0 * (hint or cap) * ctx.max_seqlen_k * H * D):
             o_sal = attention_salient_rows(q, k, v_full, ctx.cu_seqlens_k, ctx.cu_salientlens, idx_q32,
-                                           max_rows_per_seq=max(ctx.max_salient_per_seq, 1), num_salient=n_sal)
+                                           max_rows_per_seq=max_rows, num_salient=cap)
 
         stats = torch.zeros((ctx.total_seqlen, 3), dtype=torch.float32, device=q.device)
         mask = torch.empty((ctx.total_seqlen,), dtype=torch.bool, device=q.device)
@@ -343,26 +382,27 @@ class Attention(nn.Module):
         with profiling.region("delta_attention", flops):
             new_c = attention_sparse_varlen(q, k, dv, c_old, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens,
-                                            idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=3)
+                                            idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=3,
+                                            num_salient_dev=n_dev)
 
-        # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch
+        # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch; the new
+        # lists stay on the device together with their length
         if _world_size() > 1:
             dist.all_reduce(stats, op=dist.ReduceOp.SUM)
         with profiling.region("salient_select", 12.0 * ctx.total_seqlen):
             sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,
                                      ctx.cu_promptlens if is_q_pruned else None)
-        num_valid = int(sel.count.item())
-        profiling.count("salient_rows", num_valid)
-
         if is_q_pruned:
             self.context_cache.reset_block(new_c.flatten(-2, -1), seq_t)
-            ctx.idx_salient_row_k = sel.idx_k[:num_valid]
+            ctx.idx_salient_row_k = sel.idx_k
         else:
             self.context_cache.reset_full(new_c.flatten(-2, -1), seq_t, seq_ids_list=md.running_seqs)
-        ctx.idx_salient_row = sel.idx[:num_valid]
-        ctx.idx_salient_row32 = sel.idx32[:num_valid]
+        ctx.idx_salient_row = sel.idx
+        ctx.idx_salient_row32 = sel.idx32
         ctx.cu_salientlens = sel.cu_salientlens
-        ctx.max_salient_per_seq = min(num_valid, ctx.max_seqlen_q)
+        ctx.num_salient_dev = sel.count
+        ctx.max_salient_per_seq = ctx.max_seqlen_q
+        ctx.salient_hint = self._next_hint(sel.count, ctx.total_seqlen)
 
         self.v_cache.finish(md.finished_seqs)
         self.context_cache.finish(md.finished_seqs)

@@ -139,8 +139,9 @@ def bench_kv_proj(args):
     w = (torch.randn(2 * H * D, HID, device=dev) * 0.02).bfloat16()
     idx_q, _, _, _ = salient_lists(args.rows, dev)
     idx32 = idx_q.to(torch.int32)
-    ms = time_launches(lambda: ops.gathered_linear(x, w, idx32, a_mode=args.a_mode, tile_n=args.tile_n), args.iters,
-                       args.flush)
+    out = torch.empty(idx32.numel(), 2 * H * D, device=dev, dtype=torch.bfloat16)
+    ms = time_launches(lambda: ops.gathered_linear(x, w, idx32, out=out, a_mode=args.a_mode, tile_n=args.tile_n),
+                       args.iters, args.flush)
     s = idx32.numel()
     return ms, 2.0 * HID * 2 * H * D + s * HID * 2 + s * 2 * H * D * 2, "B"
 

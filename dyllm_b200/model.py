@@ -15,6 +15,7 @@ from dataclasses import dataclass
 import torch
 from torch import nn
 
+from . import ops
 from .cache_manager import CacheManager
 from .context import get_context, get_metadata
 from .layers import (Attention, ColumnParallelLinear, KVParallelLinear, LLaDAMLP, RMSNorm, RotaryEmbedding,
@@ -72,15 +73,17 @@ class LLaDAAttention(nn.Module):
             self.k_cache.reset_full(k.flatten(-2, -1), md.running_seqs_tensor, seq_ids_list=md.running_seqs)
             o = self.attn(q, k, v)
         else:
-            n_sal = ctx.idx_salient_row.numel()
+            cap = ctx.idx_salient_row.numel()   # capacity; the live count may sit on the device
+            n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
             q = self.rotary_emb.rotate(positions, q)
-            if n_sal:
-                kv = self.kv_proj.forward_gathered(hidden_states, ctx.idx_salient_row32, n_sal)
-                k_new, v_new = kv.split([self.kv_size, self.kv_size], dim=-1)
-                k_new = self.rotary_emb.rotate(positions[ctx.idx_salient_row], k_new.reshape(-1, Hkv, D))
+            if cap:
+                k_new, v_new = self.kv_proj.forward_gathered(hidden_states, ctx.idx_salient_row32, cap, n_dev, hint,
+                                                             split_col=self.kv_size)
+                ops.rope_neox_(k_new.view(cap, Hkv, D), positions, self.rotary_emb.cos_sin_cache.view(-1, D),
+                               pos_idx=ctx.idx_salient_row, num_rows_dev=n_dev)
                 rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
-                self.k_cache.scatter_update(md.running_seqs_tensor, rows_k, k_new.flatten(-2, -1))
-                v_new = v_new.reshape(-1, Hkv, D)
+                self.k_cache.scatter_update(md.running_seqs_tensor, rows_k, k_new, n_dev)
+                v_new = v_new.view(cap, Hkv, D)
             else:
                 v_new = torch.empty((0, Hkv, D), dtype=q.dtype, device=q.device)
             k_full = self.k_cache.get_seqs(md.running_seqs_tensor, allow_view=True, seq_ids_list=md.running_seqs)

@@ -108,10 +108,24 @@ def cache_dest_rows(row_idx: torch.Tensor, cu_seqlens: torch.Tensor, seq_starts:
     return dest
 
 
+_gemm_workspaces: dict = {}
+
+
+def _gemm_workspace(nbytes: int, device) -> torch.Tensor:
+    """One shared scratch tensor per device for the row staging, the FFN intermediate and split-K sums
+    (kernels on one stream use it one after the other)."""
+    ws = _gemm_workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _gemm_workspaces[device] = ws
+    return ws
+
+
 def gathered_linear(x: torch.Tensor, weight: torch.Tensor, idx: torch.Tensor | None = None,
-                    num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None,
-                    out: torch.Tensor | None = None, out_row_map: torch.Tensor | None = None,
-                    row_scale: torch.Tensor | None = None, a_mode: int = -1, tile_n: int = 0) -> torch.Tensor:
+                    num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None, rows_hint: int = 0,
+                    out: torch.Tensor | None = None, out2: torch.Tensor | None = None, split_col: int = 0,
+                    out_row_map: torch.Tensor | None = None, row_scale: torch.Tensor | None = None, a_mode: int = -1,
+                    tile_n: int = 0) -> torch.Tensor:
     """``out[map[m]] = scale[m] * (x[idx[m]] @ weight.T)`` on the tcgen05 tensor cores.
 
     ref: dyllm/model_executor/models/llada.py:108 (``kv_proj(hidden_states[idx_salient_row])``).
@@ -124,27 +138,19 @@ def gathered_linear(x: torch.Tensor, weight: torch.Tensor, idx: torch.Tensor | N
         num_rows = idx.numel() if idx is not None else x.size(0)
     n_out = weight.size(0)
     if out is None:
-        out = torch.empty((num_rows, n_out), dtype=torch.bfloat16, device=x.device)
+        out = torch.empty((num_rows, n_out if out2 is None else split_col), dtype=torch.bfloat16, device=x.device)
+    if num_rows == 0:
+        return out
+    need = load().dyllm_gathered_linear_workspace_bytes(num_rows, x.size(1), n_out)
+    ws = _gemm_workspace(need, x.device)
     call("dyllm_gathered_linear", ptr(x), x.size(0), x.size(1), x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev),
-         ptr(weight), n_out, ptr(out), out.stride(0), ptr(out_row_map), ptr(row_scale), a_mode, tile_n,
-         stream_ptr(x.device))
+         int(rows_hint), ptr(weight), n_out, ptr(out), out.stride(0), ptr(out2), out2.stride(0) if out2 is not None else 0,
+         int(split_col), ptr(out_row_map), ptr(row_scale), ptr(ws), ws.numel(), a_mode, tile_n, stream_ptr(x.device))
     return out
 
 
-_ffn_workspaces: dict = {}
-
-
-def _ffn_workspace(num_rows: int, inter: int, device) -> torch.Tensor:
-    need = load().dyllm_swiglu_ffn_workspace_bytes(num_rows, inter)
-    ws = _ffn_workspaces.get(device)
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(need, dtype=torch.uint8, device=device)
-        _ffn_workspaces[device] = ws
-    return ws
-
-
 def swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor | None = None,
-               num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None,
+               num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None, rows_hint: int = 0,
                out: torch.Tensor | None = None, out_row_map: torch.Tensor | None = None, a_mode: int = -1,
                tile_n: int = 0) -> torch.Tensor:
     """``out[map[m]] = down(silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T))`` for the gathered rows.
@@ -165,10 +171,10 @@ def swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, i
         out = torch.empty((num_rows, hidden), dtype=torch.bfloat16, device=x.device)
     if num_rows == 0:
         return out
-    ws = _ffn_workspace(num_rows, inter, x.device)
+    ws = _gemm_workspace(load().dyllm_swiglu_ffn_workspace_bytes(num_rows, hidden, inter), x.device)
     call("dyllm_swiglu_ffn", ptr(x), x.size(0), hidden, x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev),
-         ptr(w_gate_up), ptr(w_down), inter, ptr(out), out.stride(0), ptr(out_row_map), ptr(ws), ws.numel(), a_mode,
-         tile_n, stream_ptr(x.device))
+         int(rows_hint), ptr(w_gate_up), ptr(w_down), inter, ptr(out), out.stride(0), ptr(out_row_map), ptr(ws),
+         ws.numel(), a_mode, tile_n, stream_ptr(x.device))
     return out
 
 
@@ -183,6 +189,8 @@ def delta_v_update(v_new: torch.Tensor, cache: torch.Tensor, rows: torch.Tensor,
     require_cuda(rows, "rows", torch.int32, 1)
     if dv is None:
         dv = torch.empty_like(v_new)
+    if v_new.size(0) == 0:
+        return dv
     call("dyllm_delta_v_update", ptr(v_new), ptr(cache), ptr(rows), v_new.size(0), ptr(num_rows_dev), v_new.size(1),
          ptr(dv), stream_ptr(v_new.device))
     return dv

@@ -143,33 +143,45 @@ int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t*
 
 /* ------------------------------------------------------------------------------------------------
  * Gathered tensor-core GEMMs (tcgen05 / TMEM).  Weights are bf16 [out, in] row-major as in
- * torch.nn.Linear.  a_mode selects how activation rows reach shared memory: 1 = TMA gather4
- * (default when negative), 2 = 16-byte vector loads; tile_n = 64, 128 or 0 (choose).
+ * torch.nn.Linear.  The live row count may be given on the device (num_rows_dev, nullable): then
+ * num_rows is only an upper bound that sizes buffers, rows_hint (<= 0: none) is the expected count
+ * used to shape the launch, and no host synchronisation is needed.  a_mode selects how activation
+ * rows reach the tensor cores: 0 = the indexed rows are first staged into a compact buffer of the
+ * workspace and then loaded as plain TMA boxes (default when negative), 1 = TMA gather4 straight from
+ * x.  tile_n = 64, 128 or 0 (choose).
  * ---------------------------------------------------------------------------------------------- */
 
+/* Bytes of workspace dyllm_gathered_linear needs for up to max_rows rows (row staging + split-K
+ * partial sums).  Without a workspace the call still works with a_mode 1 or idx == null. */
+size_t dyllm_gathered_linear_workspace_bytes(int max_rows, int in_features, int out_features);
+
 /* out[map[m]] = scale[m] * (x[idx[m]] W^T), m < min(num_rows, *num_rows_dev).  idx null = identity,
- * out_row_map null = m (negative entries drop the row), row_scale null = 1.  in_features % 64 == 0,
- * out_features % 64 == 0.  Used for the K/V projection of salient rows
- * (ref: dyllm/model_executor/models/llada.py:108, dyllm/model_executor/layers/linear.py:50-51). */
+ * out_row_map null = m (negative entries drop the row), row_scale null = 1.  When out2 is not null,
+ * output columns >= split_col (a multiple of 128) go to out2[.., column - split_col] instead (used to
+ * write K and V of the fused K/V projection into two tensors).  in_features % 64 == 0,
+ * out_features % 64 == 0.  Few rows and few column tiles switch on a deterministic split-K.
+ * ref: dyllm/model_executor/models/llada.py:108 (kv_proj(hidden_states[idx_salient_row])),
+ *      dyllm/model_executor/layers/linear.py:50-51. */
 int dyllm_gathered_linear(const void* x, int x_rows, int in_features, int64_t ldx, const int32_t* idx,
-                          int num_rows, const int32_t* num_rows_dev, const void* weight, int out_features,
-                          void* out, int64_t ldo, const int32_t* out_row_map, const float* row_scale,
-                          int a_mode, int tile_n, void* stream);
+                          int num_rows, const int32_t* num_rows_dev, int rows_hint, const void* weight,
+                          int out_features, void* out, int64_t ldo, void* out2, int64_t ldo2, int split_col,
+                          const int32_t* out_row_map, const float* row_scale, void* workspace,
+                          size_t workspace_bytes, int a_mode, int tile_n, void* stream);
 
 /* Bytes of workspace dyllm_swiglu_ffn needs for up to max_rows gathered rows. */
-size_t dyllm_swiglu_ffn_workspace_bytes(int max_rows, int inter);
+size_t dyllm_swiglu_ffn_workspace_bytes(int max_rows, int hidden, int inter);
 
 /* out[map[m]] = down( silu(x[idx[m]] Wg^T) * (x[idx[m]] Wu^T) ) for the gathered rows: w_gate_up is
  * [2 * inter, hidden] with the gate rows first, w_down is [hidden, inter].  The SiLU product is fused
  * into the first GEMM's epilogue, the row scatter into the second's.  workspace: 16-byte aligned,
- * dyllm_swiglu_ffn_workspace_bytes(num_rows, inter) bytes.
+ * dyllm_swiglu_ffn_workspace_bytes(num_rows, hidden, inter) bytes.
  * ref: dyllm/model_executor/models/llada.py:38-43,184-185 (gather + MLP),
  *      dyllm/model_executor/layers/activations.py:9-14, dyllm/model_executor/layers/linear.py:76-93,195-220,
  *      dyllm/model_executor/layers/mlp_cache_manage.py:24-40 (scatter into the FFN-output cache). */
 int dyllm_swiglu_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int32_t* idx, int num_rows,
-                     const int32_t* num_rows_dev, const void* w_gate_up, const void* w_down, int inter, void* out,
-                     int64_t ldo, const int32_t* out_row_map, void* workspace, size_t workspace_bytes, int a_mode,
-                     int tile_n, void* stream);
+                     const int32_t* num_rows_dev, int rows_hint, const void* w_gate_up, const void* w_down,
+                     int inter, void* out, int64_t ldo, const int32_t* out_row_map, void* workspace,
+                     size_t workspace_bytes, int a_mode, int tile_n, void* stream);
 
 /* dest_rows[m] = seq_starts[seq_ids[b]] + row_idx[m] - cu_seqlens[b] (the cache row that
  * dyllm_cache_scatter_update would write) for m < min(num_rows, *num_rows_dev), -1 for the rest;
@@ -195,7 +207,9 @@ size_t dyllm_attention_sparse_workspace_bytes(int total_q, int num_heads);
  * q, c, out: [total_q, num_heads, 128]; k, v: [total_k, num_kv_heads, 128]; o_sal: [num_salient,
  * num_heads, 128]; all bf16.  idx_salient_row_q (query space) and idx_salient_row_k (key space) hold
  * num_salient ascending rows each, grouped by sequence through cu_salientlens; pass the same list
- * twice when queries are not pruned.  The softmax scale is 1/sqrt(128).  Statistics are reduced over
+ * twice when queries are not pruned.  num_salient_dev (nullable) is a device int32 holding the live list
+ * length; num_salient is then only the capacity of the lists (the per-sequence counts always come from
+ * cu_salientlens on the device).  The softmax scale is 1/sqrt(128).  Statistics are reduced over
  * heads in a fixed order.  v_layout is a bit set: bit 0 selects how the delta-V tile is fed to the
  * tensor cores (1 = as gathered, MN-major descriptor; 0 = transposed while gathering; results are
  * identical); bit 1 set means v is compact, [num_salient, num_kv_heads, 128] with row i belonging to
@@ -208,8 +222,9 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   int max_seqlen_q, int max_seqlen_k, int total_q, int total_k, int num_heads,
                                   int num_kv_heads, int head_dim, const int32_t* cu_salientlens,
                                   const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
-                                  int num_salient, float* cosine_stats, uint8_t* cosine_out, float threshold,
-                                  void* workspace, size_t workspace_bytes, int v_layout, void* stream);
+                                  int num_salient, const int32_t* num_salient_dev, float* cosine_stats,
+                                  uint8_t* cosine_out, float threshold, void* workspace, size_t workspace_bytes,
+                                  int v_layout, void* stream);
 
 
 /* Delta-V of the step and value-cache update in one pass over the salient rows:

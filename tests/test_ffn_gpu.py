@@ -1,7 +1,8 @@
 """Parity of the tcgen05 gathered GEMMs / SwiGLU FFN with the fp32 oracle.
 
 Tolerances follow the path's contract: bf16 outputs within max-abs 2e-2 and relative L2 1e-2.
-The a_mode 2 cases (vector-load gather) run before the a_mode 1 cases (TMA gather4).
+Both ways of feeding activation rows are covered: a_mode 0 (rows staged into a compact buffer, plain TMA
+boxes) and a_mode 1 (TMA gather4 straight from the activation tensor).
 """
 import pytest
 import torch
@@ -28,7 +29,7 @@ def _status_ok():
     assert _lib.load().dyllm_device_status() == 0
 
 
-@pytest.mark.parametrize("a_mode", [2, 1], ids=["mode2", "mode1"])
+@pytest.mark.parametrize("a_mode", [0, 1], ids=["staged", "gather4"])
 @pytest.mark.parametrize("rows,k,n,tile_n", [(128, 64, 64, 64), (26, 256, 128, 128), (410, 4096, 1024, 0),
                                               (300, 3584, 512, 64)])
 def test_gathered_linear(cuda_device, a_mode, rows, k, n, tile_n):
@@ -45,7 +46,7 @@ def test_gathered_linear(cuda_device, a_mode, rows, k, n, tile_n):
     _check(got, want.bfloat16(), f"gathered_linear mode {a_mode}")
 
 
-@pytest.mark.parametrize("a_mode", [2, 1], ids=["mode2", "mode1"])
+@pytest.mark.parametrize("a_mode", [0, 1], ids=["staged", "gather4"])
 def test_gathered_linear_scatter_scale_and_device_count(cuda_device, a_mode):
     from dyllm_b200 import ops
 
@@ -73,7 +74,7 @@ def test_gathered_linear_scatter_scale_and_device_count(cuda_device, a_mode):
     assert bool((out.cpu()[untouched] == 3.0).all())
 
 
-@pytest.mark.parametrize("a_mode", [2, 1], ids=["mode2", "mode1"])
+@pytest.mark.parametrize("a_mode", [0, 1], ids=["staged", "gather4"])
 @pytest.mark.parametrize("rows,hidden,inter,tile_n", [(26, 4096, 12288, 0), (410, 4096, 12288, 0), (130, 512, 1024, 64),
                                                        (130, 512, 1024, 128), (1, 256, 128, 64)])
 def test_swiglu_ffn_matches_oracle(cuda_device, a_mode, rows, hidden, inter, tile_n):
@@ -119,3 +120,63 @@ def test_swiglu_ffn_scatters_into_cache_rows(cuda_device):
     touched = torch.zeros(batch * L, dtype=torch.bool)
     touched[dest.cpu().long()] = True
     assert torch.equal(dcache.cpu()[~touched], cache[~touched])
+
+
+@pytest.mark.parametrize("a_mode", [0, 1], ids=["staged", "gather4"])
+@pytest.mark.parametrize("bound,live,hint,k,n", [
+    (1024, 211, 200, 512, 256),    # device-side count below the bound
+    (1024, 700, 100, 512, 256),    # hint too small: each CTA walks over several row tiles; split-K declined on the device
+    (512, 26, 26, 4096, 256),      # few rows, few column tiles: split-K
+    (2048, 0, 64, 256, 128),       # nothing live
+])
+def test_gathered_linear_device_count_hint_and_split_k(cuda_device, a_mode, bound, live, hint, k, n):
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(bound + live)
+    x = torch.randn(2048, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.03).bfloat16()
+    idx = torch.sort(torch.randperm(2048, generator=g)[:bound]).values.to(torch.int32)
+    out = torch.full((bound, n), 5.0, dtype=torch.bfloat16, device=cuda_device)
+    ops.gathered_linear(x.to(cuda_device), w.to(cuda_device), idx.to(cuda_device), num_rows=bound,
+                        num_rows_dev=torch.tensor([live], dtype=torch.int32, device=cuda_device), rows_hint=hint,
+                        out=out, a_mode=a_mode)
+    _status_ok()
+    if live:
+        want = (x.float()[idx[:live].long()] @ w.float().t()).bfloat16()
+        _check(out[:live], want, "device count")
+    assert bool((out[live:] == 5.0).all())
+
+
+def test_gathered_linear_column_split_into_two_outputs(cuda_device):
+    """Fused K/V projection: the first half of the columns lands in one tensor, the second in another."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(600, 512, generator=g).bfloat16()
+    w = (torch.randn(512, 512, generator=g) * 0.03).bfloat16()
+    idx = torch.sort(torch.randperm(600, generator=g)[:150]).values.to(torch.int32)
+    k_out = torch.zeros(150, 256, dtype=torch.bfloat16, device=cuda_device)
+    v_out = torch.zeros(150, 256, dtype=torch.bfloat16, device=cuda_device)
+    ops.gathered_linear(x.to(cuda_device), w.to(cuda_device), idx.to(cuda_device), out=k_out, out2=v_out, split_col=256)
+    _status_ok()
+    want = (x.float()[idx.long()] @ w.float().t()).bfloat16()
+    _check(k_out, want[:, :256], "K half")
+    _check(v_out, want[:, 256:], "V half")
+
+
+@pytest.mark.parametrize("bound,live,hint", [(2048, 300, 280), (2048, 900, 128), (256, 40, 0)])
+def test_swiglu_ffn_device_count(cuda_device, bound, live, hint):
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(live)
+    hidden, inter = 512, 1024
+    x = torch.randn(2048, hidden, generator=g).bfloat16()
+    w1 = (torch.randn(2 * inter, hidden, generator=g) * 0.03).bfloat16()
+    w2 = (torch.randn(hidden, inter, generator=g) * 0.03).bfloat16()
+    idx = torch.sort(torch.randperm(2048, generator=g)[:bound]).values.to(torch.int32)
+    out = torch.full((bound, hidden), 5.0, dtype=torch.bfloat16, device=cuda_device)
+    ops.swiglu_ffn(x.to(cuda_device), w1.to(cuda_device), w2.to(cuda_device), idx.to(cuda_device), num_rows=bound,
+                   num_rows_dev=torch.tensor([live], dtype=torch.int32, device=cuda_device), rows_hint=hint, out=out)
+    _status_ok()
+    _check(out[:live], orc.swiglu_ffn(x[idx[:live].long()], w1, w2), "swiglu device count")
+    assert bool((out[live:] == 5.0).all())

@@ -66,10 +66,11 @@ def _run_layer(dev):
         with torch.inference_mode():
             out, residual = layer(positions, x.to(dev).bfloat16(), None)
         ctx = get_context()
+        idx, idx_k = (None, None) if is_full else ctx.salient_rows()
         results.append(dict(out=out.float().cpu(), residual=residual.float().cpu(),
-                            idx=None if is_full else ctx.idx_salient_row.cpu(),
+                            idx=None if is_full else idx.cpu(),
                             cu_sal=None if is_full else ctx.cu_salientlens.cpu(),
-                            idx_k=ctx.idx_salient_row_k.cpu() if (not is_full and ro) else None))
+                            idx_k=idx_k.cpu() if (not is_full and ro) else None))
     return results
 
 
