@@ -39,10 +39,14 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_swiglu_ffn_workspace_bytes": (Z, [I, I, I]),
     "dyllm_swiglu_ffn": (I, [P, I, I, c_int64, P, I, P, I, P, P, I, P, c_int64, P, P, Z, I, I, P]),
     "dyllm_cache_dest_rows": (I, [P, P, P, P, I, I, P, P, P]),
+    "dyllm_moe_route": (I, [P, I, I, c_int64, P, I, P, P, I, I, I, P, P, P]),
+    "dyllm_moe_ffn_workspace_bytes": (Z, [I, I, I, I, I]),
+    "dyllm_moe_ffn": (I, [P, I, I, c_int64, P, I, P, I, P, P, I, P, P, I, I, I, P, c_int64, P, P, Z, P]),
     "dyllm_attention_sparse_workspace_bytes": (Z, [I, I]),
     "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, P, F, P, Z, I, P]),
     "dyllm_attention_salient_rows": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P]),
     "dyllm_attention_kernel_info": (I, [I, P]),
+    "dyllm_attention_trace": (I, [P]),
     "dyllm_delta_v_update": (I, [P, P, P, I, P, I, P, P]),
     "dyllm_add_rms_norm": (I, [P, P, P, F, P, P, I, I, P]),
     "dyllm_rope_neox": (I, [P, P, P, P, I, P, I, I, I, P]),
@@ -53,7 +57,7 @@ KERNELS_PER_CALL = {
     "dyllm_context_stats": 1, "dyllm_cosine_mask": 1, "dyllm_salient_select": 1, "dyllm_salient_select_static": 1,
     "dyllm_fused_offset": 1,
     "dyllm_cache_get_seqs": 1, "dyllm_cache_get_block": 1, "dyllm_cache_reset_full": 1, "dyllm_cache_reset_block": 1,
-    "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 2, "dyllm_swiglu_ffn": 3, "dyllm_cache_dest_rows": 1,
+    "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 2, "dyllm_swiglu_ffn": 3, "dyllm_cache_dest_rows": 1, "dyllm_moe_route": 1, "dyllm_moe_ffn": 5,
     "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 1, "dyllm_delta_v_update": 1,
     "dyllm_add_rms_norm": 1, "dyllm_rope_neox": 1,
 }

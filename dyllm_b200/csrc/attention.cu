@@ -29,7 +29,9 @@ constexpr int kAttnThreads = 192;
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one [128][128] bf16 tile = two [128][64] swizzled halves
 constexpr uint32_t kHalfBytes = 128 * 64 * 2;
 constexpr uint32_t kAttnSmem = 3 * kTileBytes + 1024;
-constexpr uint32_t kAttnTmemCols = 256;          // S: columns 0..127, O: columns 128..255
+// Tensor memory: two S buffers (columns 0..127 and 128..255) during pass A, so that the product of
+// key tile t+1 runs while tile t is being reduced; in pass B the second buffer holds O.
+constexpr uint32_t kAttnTmemCols = 256;
 constexpr float kNegBig = -1.0e30f;
 
 struct AttnParams {
@@ -49,8 +51,21 @@ struct AttnParams {
   float scale_log2;              // log2(e) / sqrt(D)
   int v_mn_major;                // 1: dV tile kept [keys][d] (MN-major operand); 0: transposed while gathering
   int v_compact;                 // 1: v holds one row per salient key, in list order; 0: v is [Tk, Hkv, D]
+  unsigned long long* trace;     // optional [256][8] phase timestamps (ns) of the first 256 CTAs; null = off
   int* status_word;
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+#define DYLLM_TRACE(slot)                                                  \
+  do {                                                                     \
+    if (p.trace && blockIdx.x < 256 && threadIdx.x == 64)                  \
+      p.trace[blockIdx.x * 8 + (slot)] = global_ns();                      \
+  } while (0)
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -89,7 +104,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* q_smem = smem;                      // Q tile
   uint8_t* kv_smem0 = smem + kTileBytes;       // K stage 0 / gathered Ksal, later P
   uint8_t* kv_smem1 = smem + 2 * kTileBytes;   // K stage 1 / gathered dV
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full, s_empty, b_full, p_full, pv_done, a_done;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], b_full, p_full, pv_done, a_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -103,8 +118,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(&k_full[1], 1);
     mbar_init(&k_empty[0], 1);
     mbar_init(&k_empty[1], 1);
-    mbar_init(&s_full, 1);
-    mbar_init(&s_empty, 128);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(&s_empty[0], 128);
+    mbar_init(&s_empty[1], 128);
     mbar_init(&b_full, EXACT ? 1 : 128);
     mbar_init(&p_full, 128);
     mbar_init(&pv_done, 1);
@@ -123,7 +140,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_s = tmem_slot;
+  const uint32_t tmem_s0 = tmem_slot;
   const uint32_t tmem_o = tmem_slot + 128;
 
   if (warp == 0) {
@@ -167,9 +184,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, v_mn_major ? 1 : 0);
     const uint32_t q_addr = smem_u32(q_smem);
     mbar_wait(&q_full, 0, &abort_flag, p.status_word, 302);
+    int uses[2] = {0, 0};   // how often each S buffer has been handed to the softmax warps
     for (int t = 0; t < num_kt + num_st; ++t) {
       const bool sal_tile = t >= num_kt;
       const int st = t - num_kt;
+      const int sb = sal_tile ? 0 : (t & 1);   // pass B keeps to buffer 0: buffer 1 holds O then
+      const int use = uses[sb]++;
+      const uint32_t tmem_s = tmem_s0 + sb * 128;
       uint32_t kb_addr;
       if (!sal_tile) {
         const int s = t & 1;
@@ -179,7 +200,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_wait(&b_full, st & 1, &abort_flag, p.status_word, 304);
         kb_addr = smem_u32(kv_smem0);
       }
-      mbar_wait(&s_empty, (t & 1) ^ 1, &abort_flag, p.status_word, 305);
+      mbar_wait(&s_empty[sb], (use & 1) ^ 1, &abort_flag, p.status_word, 305);
       tc_fence_after_sync();
       if (lane == 0) {
         // S = Q K^T: contraction over d in two swizzled halves of 64, four K = 16 steps each
@@ -193,7 +214,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         if (!sal_tile)
           umma_commit(&k_empty[t & 1]);
-        umma_commit(&s_full);
+        umma_commit(&s_full[sb]);
         if (EXACT && t == num_kt - 1)
           umma_commit(&a_done);
       }
@@ -228,6 +249,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t t_lane = static_cast<uint32_t>(qd * 32) << 16;
     const float c = p.scale_log2;
     float m = kNegBig, l = 0.f;
+    DYLLM_TRACE(0);
+
+    if (!EXACT && q0 + row < q_end) {
+      // bring this thread's C_old row (256 bytes) into L2 now; the epilogue reads it much later
+      const char* crow = reinterpret_cast<const char*>(p.c_old + (static_cast<int64_t>(q0 + row) * p.H + h) * kD);
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(crow));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(crow + 128));
+    }
 
     if (EXACT) {
       // gather this thread's query row (or zeros past the list) into the swizzled Q tile
@@ -245,26 +274,38 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
 
     // pass A: running maximum and sum over all keys
+    int uses[2] = {0, 0};
     for (int kt = 0; kt < num_kt; ++kt) {
-      mbar_wait(&s_full, kt & 1, &abort_flag, p.status_word, 307);
+      const int sb = kt & 1;
+      const int use = uses[sb]++;
+      const uint32_t tmem_s = tmem_s0 + sb * 128;
+      mbar_wait(&s_full[sb], use & 1, &abort_flag, p.status_word, 307);
       tc_fence_after_sync();
+      if (kt == 0)
+        DYLLM_TRACE(7);
       const int valid = len_k - kt * kBKeys;   // keys of this tile that belong to the sequence
 #pragma unroll 1
       for (int c0 = 0; c0 < kBKeys; c0 += 32) {
         uint32_t sr[32];
         tmem_ld_32x32(tmem_s + t_lane + c0, sr);
         tmem_ld_wait();
-        if (c0 + 32 >= kBKeys) {  // last chunk read: the MMA warp may overwrite S
+        if (c0 + 32 >= kBKeys) {  // last chunk read: the MMA warp may overwrite this S buffer
           tc_fence_before_sync();
-          mbar_arrive(&s_empty);
+          mbar_arrive(&s_empty[sb]);
         }
         float cmax = kNegBig;
+        if (valid >= kBKeys) {   // whole tile inside the sequence: no masking
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(sr[i]);
-          s = (c0 + i < valid) ? s : kNegBig;
-          sr[i] = __float_as_uint(s);
-          cmax = fmaxf(cmax, s);
+          for (int i = 0; i < 32; ++i)
+            cmax = fmaxf(cmax, __uint_as_float(sr[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float s = __uint_as_float(sr[i]);
+            s = (c0 + i < valid) ? s : kNegBig;
+            sr[i] = __float_as_uint(s);
+            cmax = fmaxf(cmax, s);
+          }
         }
         const float m_new = fmaxf(m, cmax);
         const float mc = m_new * c;
@@ -278,9 +319,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
 
     // pass B: salient keys
+    DYLLM_TRACE(1);
     const float mc = m * c;
     for (int st = 0; st < num_st; ++st) {
-      const int t = num_kt + st;
       // The buffers are free for tile 0 once the last Q K^T product is complete: s_full of the last
       // key tile was observed above and is committed after every earlier MMA.  Later tiles wait for the
       // previous P dV product.
@@ -325,16 +366,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_arrive(&b_full);
       }
       // P = exp2(S2 * c - m * c) for the live columns
-      mbar_wait(&s_full, t & 1, &abort_flag, p.status_word, 309);
+      DYLLM_TRACE(2);
+      const int use = uses[0]++;
+      mbar_wait(&s_full[0], use & 1, &abort_flag, p.status_word, 309);
+      DYLLM_TRACE(3);
       tc_fence_after_sync();
 #pragma unroll 1
       for (int c0 = 0; c0 < kBKeys; c0 += 32) {
         uint32_t sr[32];
-        tmem_ld_32x32(tmem_s + t_lane + c0, sr);
+        tmem_ld_32x32(tmem_s0 + t_lane + c0, sr);
         tmem_ld_wait();
         if (c0 + 32 >= kBKeys) {
           tc_fence_before_sync();
-          mbar_arrive(&s_empty);
+          mbar_arrive(&s_empty[0]);
         }
         uint32_t pk[16];
 #pragma unroll
@@ -353,11 +397,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       fence_proxy_async_smem();
       mbar_arrive(&p_full);
+      DYLLM_TRACE(4);
     }
     if (num_st > 0) {
       mbar_wait(&pv_done, (num_st - 1) & 1, &abort_flag, p.status_word, 310);
       tc_fence_after_sync();
     }
+    DYLLM_TRACE(5);
 
     // epilogue: new = old + O / rowsum; bf16 store; partial statistics of this head.  The
     // tensor-memory loads are warp-collective, so every lane issues them; only the global-memory
@@ -369,7 +415,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const __nv_bfloat16* cold = EXACT ? nullptr : p.c_old + off;
     __nv_bfloat16* dst = (EXACT ? p.o_sal : p.out) + off;
     float dot = 0.f, nn = 0.f, no = 0.f;
-#pragma unroll 1
+    // the whole C_old row in one batch of independent loads
+    uint4 old_row[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      old_row[j] = (EXACT || !live) ? make_uint4(0, 0, 0, 0) : __ldg(reinterpret_cast<const uint4*>(cold) + j);
+#pragma unroll
     for (int c0 = 0; c0 < kD; c0 += 32) {
       uint32_t orr[32];
       if (num_st > 0) {
@@ -381,10 +432,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           orr[i] = 0u;
       }
       if (live) {
-        uint4 oldv[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          oldv[j] = EXACT ? make_uint4(0, 0, 0, 0) : __ldg(reinterpret_cast<const uint4*>(cold + c0) + j);
+        const uint4* oldv = old_row + c0 / 8;
         const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(oldv);
         uint32_t pk[16];
 #pragma unroll
@@ -412,6 +460,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       ps[1] = nn;
       ps[2] = no;
     }
+    DYLLM_TRACE(6);
   }
 
   tc_fence_before_sync();
@@ -522,6 +571,7 @@ attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, cons
 }
 
 bool g_attn_smem_set[2][64] = {{false}, {false}};
+unsigned long long* g_attn_trace = nullptr;
 
 template <bool EXACT>
 int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
@@ -618,6 +668,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
   p.v_mn_major = v_mn_major;
   p.v_compact = v_compact;
+  p.trace = g_attn_trace;
   p.status_word = device_status_word();
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
   rc = launch_attention<false>(tq, tk, tk, p, blocks, s);
@@ -678,6 +729,11 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
   p.status_word = device_status_word();
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
   return launch_attention<true>(tk, tk, tv, p, blocks, static_cast<cudaStream_t>(stream));
+}
+
+int dyllm_attention_trace(void* device_buffer) {
+  g_attn_trace = static_cast<unsigned long long*>(device_buffer);
+  return DYLLM_OK;
 }
 
 int dyllm_attention_kernel_info(int dim, int64_t* info10) {

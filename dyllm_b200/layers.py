@@ -283,6 +283,74 @@ class LLaDAMLP(nn.Module):
         return self.cache_update.result()
 
 
+class LLaDAMoESparseBlock(nn.Module):
+    """Sparse MoE feed-forward: softmax top-k router (no renormalisation unless the config asks for it),
+    SiLU experts, expert tensor parallelism or expert parallelism with an all-reduce combine.
+    ref: dyllm/model_executor/models/lladamoe.py:48-142."""
+
+    def __init__(self, config, expert_parallel_size: int = 1) -> None:
+        super().__init__()
+        self.num_experts = config.num_experts
+        self.top_k = config.num_experts_per_tok
+        self.renormalize = bool(getattr(config, "norm_topk_prob", False))
+        H, I = config.hidden_size, config.expert_intermediate_size
+        self.hidden_size, self.intermediate_size = H, I
+        world = _world_size()
+        if expert_parallel_size not in (1, world):
+            raise ValueError("expert_parallel_size must be 1 (expert tensor parallelism) or "
+                             f"tensor_parallel_size ({world}); got {expert_parallel_size}")
+        self.ep_size = expert_parallel_size
+        self.ep_rank = _rank() if expert_parallel_size > 1 else 0
+        self.expert_parallel = self.ep_size > 1
+        if self.expert_parallel:
+            if self.num_experts % self.ep_size != 0:
+                raise ValueError(f"num_experts ({self.num_experts}) must be divisible by EP size ({self.ep_size})")
+            self.num_local_experts = self.num_experts // self.ep_size
+            self.expert_start = self.ep_rank * self.num_local_experts
+            self.local_intermediate_size = I
+        else:
+            if I % world != 0:
+                raise ValueError(f"expert_intermediate_size ({I}) must be divisible by TP size ({world})")
+            self.num_local_experts = self.num_experts
+            self.expert_start = 0
+            self.local_intermediate_size = I // world
+        self.gate = ReplicatedLinear(H, self.num_experts, bias=False)
+        self.gate_up_proj = nn.Parameter(torch.empty(self.num_local_experts, 2 * self.local_intermediate_size, H))
+        self.down_proj = nn.Parameter(torch.empty(self.num_local_experts, H, self.local_intermediate_size))
+        self.cache_update = MLPcache(H)
+
+    def _experts(self, x, idx32, num_rows, n_dev, hint, out=None, out_row_map=None):
+        w, ids = ops.moe_route(x, self.gate.weight, self.top_k, self.renormalize, idx32, num_rows, n_dev)
+        return ops.moe_ffn(x, self.gate_up_proj, self.down_proj, w, ids, self.expert_start, idx32, num_rows, n_dev,
+                           hint, out, out_row_map)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Reference calling convention: ``x`` holds the rows to process."""
+        y = self._experts(x, None, x.size(0), None, 0)
+        if _world_size() > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM)
+        return self.cache_update(y)
+
+    def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Sparse step on the full activation: rows through the salient list, results scattered into the
+        FFN-output cache (at TP/EP > 1 after the all-reduce)."""
+        ctx, md = get_context(), get_metadata()
+        cap = ctx.idx_salient_row.numel()
+        n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
+        cm = self.cache_update.cache_manager
+        if cap:
+            rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
+            if _world_size() > 1:
+                y = self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint)
+                dist.all_reduce(y, op=dist.ReduceOp.SUM)
+                cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
+            else:
+                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
+                self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
+        cm.finish(md.finished_seqs)
+        return self.cache_update.result()
+
+
 # --------------------------------------------------------------------------------------------------
 # attention (ref: dyllm/model_executor/layers/attention.py)
 # --------------------------------------------------------------------------------------------------

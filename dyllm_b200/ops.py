@@ -227,3 +227,51 @@ def rope_neox_(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, 
     call("dyllm_rope_neox", ptr(x), ptr(positions), ptr(pos_idx), ptr(cos_sin), x.size(0), ptr(num_rows_dev), x.size(1),
          x.size(2), cos_sin.size(0), stream_ptr(x.device))
     return x
+
+
+def moe_route(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, renormalize: bool = False,
+              idx: torch.Tensor | None = None, num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None):
+    """fp32 softmax router with top-k selection; returns (weights fp32 [rows, k], expert ids int32 [rows, k]).
+
+    ref: dyllm/model_executor/layers/fused_moe.py:375-407.
+    """
+    require_cuda(x, "x", torch.bfloat16, 2)
+    require_cuda(router_weight, "router_weight", torch.bfloat16, 2)
+    if num_rows is None:
+        num_rows = idx.numel() if idx is not None else x.size(0)
+    w = torch.empty((num_rows, top_k), dtype=torch.float32, device=x.device)
+    ids = torch.empty((num_rows, top_k), dtype=torch.int32, device=x.device)
+    call("dyllm_moe_route", ptr(x), x.size(0), x.size(1), x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev),
+         ptr(router_weight), router_weight.size(0), int(top_k), int(bool(renormalize)), ptr(w), ptr(ids),
+         stream_ptr(x.device))
+    return w, ids
+
+
+def moe_ffn(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+            expert_start: int = 0, idx: torch.Tensor | None = None, num_rows: int | None = None,
+            num_rows_dev: torch.Tensor | None = None, rows_hint: int = 0, out: torch.Tensor | None = None,
+            out_row_map: torch.Tensor | None = None) -> torch.Tensor:
+    """Expert-grouped SwiGLU FFN with the routing weights folded in and the top-k slots summed.
+
+    ref: dyllm/model_executor/layers/fused_moe.py:269-335; dyllm/model_executor/models/lladamoe.py:107-142.
+    """
+    require_cuda(x, "x", torch.bfloat16, 2)
+    require_cuda(w1, "w1", torch.bfloat16, 3)
+    require_cuda(w2, "w2", torch.bfloat16, 3)
+    require_cuda(topk_weights, "topk_weights", torch.float32, 2)
+    require_cuda(topk_ids, "topk_ids", torch.int32, 2)
+    e_local, hidden, inter = w2.size(0), w2.size(1), w2.size(2)
+    if w1.shape != (e_local, 2 * inter, hidden):
+        raise RuntimeError("w1 must be [E, 2 * inter, hidden] and w2 [E, hidden, inter]")
+    top_k = topk_ids.size(1)
+    if num_rows is None:
+        num_rows = idx.numel() if idx is not None else x.size(0)
+    if out is None:
+        out = torch.empty((num_rows, hidden), dtype=torch.bfloat16, device=x.device)
+    if num_rows == 0:
+        return out
+    ws = _gemm_workspace(load().dyllm_moe_ffn_workspace_bytes(num_rows, top_k, e_local, hidden, inter), x.device)
+    call("dyllm_moe_ffn", ptr(x), x.size(0), hidden, x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev), int(rows_hint),
+         ptr(topk_weights), ptr(topk_ids), top_k, ptr(w1), ptr(w2), e_local, int(expert_start), inter, ptr(out),
+         out.stride(0), ptr(out_row_map), ptr(ws), ws.numel(), stream_ptr(x.device))
+    return out

@@ -245,10 +245,48 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
                                  int total_k, int num_heads, int num_kv_heads, int head_dim,
                                  const int32_t* cu_salientlens, const int32_t* idx_salient_row_q, void* stream);
 
+/* Tracing aid: while a device buffer of 256 * 8 uint64 is registered, each of the first 256 CTAs of
+ * dyllm_attention_sparse_varlen stores %globaltimer (ns) at seven phase boundaries (slot 0 start, 7 first
+ * logits ready, 1 end of pass A, 2 salient rows gathered, 3 their logits ready, 4 P written, 5 P dV
+ * done, 6 end).  Pass null to switch tracing off (the default). */
+int dyllm_attention_trace(void* device_buffer);
+
 /* Launch resources of the main attention kernel: [registers, local bytes, static shared bytes,
  * dynamic shared bytes, threads per block, resident blocks per SM, query rows per block, keys per
  * tile, head-dim split, ok].  ref: dyllm/csrc/attention/attention.cpp:184-208. */
 int dyllm_attention_kernel_info(int dim, int64_t* info10);
+
+/* ------------------------------------------------------------------------------------------------
+ * Mixture-of-experts FFN on salient rows (softmax top-k router + expert-grouped tcgen05 GEMMs)
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Router: for row m < min(num_rows, *num_rows_dev) of x[idx[m]] (idx null = identity) the fp32 logits
+ * x . router_weight^T, softmax over the experts, the top_k probabilities (optionally renormalised to
+ * sum 1; rounded to bf16 as the reference hands them on) and their expert ids, best first.
+ * router_weight: bf16 [num_experts, hidden]; topk_weights: fp32 [num_rows, top_k]; topk_ids: int32.
+ * ref: dyllm/model_executor/layers/fused_moe.py:375-407 (moe_gate), lladamoe.py:90-91. */
+int dyllm_moe_route(const void* x, int x_rows, int hidden, int64_t ldx, const int32_t* idx, int num_rows,
+                    const int32_t* num_rows_dev, const void* router_weight, int num_experts, int top_k,
+                    int renormalize, float* topk_weights, int32_t* topk_ids, void* stream);
+
+/* Bytes of workspace dyllm_moe_ffn needs. */
+size_t dyllm_moe_ffn_workspace_bytes(int max_rows, int top_k, int num_local_experts, int hidden, int inter);
+
+/* out[map[m]] = sum over the slots j of row m whose expert e = topk_ids[m, j] - expert_start is local
+ * (0 <= e < num_local_experts) of  topk_weights[m, j] * down_e( silu(x Wg_e^T) * (x Wu_e^T) ),
+ * x = x[idx[m]].  w1: bf16 [num_local_experts, 2 * inter, hidden] (gate rows first), w2: bf16
+ * [num_local_experts, hidden, inter].  Rows without a local expert get zeros.  The (row, slot) pairs are
+ * grouped by expert on the device, each group padded to 128-row tiles; the routing weight is applied
+ * in the down projection's epilogue and the slot sum runs in fp32 in slot order.  With
+ * expert_start = 0 and all experts local this is the reference's fused_experts; a contiguous expert
+ * range gives one rank's share under expert parallelism (the caller all-reduces the outputs).
+ * ref: dyllm/model_executor/layers/fused_moe.py:37-85,269-335 (moe_align_block_size, fused_experts),
+ *      dyllm/model_executor/models/lladamoe.py:107-142 (expert-parallel selection). */
+int dyllm_moe_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int32_t* idx, int num_rows,
+                  const int32_t* num_rows_dev, int rows_hint, const float* topk_weights, const int32_t* topk_ids,
+                  int top_k, const void* w1, const void* w2, int num_local_experts, int expert_start, int inter,
+                  void* out, int64_t ldo, const int32_t* out_row_map, void* workspace, size_t workspace_bytes,
+                  void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Row-wise kernels around the path (every query row, HBM-bound)
