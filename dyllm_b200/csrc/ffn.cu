@@ -14,10 +14,10 @@ constexpr int kMaxSplits = 4;
 
 namespace {
 
-template <int BNH, bool SWIGLU, int A_MODE, int STAGES>
+template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
   using Cfg = GemmCfg<BNH, SWIGLU, STAGES>;
-  auto kernel = gathered_gemm_kernel<BNH, SWIGLU, A_MODE, STAGES>;
+  auto kernel = gathered_gemm_kernel<BNH, SWIGLU, A_MODE, STAGES, MINB>;
   // one flag per kernel instantiation and device: the opt-in shared-memory size is a per-function attribute
   static bool smem_set[64] = {false};
   int dev = 0;
@@ -34,12 +34,12 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
   return check_launch("gathered_gemm");
 }
 
-template <int BNH, bool SWIGLU, int STAGES>
+template <int BNH, bool SWIGLU, int STAGES, int MINB = 1>
 int launch_mode(int a_mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid,
                 cudaStream_t stream) {
   if (a_mode == 0)
-    return launch_one<BNH, SWIGLU, 0, STAGES>(ta, tb, p, grid, stream);
-  return launch_one<BNH, SWIGLU, 1, STAGES>(ta, tb, p, grid, stream);
+    return launch_one<BNH, SWIGLU, 0, STAGES, MINB>(ta, tb, p, grid, stream);
+  return launch_one<BNH, SWIGLU, 1, STAGES, MINB>(ta, tb, p, grid, stream);
 }
 
 // compact[m] = x[idx[m]] for the live rows; one warp per row, 16-byte accesses.
@@ -102,6 +102,7 @@ splitk_reduce_kernel(const float* __restrict__ partial, int splits, int split_ro
 struct Plan {
   int tile_n;
   int splits;
+  bool two_per_sm;   // narrow tiles, half-depth pipeline, two CTAs per SM (weight-streaming regime)
   dim3 grid;
 };
 
@@ -116,11 +117,13 @@ Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_
     tile_n = (n % 128 == 0 && mt_h * (n / 128) >= sms * 3 / 4) ? 128 : 64;
   plan.tile_n = tile_n;
   const int n_tiles = n / tile_n;
+  plan.two_per_sm = tile_n == 64 && mt_h <= 2;
+  const int slots = plan.two_per_sm ? 2 * sms : sms;
   plan.splits = 1;
   if (!swiglu && can_split && h <= kSplitRows) {
     const int ctas = mt_h * n_tiles;
-    if (ctas * 2 <= sms) {
-      int s = sms / ctas;
+    if (ctas * 2 <= slots) {
+      int s = slots / ctas;
       s = s > kMaxSplits ? kMaxSplits : s;
       const int num_kt = K / kGemmBK;
       s = s > num_kt ? num_kt : s;
@@ -207,10 +210,14 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   if (swiglu) {
     if (plan.tile_n == 128)
       rc = launch_mode<128, true, 4>(a_mode, ta, tb, p, plan.grid, stream);
+    else if (plan.two_per_sm)
+      rc = launch_mode<64, true, 3, 2>(a_mode, ta, tb, p, plan.grid, stream);
     else
       rc = launch_mode<64, true, 6>(a_mode, ta, tb, p, plan.grid, stream);
   } else if (plan.tile_n == 128) {
     rc = launch_mode<128, false, 6>(a_mode, ta, tb, p, plan.grid, stream);
+  } else if (plan.two_per_sm) {
+    rc = launch_mode<64, false, 4, 2>(a_mode, ta, tb, p, plan.grid, stream);
   } else {
     rc = launch_mode<64, false, 8>(a_mode, ta, tb, p, plan.grid, stream);
   }

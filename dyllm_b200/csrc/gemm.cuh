@@ -67,8 +67,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int BNH, bool SWIGLU, int A_MODE, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// MINB = 2 (with half the pipeline depth) lets two CTAs share an SM: used when few row tiles are live and
+// the kernel is bound by streaming the weights, so that every SM has loads in flight in a single wave.
+template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB>
+__global__ void __launch_bounds__(kGemmThreads, MINB)
 gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const GemmParams p) {
   using Cfg = GemmCfg<BNH, SWIGLU, STAGES>;
