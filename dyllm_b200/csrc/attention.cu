@@ -13,9 +13,10 @@
 // A second small kernel adds the per-head partials in head order (run-to-run identical results),
 // overwrites the salient query rows with the exactly attended rows and writes the threshold mask.
 //
-// One CTA = (sequence, query head, 128 query rows); 6 warps: TMA producer, MMA issuer, 4 softmax warps.
-// 96 KB of shared memory and 256 tensor-memory columns per CTA, so two CTAs share an SM and one
-// CTA's tensor-core work overlaps the other's exponentials.
+// One CTA = (sequence, query head, 128 query rows); 10 warps: TMA producer, MMA issuer, 8 softmax warps
+// (two per 32-row lane quarter, each taking half of the columns).  96 KB of shared memory and 256
+// tensor-memory columns per CTA, so two CTAs share an SM and one CTA's tensor-core work overlaps the
+// other's exponentials.
 #include "common.cuh"
 
 namespace dyllm {
@@ -25,7 +26,7 @@ namespace {
 constexpr int kD = 128;          // head dimension
 constexpr int kBQ = 128;         // query rows per CTA
 constexpr int kBKeys = 128;      // keys per tile
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;          // TMA producer warp, MMA warp, eight softmax warps
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one [128][128] bf16 tile = two [128][64] swizzled halves
 constexpr uint32_t kHalfBytes = 128 * 64 * 2;
 constexpr uint32_t kAttnSmem = 3 * kTileBytes + 1024;
@@ -107,23 +108,26 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], b_full, p_full, pv_done, a_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int s_src[128];        // source row of each gather slot (-1 = none)
+  __shared__ float2 s_ml[2][128];   // (max, sum) of the two column halves of each query row
+  __shared__ float4 s_st[128];      // statistics of the second half of each row
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    mbar_init(&q_full, EXACT ? 128 : 1);
+    mbar_init(&q_full, EXACT ? 256 : 1);
     mbar_init(&k_full[0], 1);
     mbar_init(&k_full[1], 1);
     mbar_init(&k_empty[0], 1);
     mbar_init(&k_empty[1], 1);
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(&s_empty[0], 128);
-    mbar_init(&s_empty[1], 128);
-    mbar_init(&b_full, EXACT ? 1 : 128);
-    mbar_init(&p_full, 128);
+    mbar_init(&s_empty[0], 256);
+    mbar_init(&s_empty[1], 256);
+    mbar_init(&b_full, EXACT ? 1 : 256);
+    mbar_init(&p_full, 256);
     mbar_init(&pv_done, 1);
     mbar_init(&a_done, 1);
     fence_mbar_init();
@@ -244,36 +248,54 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- softmax / gather / epilogue
+    // Eight warps: two warps share each tensor-memory lane quarter (= 32 query rows) and split the
+    // columns of every tile in halves, so a thread owns one query row and 64 of 128 columns.
+    const int sw = warp - 2;                 // 0..7
     const int qd = warp & 3;                 // tensor-memory lane quarter of this warp
-    const int row = qd * 32 + lane;          // query row inside the tile, also the gather slot
+    const int half = sw >> 2;                // which 64 columns of a tile / of the head dimension
+    const int row = qd * 32 + lane;          // query row inside the tile
+    const int st_tid = sw * 32 + lane;       // 0..255 among the softmax threads
     const uint32_t t_lane = static_cast<uint32_t>(qd * 32) << 16;
+    const int col0 = half * 64;
     const float c = p.scale_log2;
     float m = kNegBig, l = 0.f;
     DYLLM_TRACE(0);
 
     if (!EXACT && q0 + row < q_end) {
-      // bring this thread's C_old row (256 bytes) into L2 now; the epilogue reads it much later
-      const char* crow = reinterpret_cast<const char*>(p.c_old + (static_cast<int64_t>(q0 + row) * p.H + h) * kD);
+      // bring this thread's half of the C_old row (128 bytes) into L2 now; the epilogue reads it much later
+      const char* crow =
+          reinterpret_cast<const char*>(p.c_old + (static_cast<int64_t>(q0 + row) * p.H + h) * kD + col0);
       asm volatile("prefetch.global.L2 [%0];" ::"l"(crow));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(crow + 128));
     }
-
+    // source rows of the first gather (salient key rows, or the query rows of the EXACT variant)
+    if (half == 0) {
+      int src = -1;
+      if (EXACT) {
+        if (q0 + row < q_end)
+          src = p.idx_q[sal_begin + q0 + row];
+      } else if (row < n_sal) {
+        src = p.idx_k[sal_begin + row];
+      }
+      s_src[row] = src;
+    }
     if (EXACT) {
-      // gather this thread's query row (or zeros past the list) into the swizzled Q tile
-      const bool have = q0 + row < q_end;
-      const int64_t qrow = have ? p.idx_q[sal_begin + q0 + row] : 0;
-      const uint4* qsrc = reinterpret_cast<const uint4*>(p.q + (qrow * p.H + h) * kD);
+      // cooperative gather of the query rows (zeros past the list) into the swizzled Q tile
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const uint4 qv = have ? __ldg(qsrc + ch) : zero;
-        *reinterpret_cast<uint4*>(q_smem + (ch >> 3) * kHalfBytes + sw128_offset(row, ch & 7)) = qv;
+      for (int it = 0; it < 8; ++it) {
+        const int item = it * 256 + st_tid;
+        const int r = item >> 4, ch = item & 15;
+        const int src = s_src[r];
+        const uint4 qv = src >= 0
+            ? __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(src) * p.H + h) * kD) + ch) : zero;
+        *reinterpret_cast<uint4*>(q_smem + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = qv;
       }
       fence_proxy_async_smem();
       mbar_arrive(&q_full);
     }
 
-    // pass A: running maximum and sum over all keys
+    // pass A: running maximum and sum over this thread's half of the columns of every key tile
     int uses[2] = {0, 0};
     for (int kt = 0; kt < num_kt; ++kt) {
       const int sb = kt & 1;
@@ -285,11 +307,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         DYLLM_TRACE(7);
       const int valid = len_k - kt * kBKeys;   // keys of this tile that belong to the sequence
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBKeys; c0 += 32) {
+      for (int cc = 0; cc < 64; cc += 32) {
+        const int c0 = col0 + cc;
         uint32_t sr[32];
         tmem_ld_32x32(tmem_s + t_lane + c0, sr);
         tmem_ld_wait();
-        if (c0 + 32 >= kBKeys) {  // last chunk read: the MMA warp may overwrite this S buffer
+        if (cc == 32) {  // last chunk read: the MMA warp may overwrite this S buffer
           tc_fence_before_sync();
           mbar_arrive(&s_empty[sb]);
         }
@@ -317,43 +340,53 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         m = m_new;
       }
     }
+    // merge the two column halves of each row: m = max, l rescaled to the common maximum
+    s_ml[half][row] = make_float2(m, l);
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    {
+      const float2 other = s_ml[half ^ 1][row];
+      const float m_all = fmaxf(m, other.x);
+      l = l * ex2((m - m_all) * c) + other.y * ex2((other.x - m_all) * c);
+      m = m_all;
+    }
 
-    // pass B: salient keys
+    // pass B: salient keys (EXACT: all keys again, with their values)
     DYLLM_TRACE(1);
     const float mc = m * c;
     for (int st = 0; st < num_st; ++st) {
       // The buffers are free for tile 0 once the last Q K^T product is complete: s_full of the last
       // key tile was observed above and is committed after every earlier MMA.  Later tiles wait for the
       // previous P dV product.
-      if (!EXACT && st > 0)
+      if (!EXACT && st > 0) {
         mbar_wait(&pv_done, (st - 1) & 1, &abort_flag, p.status_word, 308);
+        if (half == 0) {
+          const int j = st * kBKeys + row;
+          s_src[row] = j < n_sal ? p.idx_k[sal_begin + j] : -1;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      }
       const int n_tile = min(kBKeys, (EXACT ? len_k : n_sal) - st * kBKeys);
-      // gather slot `row`: K row and dV row of one salient key, or zeros
       if (!EXACT) {
-        const bool have = row < n_tile;
-        const int64_t krow = have ? p.idx_k[sal_begin + st * kBKeys + row] : 0;
-        const uint4* ksrc = reinterpret_cast<const uint4*>(p.k + (krow * p.Hkv + hk) * kD);
-        const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + st * kBKeys + (have ? row : 0)) : krow;
-        const uint4* vsrc = reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD);
+        // cooperative gather: 128 slots x 16 chunks of the K rows and of the dV rows, zeros past the list
         const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
-          const uint4 kv = have ? __ldg(ksrc + ch) : zero;
-          *reinterpret_cast<uint4*>(kv_smem0 + (ch >> 3) * kHalfBytes + sw128_offset(row, ch & 7)) = kv;
-        }
-        if (v_mn_major) {
-#pragma unroll
-          for (int ch = 0; ch < 16; ++ch) {
-            const uint4 vv = have ? __ldg(vsrc + ch) : zero;
-            *reinterpret_cast<uint4*>(kv_smem1 + (ch >> 3) * kHalfBytes + sw128_offset(row, ch & 7)) = vv;
-          }
-        } else {
-          // transposed tile [d][key]: element (d, key = row)
-          uint8_t* base = kv_smem1 + (row >> 6) * kHalfBytes + ((row & 7) << 1);
-          const uint32_t key_chunk = (row & 63) >> 3;
-#pragma unroll
-          for (int ch = 0; ch < 16; ++ch) {
-            const uint4 vv = have ? __ldg(vsrc + ch) : zero;
+        for (int it = 0; it < 8; ++it) {
+          const int item = it * 256 + st_tid;
+          const int r = item >> 4, ch = item & 15;
+          const int src = s_src[r];
+          const bool have = src >= 0;
+          const uint4 kv = have
+              ? __ldg(reinterpret_cast<const uint4*>(p.k + (static_cast<int64_t>(src) * p.Hkv + hk) * kD) + ch) : zero;
+          *reinterpret_cast<uint4*>(kv_smem0 + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = kv;
+          const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + st * kBKeys + r) : src;
+          const uint4 vv = have
+              ? __ldg(reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD) + ch) : zero;
+          if (v_mn_major) {
+            *reinterpret_cast<uint4*>(kv_smem1 + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = vv;
+          } else {
+            // transposed tile [d][key]: element (d, key = r)
+            uint8_t* base = kv_smem1 + (r >> 6) * kHalfBytes + ((r & 7) << 1);
+            const uint32_t key_chunk = (r & 63) >> 3;
             const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -365,18 +398,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         fence_proxy_async_smem();
         mbar_arrive(&b_full);
       }
-      // P = exp2(S2 * c - m * c) for the live columns
+      // P = exp2(S2 * c - m * c) for the live columns of this thread's half
       DYLLM_TRACE(2);
       const int use = uses[0]++;
       mbar_wait(&s_full[0], use & 1, &abort_flag, p.status_word, 309);
-      DYLLM_TRACE(3);
       tc_fence_after_sync();
+      DYLLM_TRACE(3);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBKeys; c0 += 32) {
+      for (int cc = 0; cc < 64; cc += 32) {
+        const int c0 = col0 + cc;
         uint32_t sr[32];
         tmem_ld_32x32(tmem_s0 + t_lane + c0, sr);
         tmem_ld_wait();
-        if (c0 + 32 >= kBKeys) {
+        if (cc == 32) {
           tc_fence_before_sync();
           mbar_arrive(&s_empty[0]);
         }
@@ -405,26 +439,25 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     DYLLM_TRACE(5);
 
-    // epilogue: new = old + O / rowsum; bf16 store; partial statistics of this head.  The
-    // tensor-memory loads are warp-collective, so every lane issues them; only the global-memory
-    // traffic is predicated on the row being inside the sequence.
+    // epilogue: new = old + O / rowsum for this thread's 64 of the 128 head dimensions; bf16 store;
+    // partial statistics of this head.  The tensor-memory loads are warp-collective, so every lane issues
+    // them; only the global-memory traffic is predicated on the row being inside the sequence.
     const int r = q0 + row;
     const bool live = r < q_end;
     const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-    const int64_t off = (static_cast<int64_t>((live ? r : q0) + (EXACT ? sal_begin : 0)) * p.H + h) * kD;
+    const int64_t off = (static_cast<int64_t>((live ? r : q0) + (EXACT ? sal_begin : 0)) * p.H + h) * kD + col0;
     const __nv_bfloat16* cold = EXACT ? nullptr : p.c_old + off;
     __nv_bfloat16* dst = (EXACT ? p.o_sal : p.out) + off;
     float dot = 0.f, nn = 0.f, no = 0.f;
-    // the whole C_old row in one batch of independent loads
-    uint4 old_row[16];
+    uint4 old_row[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
+    for (int j = 0; j < 8; ++j)
       old_row[j] = (EXACT || !live) ? make_uint4(0, 0, 0, 0) : __ldg(reinterpret_cast<const uint4*>(cold) + j);
 #pragma unroll
-    for (int c0 = 0; c0 < kD; c0 += 32) {
+    for (int cc = 0; cc < 64; cc += 32) {
       uint32_t orr[32];
       if (num_st > 0) {
-        tmem_ld_32x32(tmem_o + t_lane + c0, orr);
+        tmem_ld_32x32(tmem_o + t_lane + col0 + cc, orr);
         tmem_ld_wait();
       } else {
 #pragma unroll
@@ -432,7 +465,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           orr[i] = 0u;
       }
       if (live) {
-        const uint4* oldv = old_row + c0 / 8;
+        const uint4* oldv = old_row + cc / 8;
         const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(oldv);
         uint32_t pk[16];
 #pragma unroll
@@ -451,14 +484,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          reinterpret_cast<uint4*>(dst + c0)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          reinterpret_cast<uint4*>(dst + cc)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
       }
     }
-    if (live && !EXACT) {
-      float* ps = p.partial + (static_cast<int64_t>(h) * p.Tq + r) * 3;
-      ps[0] = dot;
-      ps[1] = nn;
-      ps[2] = no;
+    if (!EXACT) {
+      // the two halves of a row add their statistics in a fixed order (half 0 + half 1)
+      if (half == 1)
+        s_st[row] = make_float4(dot, nn, no, 0.f);
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0 && live) {
+        const float4 o = s_st[row];
+        float* ps = p.partial + (static_cast<int64_t>(h) * p.Tq + r) * 3;
+        ps[0] = dot + o.x;
+        ps[1] = nn + o.y;
+        ps[2] = no + o.z;
+      }
     }
     DYLLM_TRACE(6);
   }

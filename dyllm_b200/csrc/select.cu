@@ -94,8 +94,7 @@ __global__ void cosine_mask_kernel(const float* __restrict__ stats, uint8_t* __r
 // salient_select: warp-ballot flags + block scan + decoupled look-back across tiles
 // ----------------------------------------------------------------------------------------------
 constexpr int kSelWarps = 8;
-constexpr int kSelChunks = 8;                                // 32-row chunks per warp
-constexpr int kSelTileRows = kSelWarps * kSelChunks * 32;    // 2048 rows per tile
+constexpr int kSelTileRowsSmall = kSelWarps * 2 * 128;   // 2048 rows per tile (workspace is sized for these)
 constexpr uint32_t kLookbackSpinLimit = 1u << 24;
 
 // Workspace layout: [0] ticket counter (uint32), [1] padding, then one 64-bit descriptor per tile:
@@ -118,16 +117,26 @@ __device__ __forceinline__ int lower_bound_i32(const int32_t* a, int n, int key)
   return lo;
 }
 
+// Each thread owns 4 consecutive rows of a 128-row group (48 contiguous bytes = three 16-byte loads),
+// so a warp reads 1536 contiguous bytes per group; a warp takes SUPER groups, a tile 8 * SUPER * 128
+// rows.  Flags become a 4-bit nibble per thread; positions come from a warp prefix sum of the nibble
+// popcounts, a block scan over the warps and a decoupled look-back over the tiles (32 predecessors per
+// step).  The prefix front moves a bounded number of tiles per microsecond, so large inputs use large
+// tiles (SUPER = 8) and small inputs small ones (SUPER = 2) for parallelism.
+template <int SUPER>
 __global__ void __launch_bounds__(kSelWarps * 32)
 salient_select_kernel(const float* __restrict__ stats, int rows, float threshold,
                       const int32_t* __restrict__ cu_seqlens_q, int batch, const int32_t* __restrict__ cu_promptlens,
                       int64_t* __restrict__ idx_out, int32_t* __restrict__ idx32_out, int64_t* __restrict__ idx_k_out,
                       int32_t* __restrict__ cu_salientlens_out, int32_t* __restrict__ count_out,
                       uint8_t* __restrict__ mask_out, SelectWorkspace* ws, int* status_word) {
-  __shared__ uint32_t s_masks[kSelWarps * kSelChunks];
+  constexpr int kTileRows = kSelWarps * SUPER * 128;
+  __shared__ int s_excl[kSelWarps * SUPER * 32];       // per thread and group: flags of the tile before its rows
+  __shared__ uint8_t s_nib[kSelWarps * SUPER * 32];    // per thread and group: its 4 flags
   __shared__ int s_warp_count[kSelWarps];
   __shared__ int s_tile;
   __shared__ int s_tile_prefix;
+  __shared__ int s_b_range[2];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -136,73 +145,120 @@ salient_select_kernel(const float* __restrict__ stats, int rows, float threshold
     s_tile = static_cast<int>(atomicAdd(&ws->ticket, 1u));
   __syncthreads();
   const int tile = s_tile;
-  const int tile_row0 = tile * kSelTileRows;
+  const int tile_row0 = tile * kTileRows;
+  const int tile_row1 = min(tile_row0 + kTileRows, rows);
+  // sequence boundaries inside this tile: two binary searches by two threads, under the loads below
+  if (threadIdx.x == 32)
+    s_b_range[0] = lower_bound_i32(cu_seqlens_q, batch + 1, tile_row0);
+  if (threadIdx.x == 64)
+    s_b_range[1] = lower_bound_i32(cu_seqlens_q, batch + 1, tile_row1);
 
-  // 1. flags: lane = row inside a 32-row chunk, ballot gives the chunk's bit mask
-  uint32_t my_masks[kSelChunks];
+  // 1. loads (all issued before any use), flags, warp-level exclusive positions
+  float4 v[SUPER][3];
+  int row0[SUPER];
+#pragma unroll
+  for (int g = 0; g < SUPER; ++g) {
+    row0[g] = tile_row0 + (warp * SUPER + g) * 128 + lane * 4;
+    if (row0[g] + 3 < rows) {
+      const float4* src = reinterpret_cast<const float4*>(stats + static_cast<int64_t>(row0[g]) * 3);
+      v[g][0] = __ldg(src);
+      v[g][1] = __ldg(src + 1);
+      v[g][2] = __ldg(src + 2);
+    } else {
+      float t[12];
+#pragma unroll
+      for (int i = 0; i < 12; ++i) {
+        const int64_t e = static_cast<int64_t>(row0[g]) * 3 + i;
+        t[i] = e < static_cast<int64_t>(rows) * 3 ? __ldg(stats + e) : 0.f;
+      }
+      v[g][0] = make_float4(t[0], t[1], t[2], t[3]);
+      v[g][1] = make_float4(t[4], t[5], t[6], t[7]);
+      v[g][2] = make_float4(t[8], t[9], t[10], t[11]);
+    }
+  }
+  uint32_t nib[SUPER];
+  int excl[SUPER];   // flags of this warp that precede this thread's first row of the group
   int warp_count = 0;
 #pragma unroll
-  for (int c = 0; c < kSelChunks; ++c) {
-    const int r = tile_row0 + (warp * kSelChunks + c) * 32 + lane;
-    bool flag = false;
-    if (r < rows) {
-      const float* s = stats + static_cast<int64_t>(r) * 3;
-      flag = below_threshold(__ldg(s), __ldg(s + 1), __ldg(s + 2), threshold);
-      if (mask_out)
-        mask_out[r] = flag ? 1 : 0;
+  for (int g = 0; g < SUPER; ++g) {
+    const float4 a = v[g][0], b = v[g][1], c = v[g][2];
+    uint32_t f = 0;
+    if (row0[g] + 0 < rows && below_threshold(a.x, a.y, a.z, threshold)) f |= 1u;
+    if (row0[g] + 1 < rows && below_threshold(a.w, b.x, b.y, threshold)) f |= 2u;
+    if (row0[g] + 2 < rows && below_threshold(b.z, b.w, c.x, threshold)) f |= 4u;
+    if (row0[g] + 3 < rows && below_threshold(c.y, c.z, c.w, threshold)) f |= 8u;
+    nib[g] = f;
+    if (mask_out) {
+      if (row0[g] + 3 < rows) {
+        *reinterpret_cast<uchar4*>(mask_out + row0[g]) = make_uchar4(f & 1u, (f >> 1) & 1u, (f >> 2) & 1u, (f >> 3) & 1u);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (row0[g] + j < rows)
+            mask_out[row0[g] + j] = (f >> j) & 1u;
+      }
     }
-    const uint32_t m = __ballot_sync(0xffffffffu, flag);
-    my_masks[c] = m;
-    warp_count += __popc(m);
+    const int cnt = __popc(f);
+    int incl = cnt;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off)
+        incl += o;
+    }
+    excl[g] = warp_count + incl - cnt;
+    warp_count += __shfl_sync(0xffffffffu, incl, 31);
   }
   if (lane == 0)
     s_warp_count[warp] = warp_count;
-  if (lane < kSelChunks) {
-    uint32_t m = 0;
-#pragma unroll
-    for (int c = 0; c < kSelChunks; ++c)
-      m = (lane == c) ? my_masks[c] : m;
-    s_masks[warp * kSelChunks + lane] = m;
-  }
   __syncthreads();
 
-  // 2. tile aggregate, then exclusive prefix over earlier tiles (decoupled look-back by warp 0)
+  // 2. tile aggregate, then exclusive prefix over earlier tiles: decoupled look-back by warp 0, whose
+  // 32 lanes inspect 32 predecessors at a time
   if (warp == 0) {
-    int v = lane < kSelWarps ? s_warp_count[lane] : 0;
+    int t = lane < kSelWarps ? s_warp_count[lane] : 0;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1)
-      v += __shfl_xor_sync(0xffffffffu, v, off);
-    const int aggregate = v;
-    int exclusive = 0;
+      t += __shfl_xor_sync(0xffffffffu, t, off);
+    const int aggregate = t;
+    volatile unsigned long long* tiles = ws->tiles;
     if (lane == 0) {
-      volatile unsigned long long* tiles = ws->tiles;
-      if (tile == 0) {
-        tiles[0] = (2ull << 32) | static_cast<unsigned int>(aggregate);
-      } else {
-        tiles[tile] = (1ull << 32) | static_cast<unsigned int>(aggregate);
-        __threadfence();
-        int look = tile - 1;
-        uint32_t spins = 0;
-        bool gave_up = false;
-        while (look >= 0) {
-          const unsigned long long d = tiles[look];
-          const unsigned int state = static_cast<unsigned int>(d >> 32) & 3u;
-          if (state == 0) {
-            if (++spins > kLookbackSpinLimit) {
-              gave_up = true;
-              break;
-            }
-            continue;
-          }
-          exclusive += static_cast<int>(static_cast<unsigned int>(d));
-          if (state == 2)
-            break;
-          --look;
+      tiles[tile] = ((tile == 0 ? 2ull : 1ull) << 32) | static_cast<unsigned int>(aggregate);
+      __threadfence();
+    }
+    int exclusive = 0;
+    bool gave_up = false;
+    for (int base = tile - 1; base >= 0 && !gave_up; base -= 32) {
+      const int look = base - lane;
+      unsigned long long d = 2ull << 32;   // before the first tile: inclusive prefix 0
+      uint32_t spins = 0;
+      for (;;) {
+        if (look >= 0)
+          d = tiles[look];
+        const bool ready = ((d >> 32) & 3ull) != 0;
+        if (__all_sync(0xffffffffu, ready))
+          break;
+        if (++spins > kLookbackSpinLimit) {
+          gave_up = true;
+          break;
         }
-        if (gave_up && status_word)
-          atomicCAS(status_word, 0, 101);
-        tiles[tile] = (2ull << 32) | static_cast<unsigned int>(exclusive + aggregate);
       }
+      gave_up = __any_sync(0xffffffffu, gave_up);
+      const uint32_t inclusive_mask = __ballot_sync(0xffffffffu, ((d >> 32) & 3ull) == 2);
+      const int first = inclusive_mask ? __ffs(inclusive_mask) - 1 : 31;   // nearest predecessor with a full prefix
+      int contrib = lane <= first ? static_cast<int>(static_cast<unsigned int>(d)) : 0;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+        contrib += __shfl_xor_sync(0xffffffffu, contrib, off);
+      exclusive += contrib;
+      if (inclusive_mask)
+        break;
+    }
+    if (lane == 0) {
+      if (gave_up && status_word)
+        atomicCAS(status_word, 0, 101);
+      if (tile != 0)
+        tiles[tile] = (2ull << 32) | static_cast<unsigned int>(exclusive + aggregate);
       __threadfence();
       s_tile_prefix = exclusive;
     }
@@ -215,37 +271,37 @@ salient_select_kernel(const float* __restrict__ stats, int rows, float threshold
   for (int w = 0; w < warp; ++w)
     base += s_warp_count[w];
 #pragma unroll
-  for (int c = 0; c < kSelChunks; ++c) {
-    const uint32_t m = my_masks[c];
-    if ((m >> lane) & 1u) {
-      const int r = tile_row0 + (warp * kSelChunks + c) * 32 + lane;
-      const int pos = base + __popc(m & ((1u << lane) - 1u));
-      idx_out[pos] = r;
-      if (idx32_out)
-        idx32_out[pos] = r;
-      if (idx_k_out) {
-        // sequence b with cu_q[b] <= r < cu_q[b + 1]
-        const int b = lower_bound_i32(cu_seqlens_q, batch + 1, r + 1) - 1;
-        idx_k_out[pos] = static_cast<int64_t>(r) + cu_promptlens[b + 1];
+  for (int g = 0; g < SUPER; ++g) {
+    const int slot = (warp * SUPER + g) * 32 + lane;
+    s_excl[slot] = base + excl[g] - tile_prefix;   // relative to the tile
+    s_nib[slot] = static_cast<uint8_t>(nib[g]);
+    int pos = base + excl[g];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if ((nib[g] >> j) & 1u) {
+        const int r = row0[g] + j;
+        idx_out[pos] = r;
+        if (idx32_out)
+          idx32_out[pos] = r;
+        if (idx_k_out) {
+          // sequence b with cu_q[b] <= r < cu_q[b + 1]
+          const int b = lower_bound_i32(cu_seqlens_q, batch + 1, r + 1) - 1;
+          idx_k_out[pos] = static_cast<int64_t>(r) + cu_promptlens[b + 1];
+        }
+        ++pos;
       }
     }
-    base += __popc(m);
   }
+  __syncthreads();
 
   // 4. per-sequence prefix counts for the sequence boundaries that fall inside this tile
-  const int tile_row1 = min(tile_row0 + kSelTileRows, rows);
-  const int b_lo = lower_bound_i32(cu_seqlens_q, batch + 1, tile_row0);
-  const int b_hi = lower_bound_i32(cu_seqlens_q, batch + 1, tile_row1);
+  const int b_lo = s_b_range[0];
+  const int b_hi = s_b_range[1];
   for (int b = b_lo + threadIdx.x; b < b_hi; b += blockDim.x) {
-    const int local = cu_seqlens_q[b] - tile_row0;  // in [0, kSelTileRows)
-    int cnt = tile_prefix;
-    const int full_words = local >> 5;
-    for (int w = 0; w < full_words; ++w)
-      cnt += __popc(s_masks[w]);
-    const int rem = local & 31;
-    if (rem)
-      cnt += __popc(s_masks[full_words] & ((1u << rem) - 1u));
-    cu_salientlens_out[b] = cnt;
+    const int local = cu_seqlens_q[b] - tile_row0;  // in [0, kTileRows)
+    const int slot = local >> 2;                    // owner thread slot: 4 rows each, in row order
+    const int j = local & 3;
+    cu_salientlens_out[b] = tile_prefix + s_excl[slot] + __popc(static_cast<uint32_t>(s_nib[slot]) & ((1u << j) - 1u));
   }
   if (tile_row1 == rows) {  // last tile: boundaries at or beyond the end, and the total
     int total = tile_prefix;
@@ -289,7 +345,7 @@ __global__ void fused_offset_kernel(const int32_t* __restrict__ idxs, const int3
 }  // namespace
 
 size_t select_workspace_bytes(int rows) {
-  const int tiles = rows > 0 ? cdiv_i(rows, kSelTileRows) : 1;
+  const int tiles = rows > 0 ? cdiv_i(rows, kSelTileRowsSmall) : 1;
   return sizeof(unsigned int) * 2 + sizeof(unsigned long long) * static_cast<size_t>(tiles);
 }
 
@@ -302,12 +358,17 @@ int launch_salient_select(const float* stats, int rows, float threshold, const i
     select_empty_kernel<<<1, 128, 0, stream>>>(cu_salientlens_out, count_out, batch);
     return check_launch("salient_select(empty)");
   }
-  const int tiles = cdiv_i(rows, kSelTileRows);
   if (cudaMemsetAsync(workspace, 0, select_workspace_bytes(rows), stream) != cudaSuccess)
     return set_error(DYLLM_ERR_CUDA, "salient_select: clearing the workspace failed");
-  salient_select_kernel<<<tiles, kSelWarps * 32, 0, stream>>>(
-      stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
-      cu_salientlens_out, count_out, mask_out, static_cast<SelectWorkspace*>(workspace), device_status_word());
+  SelectWorkspace* w = static_cast<SelectWorkspace*>(workspace);
+  if (rows > 64 * 1024)
+    salient_select_kernel<8><<<cdiv_i(rows, kSelWarps * 8 * 128), kSelWarps * 32, 0, stream>>>(
+        stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
+        cu_salientlens_out, count_out, mask_out, w, device_status_word());
+  else
+    salient_select_kernel<2><<<cdiv_i(rows, kSelTileRowsSmall), kSelWarps * 32, 0, stream>>>(
+        stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
+        cu_salientlens_out, count_out, mask_out, w, device_status_word());
   return check_launch("salient_select");
 }
 
@@ -322,7 +383,7 @@ int launch_salient_select(const float* stats, int rows, float threshold, const i
 // ----------------------------------------------------------------------------------------------
 constexpr int kStaticSelectMaxRows = 4 * 1024 * 1024;
 constexpr size_t kStaticSelectBytes =
-    sizeof(unsigned int) * 2 + sizeof(unsigned long long) * (kStaticSelectMaxRows / kSelTileRows);
+    sizeof(unsigned int) * 2 + sizeof(unsigned long long) * (kStaticSelectMaxRows / kSelTileRowsSmall);
 static __device__ __align__(256) unsigned char g_static_select_scratch[kStaticSelectBytes];
 
 namespace {
@@ -394,6 +455,8 @@ int dyllm_salient_select(const float* stats, int rows, float threshold, const in
                 select_workspace_bytes(rows));
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 7) == 0, DYLLM_ERR_INVALID_ARGUMENT,
                 "salient_select: workspace must be 8-byte aligned");
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(stats) & 15) == 0 && (reinterpret_cast<uintptr_t>(mask_out) & 3) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "salient_select: stats must be 16-byte and mask_out 4-byte aligned");
   return launch_salient_select(stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out,
                                idx_k_out, cu_salientlens_out, count_out, mask_out, workspace,
                                static_cast<cudaStream_t>(stream));
@@ -416,6 +479,8 @@ int dyllm_salient_select_static(const float* stats, int rows, float threshold, c
   DYLLM_REQUIRE(rows == 0 || (stats && idx_out), DYLLM_ERR_INVALID_ARGUMENT, "salient_select_static: null pointer");
   DYLLM_REQUIRE(!idx_k_out || cu_promptlens, DYLLM_ERR_INVALID_ARGUMENT,
                 "salient_select_static: idx_k_out needs cu_promptlens");
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(stats) & 15) == 0 && (reinterpret_cast<uintptr_t>(mask_out) & 3) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "salient_select_static: stats must be 16-byte and mask_out 4-byte aligned");
   void* scratch = nullptr;
   const int rc = static_select_scratch(&scratch);
   if (rc != DYLLM_OK)
