@@ -14,10 +14,10 @@ constexpr int kMaxSplits = 4;
 
 namespace {
 
-template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB>
+template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB, int MT = 1>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-  using Cfg = GemmCfg<BNH, SWIGLU, STAGES>;
-  auto kernel = gathered_gemm_kernel<BNH, SWIGLU, A_MODE, STAGES, MINB>;
+  using Cfg = GemmCfg<BNH, SWIGLU, STAGES, MT>;
+  auto kernel = gathered_gemm_kernel<BNH, SWIGLU, A_MODE, STAGES, MINB, MT>;
   // one flag per kernel instantiation and device: the opt-in shared-memory size is a per-function attribute
   static bool smem_set[64] = {false};
   int dev = 0;
@@ -103,12 +103,13 @@ struct Plan {
   int tile_n;
   int splits;
   bool two_per_sm;   // narrow tiles, half-depth pipeline, two CTAs per SM (weight-streaming regime)
+  bool tall;         // 256-row tiles (two accumulators per weight tile) for many rows
   dim3 grid;
 };
 
 // Launch shape from the row-count hint: tile width so that the expected tiles fill the SMs, split-K
 // when even the narrow tiles leave most SMs idle, one grid row per expected row tile.
-Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_split) {
+Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_split, bool allow_tall) {
   const int sms = sm_count();
   const int h = (hint > 0 && hint < M) ? hint : M;
   const int mt_h = cdiv_i(h, kGemmBM);
@@ -117,6 +118,8 @@ Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_
     tile_n = (n % 128 == 0 && mt_h * (n / 128) >= sms * 3 / 4) ? 128 : 64;
   plan.tile_n = tile_n;
   const int n_tiles = n / tile_n;
+  // many rows: the 128-row tile is limited by weight traffic from L2; 256-row tiles halve it
+  plan.tall = allow_tall && tile_n == 128 && h > 256 && cdiv_i(h, 2 * kGemmBM) * n_tiles >= sms;
   plan.two_per_sm = tile_n == 64 && mt_h <= 2;
   const int slots = plan.two_per_sm ? 2 * sms : sms;
   plan.splits = 1;
@@ -130,8 +133,9 @@ Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_
       plan.splits = s < 1 ? 1 : s;
     }
   }
-  int m_groups = mt_h;
-  const int mt_all = cdiv_i(M, kGemmBM);
+  const int bm = plan.tall ? 2 * kGemmBM : kGemmBM;
+  int m_groups = cdiv_i(h, bm);
+  const int mt_all = cdiv_i(M, bm);
   m_groups = m_groups > mt_all ? mt_all : m_groups;
   plan.grid = dim3(n_tiles, m_groups < 1 ? 1 : m_groups, plan.splits);
   return plan;
@@ -187,7 +191,8 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
                 "gemm: split column %d must be a multiple of 128 inside (0, %d)", p.split_col, n);
   if (p.M <= 0)
     return DYLLM_OK;
-  const Plan plan = make_plan(swiglu, p.M, rows_hint, n, p.K, tile_n, partial != nullptr);
+  const Plan plan = make_plan(swiglu, p.M, rows_hint, n, p.K, tile_n, partial != nullptr,
+                              a_mode == 0 && !p.tile_expert);
   DYLLM_REQUIRE((plan.tile_n == 64 || plan.tile_n == 128) && n % plan.tile_n == 0, DYLLM_ERR_UNSUPPORTED,
                 "gemm: tile_n %d does not divide N = %d", plan.tile_n, n);
   p.status_word = device_status_word();
@@ -198,7 +203,7 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   CUtensorMap ta, tb;
   int rc;
   if (a_mode == 0)
-    rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, lda, kGemmBM, kGemmBK, true);
+    rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, lda, plan.tall ? 2 * kGemmBM : kGemmBM, kGemmBK, true);
   else
     rc = encode_tmap_2d_bf16(&ta, p.a, p.a_rows, p.K, lda, 1, kGemmBK, true);
   if (rc != DYLLM_OK)
@@ -207,7 +212,12 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   if (rc != DYLLM_OK)
     return rc;
 
-  if (swiglu) {
+  if (plan.tall) {
+    if (swiglu)
+      rc = launch_one<128, true, 0, 3, 1, 2>(ta, tb, p, plan.grid, stream);
+    else
+      rc = launch_one<128, false, 0, 4, 1, 2>(ta, tb, p, plan.grid, stream);
+  } else if (swiglu) {
     if (plan.tile_n == 128)
       rc = launch_mode<128, true, 4>(a_mode, ta, tb, p, plan.grid, stream);
     else if (plan.two_per_sm)

@@ -48,10 +48,14 @@ constexpr int kGemmBM = 128;
 constexpr int kGemmBK = 64;
 constexpr int kGemmThreads = 192;
 
-template <int BNH, bool SWIGLU, int STAGES>
+// MT = 1: 128-row tiles, two accumulators alternate between consecutive row tiles (the epilogue of one
+// tile overlaps the main loop of the next).  MT = 2: 256-row tiles made of two 128-row accumulators that
+// share every weight tile in shared memory, which halves the weight traffic from L2 per flop (the
+// limit at many rows); the epilogue is then not overlapped.
+template <int BNH, bool SWIGLU, int STAGES, int MT = 1>
 struct GemmCfg {
   static constexpr int BN = SWIGLU ? 2 * BNH : BNH;  // UMMA N
-  static constexpr uint32_t A_BYTES = kGemmBM * kGemmBK * 2;
+  static constexpr uint32_t A_BYTES = MT * kGemmBM * kGemmBK * 2;
   static constexpr uint32_t B_BYTES = BN * kGemmBK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + alignment slack
@@ -69,12 +73,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // MINB = 2 (with half the pipeline depth) lets two CTAs share an SM: used when few row tiles are live and
 // the kernel is bound by streaming the weights, so that every SM has loads in flight in a single wave.
-template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB>
+template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, MINB)
 gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const GemmParams p) {
-  using Cfg = GemmCfg<BNH, SWIGLU, STAGES>;
-  constexpr int BM = kGemmBM, BK = kGemmBK, BN = Cfg::BN;
+  using Cfg = GemmCfg<BNH, SWIGLU, STAGES, MT>;
+  constexpr int BM = kGemmBM * MT, BK = kGemmBK, BN = Cfg::BN;
+  static_assert(MT == 1 || A_MODE == 0, "256-row tiles take their rows as one TMA box");
 
   const int n_tile = blockIdx.x;
   const int m_count = p.m_count_dev ? min(*p.m_count_dev, p.M) : p.M;
@@ -169,11 +174,13 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+    constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN, 0, 0);
     int it = 0, ti = 0;
     for (int mt = blockIdx.y; mt * BM < m_count; mt += gridDim.y, ++ti) {
-      const int acc = ti & 1;
-      mbar_wait(&tmem_empty_bar[acc], ((ti >> 1) & 1) ^ 1, &abort_flag, p.status_word, 205);
+      // MT = 1: accumulators alternate; MT = 2: both belong to this tile and barrier 0 guards them
+      const int acc = MT == 1 ? (ti & 1) : 0;
+      const uint32_t use = MT == 1 ? (ti >> 1) : ti;
+      mbar_wait(&tmem_empty_bar[acc], (use & 1) ^ 1, &abort_flag, p.status_word, 205);
       tc_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + acc * BN;
       for (int kt = 0; kt < num_kt; ++kt, ++it) {
@@ -187,8 +194,11 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr, 16, 1024);
           const uint64_t b_desc = umma_smem_desc_sw128(b_addr, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
+          for (int k = 0; k < BK / 16; ++k) {
             umma_ss(tmem_acc, a_desc + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+            if (MT == 2)   // second 128 rows (16 KB further in the A stage) against the same weight tile
+              umma_ss(tmem_acc + BN, a_desc + 1024 + 2 * k, b_desc + 2 * k, idesc, (kt | k) != 0 ? 1u : 0u);
+          }
           umma_commit(&empty_bar[s]);
           if (kt == num_kt - 1)
             umma_commit(&tmem_full_bar[acc]);
@@ -205,12 +215,15 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int row = q * 32 + lane;     // accumulator row == logical row m0 + row
     int ti = 0;
     for (int mt = blockIdx.y; mt * BM < m_count; mt += gridDim.y, ++ti) {
-      const int acc = ti & 1;
-      const int m = mt * BM + row;
-      const bool live = m < m_count;
-      mbar_wait(&tmem_full_bar[acc], (ti >> 1) & 1, &abort_flag, p.status_word, 204);
+      const int acc = MT == 1 ? (ti & 1) : 0;
+      const uint32_t use = MT == 1 ? (ti >> 1) : ti;
+      mbar_wait(&tmem_full_bar[acc], use & 1, &abort_flag, p.status_word, 204);
       tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int sub = 0; sub < MT; ++sub) {
+      const int m = mt * BM + sub * kGemmBM + row;
+      const bool live = m < m_count;
+      const uint32_t t_row = tmem_base + (MT == 1 ? acc : sub) * BN + (static_cast<uint32_t>(q * 32) << 16);
       int out_row = m;
       if (p.out_row_map && live)
         out_row = p.out_row_map[m];
@@ -275,7 +288,8 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
       }
-      // the accumulator may be overwritten by the tile after next
+      }
+      // the accumulator may be overwritten by the tile after next (MT = 2: by the next tile)
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty_bar[acc]);
     }
