@@ -151,12 +151,87 @@ class StepRunner:
         logits = self.model.compute_logits(hidden)
         return self._unmask(seqs, logits, ctx)
 
-    def generate(self, prompts: List[List[int]], max_new_tokens: int) -> List[List[int]]:
-        """Runs all denoising steps of one batch and returns the generated token ids (host lists)."""
+    def generate(self, prompts: List[List[int]], max_new_tokens: int, device_state: bool = True) -> List[List[int]]:
+        """Runs all denoising steps of one batch and returns the generated token ids (host lists).
+
+        With ``device_state`` (equal-length prompts, and steps * tokens-per-step == max_new_tokens) the token
+        matrix, the step layouts and the list of positions unmasked in the previous step stay on the device:
+        the prompts go up once, the generated ids come back once, and no step waits for the host."""
+        lens = {len(p) for p in prompts}
+        gen = max_new_tokens
+        steps_per_block = max(1, self.steps * self.block_length // gen)
+        num_transfer = max(1, self.block_length // steps_per_block)
+        if device_state and len(lens) == 1 and self.steps * num_transfer == gen and gen % self.block_length == 0:
+            return self._generate_device(prompts, gen, steps_per_block, num_transfer)
         seqs = self.new_batch(prompts, max_new_tokens)
         for _ in range(self.steps):
             self.step(seqs)
         return [s.token_ids[s.num_prompt_tokens:] for s in seqs]
+
+    @torch.inference_mode()
+    def _generate_device(self, prompts, gen, steps_per_block, num_transfer):
+        dev = self.device
+        B, P = len(prompts), len(prompts[0])
+        L, blk_len = P + gen, self.block_length
+        prompt_t = torch.tensor(prompts, dtype=torch.int64)
+        io_bytes["h2d"] += prompt_t.numel() * 8
+        tokens = torch.full((B, L), self.mask_id, dtype=torch.int64, device=dev)
+        tokens[:, :P] = prompt_t.pin_memory().to(dev, non_blocking=True)
+        seq_ids = list(range(B))
+        set_metadata(seq_ids, seq_ids, [])
+        md = get_metadata()
+        md.running_seqs_tensor = torch.tensor(seq_ids, dtype=torch.long, device=dev)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        # step layouts: dense / full-sequence sparse share one, response-only sparse has its own
+        cu_full_l = [b * L for b in range(B + 1)]
+        cu_ro_l = [b * gen for b in range(B + 1)]
+        cu_full, cu_ro = i32(cu_full_l), i32(cu_ro_l)
+        cu_prompt = i32([b * P for b in range(B + 1)])
+        cu_sal = i32([b * num_transfer for b in range(B + 1)])
+        lens_t = i32([L] * B)
+        pos_full = torch.arange(L, device=dev).repeat(B)
+        pos_ro = torch.arange(P, L, device=dev).repeat(B)
+        row_base_full = (torch.arange(B, device=dev) * L).unsqueeze(1)
+        row_base_ro = (torch.arange(B, device=dev) * gen).unsqueeze(1)
+        blk_ar = torch.arange(blk_len, device=dev).unsqueeze(0)
+        last_pos = None   # [B, num_transfer] positions unmasked in the previous step, ascending per row
+        for step in range(self.steps):
+            is_full = step < self.num_full_steps
+            pruned = (not is_full) and step > self.refresh_period and step % self.refresh_period != 0
+            if is_full:
+                set_context(True, cu_seqlens_q=cu_full, cu_seqlens_q_cpu=cu_full_l, cu_seqlens_k=cu_full, max_seqlen_q=L,
+                            max_seqlen_k=L, context_lens=lens_t, context_lens_cpu=[L] * B, total_seqlen=B * L,
+                            total_seqlen_k=B * L)
+                input_ids, positions = tokens.reshape(-1), pos_full
+            else:
+                idx_k = (last_pos + row_base_full).reshape(-1)
+                idx_q = (last_pos - P + row_base_ro).reshape(-1) if pruned else idx_k
+                set_context(False, cu_seqlens_q=cu_ro if pruned else cu_full,
+                            cu_seqlens_q_cpu=cu_ro_l if pruned else cu_full_l, cu_seqlens_k=cu_full,
+                            cu_promptlens=cu_prompt, cu_updatedlens=cu_sal, cu_salientlens=cu_sal,
+                            max_seqlen_q=gen if pruned else L, max_seqlen_k=L, idx_salient_row=idx_q,
+                            idx_salient_row_k=idx_k if pruned else None, idx_salient_row32=idx_q.to(torch.int32),
+                            max_salient_per_seq=num_transfer, context_lens=lens_t, context_lens_cpu=[L] * B,
+                            total_seqlen_k=B * L, total_seqlen=B * (gen if pruned else L))
+                input_ids = tokens[:, P:].reshape(-1) if pruned else tokens.reshape(-1)
+                positions = pos_ro if pruned else pos_full
+            hidden = self.model(input_ids, positions)
+            logits = self.model.compute_logits(hidden)
+            # confidence rule on the current block (ref: sampler.py:244-315), entirely on the device
+            blk = min(step // steps_per_block, gen // blk_len - 1)
+            start = P + blk * blk_len
+            rows = (row_base_ro + (start - P) if (not is_full and pruned) else row_base_full + start) + blk_ar
+            cand = logits.index_select(0, rows.reshape(-1)).float().view(B, blk_len, -1)
+            conf, tok = torch.softmax(cand, dim=-1).max(dim=-1)
+            still_masked = tokens[:, start:start + blk_len] == self.mask_id
+            conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
+            _, top_i = conf.topk(num_transfer, dim=-1)
+            top_i, _ = torch.sort(top_i, dim=-1)          # ascending rows for the kernels
+            last_pos = top_i + start
+            tokens.scatter_(1, last_pos, tok.gather(1, top_i))
+        out = tokens[:, P:].cpu()
+        io_bytes["d2h"] += out.numel() * 8
+        return out.tolist()
 
     def _unmask(self, seqs: List[Sequence], logits: torch.Tensor, ctx) -> int:
         B = len(seqs)

@@ -1,0 +1,32 @@
+"""The device-resident generation loop unmasks exactly the tokens the host-driven loop does (which builds
+each step's Context the way the reference's ModelRunner.prepare_full / prepare_sparse do)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_state_generation_equals_host_driven_generation(cuda_device):
+    from dyllm_b200 import _lib, runner
+    from dyllm_b200.model import LLaDAForDLM, LLaDAShape, init_weights_
+
+    shape = LLaDAShape(hidden_size=256, num_attention_heads=2, n_kv_heads=2, head_dim=128, mlp_hidden_size=512,
+                       num_hidden_layers=3, vocab_size=1024, mask_token_id=1000, max_sequence_length=256)
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(cuda_device):
+            model = LLaDAForDLM(shape, 0.99)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    init_weights_(model, seed=3, std=0.05)
+    model.eval()
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, 900, (3, 40), generator=g).tolist()
+    sr = runner.StepRunner(model, shape.mask_token_id, block_length=8, steps=32, num_full_steps=4, refresh_period=4)
+    host = sr.generate(prompts, 32, device_state=False)
+    dev = sr.generate(prompts, 32, device_state=True)
+    assert _lib.load().dyllm_device_status() == 0
+    assert host == dev
+    assert all(t != shape.mask_token_id for row in dev for t in row)
+    # deterministic across runs
+    assert sr.generate(prompts, 32, device_state=True) == dev
