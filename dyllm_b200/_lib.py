@@ -43,7 +43,7 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_moe_ffn_workspace_bytes": (Z, [I, I, I, I, I]),
     "dyllm_moe_ffn": (I, [P, I, I, c_int64, P, I, P, I, P, P, I, P, P, I, I, I, P, c_int64, P, P, Z, P]),
     "dyllm_attention_sparse_workspace_bytes": (Z, [I, I]),
-    "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, P, F, P, Z, I, P]),
+    "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, P, F, P, Z, I, P, P, I, P]),
     "dyllm_attention_salient_rows": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P]),
     "dyllm_attention_kernel_info": (I, [I, P]),
     "dyllm_attention_trace": (I, [P]),

@@ -34,7 +34,8 @@ def _check_tensor(t, name, device, dtype, dim):
 def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: int, max_seqlen_k: int,
                             total_seqlen: int, cu_salientlens, idx_salient_row, cosine_stats, cosine_out,
                             threshold: float = 0.0, is_q_pruned: bool = False, idx_salient_row_k=None,
-                            force_mask_v_rows: int = -1, v_layout: int = 1, num_salient_dev=None) -> torch.Tensor:
+                            force_mask_v_rows: int = -1, v_layout: int = 1, num_salient_dev=None,
+                            c_cache=None) -> torch.Tensor:
     """ref: dyllm/csrc/attention/attention.cpp:64-179.
 
     Same arguments, checks and return value (a fresh ``O`` shaped like ``Q``).  ``force_mask_v_rows``
@@ -44,7 +45,8 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     MN-major operand, bit 1 = ``V`` is compact ``[num_salient, Hkv, D]`` (row i = key
     ``idx_salient_row_k[i]``) instead of the zero-padded ``[T_k, Hkv, D]`` tensor.  ``num_salient_dev``
     (extension): device int32 scalar with the live length of the index lists, whose tensors are then
-    only capacity-sized.
+    only capacity-sized.  ``c_cache`` (extension): ``(seq_starts, seq_ids, update_in_place)``; ``C`` is then the
+    context cache arena ``[cache_rows, H, D]`` read (and optionally updated) in place instead of a packed copy.
     """
     if not (isinstance(Q, torch.Tensor) and Q.is_cuda):
         raise RuntimeError("Q must be CUDA")
@@ -66,8 +68,10 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
         raise RuntimeError("Q and K/V token dimensions must be non-empty")
     if Q.size(2) != K.size(2):
         raise RuntimeError("Q, K, and V must have the same head dimension")
-    if C.shape != Q.shape:
+    if c_cache is None and C.shape != Q.shape:
         raise RuntimeError("C must have the same shape as Q")
+    if c_cache is not None and C.shape[1:] != Q.shape[1:]:
+        raise RuntimeError("the context cache must be [cache_rows, Q.size(1), Q.size(2)]")
     if not (o_sal.size(0) == idx_salient_row.numel() and o_sal.size(1) == Q.size(1) and o_sal.size(2) == Q.size(2)):
         raise RuntimeError("o_sal must be [idx_salient_row.numel(), Q.size(1), Q.size(2)]")
     if not (Q.size(1) > 0 and K.size(1) > 0 and Q.size(1) % K.size(1) == 0):
@@ -105,7 +109,9 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     call("dyllm_attention_sparse_varlen", ptr(Q), ptr(K), ptr(V), ptr(C), ptr(o_sal), ptr(out), ptr(cu_seqlens_q),
          ptr(cu_seqlens_k), cu_seqlens_q.numel() - 1, int(max_seqlen_q), int(max_seqlen_k), Q.size(0), K.size(0), H,
          K.size(1), Q.size(2), ptr(cu_salientlens), ptr(idx_salient_row), ptr(idx_k), idx_salient_row.numel(),
-         ptr(num_salient_dev), ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_layout), stream_ptr(dev))
+         ptr(num_salient_dev), ptr(cosine_stats), ptr(cosine_out), float(threshold), ptr(ws), ws.numel(), int(v_layout),
+         ptr(c_cache[0]) if c_cache else None, ptr(c_cache[1]) if c_cache else None,
+         int(bool(c_cache[2])) if c_cache else 0, stream_ptr(dev))
     return out
 
 

@@ -41,7 +41,10 @@ struct AttnParams {
   __nv_bfloat16* o_sal;          // EXACT: [num_salient, H, D] output
   const __nv_bfloat16* k;        // [Tk, Hkv, D]
   const __nv_bfloat16* v;        // [Tk, Hkv, D] delta-V (non-zero on salient key rows only)
-  const __nv_bfloat16* c_old;    // [Tq, H, D]
+  const __nv_bfloat16* c_old;    // [Tq, H, D], or the context cache arena when c_seq_starts is set
+  __nv_bfloat16* c_cache;        // cache arena to update in place (same memory as c_old), or null
+  const int64_t* c_seq_starts;   // first cache row of every sequence id; null = c_old is packed like Q
+  const int64_t* c_seq_ids;      // [B] sequence id of every batch entry
   __nv_bfloat16* out;            // [Tq, H, D]
   float* partial;                // [H, Tq, 3] per-head statistics
   const int32_t* cu_q;           // [B + 1]
@@ -98,6 +101,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int num_kt = (len_k + kBKeys - 1) / kBKeys;
   const int hk = h / (p.H / p.Hkv);
   const int num_st = EXACT ? num_kt : (n_sal + kBKeys - 1) / kBKeys;   // tiles of pass B
+  // C_old row of query row r: r + c_delta (cache-resident context: the last len_q rows of the sequence)
+  int64_t c_delta = 0;
+  if (!EXACT && p.c_seq_starts)
+    c_delta = p.c_seq_starts[p.c_seq_ids[b]] + (len_k - (q_end - q_begin)) - q_begin;
   const bool v_mn_major = EXACT ? true : (p.v_mn_major != 0);
 
   extern __shared__ uint8_t smem_raw[];
@@ -264,7 +271,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (!EXACT && q0 + row < q_end) {
       // bring this thread's half of the C_old row (128 bytes) into L2 now; the epilogue reads it much later
       const char* crow =
-          reinterpret_cast<const char*>(p.c_old + (static_cast<int64_t>(q0 + row) * p.H + h) * kD + col0);
+          reinterpret_cast<const char*>(p.c_old + ((q0 + row + c_delta) * p.H + h) * kD + col0);
       asm volatile("prefetch.global.L2 [%0];" ::"l"(crow));
     }
     // source rows of the first gather (salient key rows, or the query rows of the EXACT variant)
@@ -446,8 +453,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const bool live = r < q_end;
     const float inv_l = l > 0.f ? 1.0f / l : 0.f;
     const int64_t off = (static_cast<int64_t>((live ? r : q0) + (EXACT ? sal_begin : 0)) * p.H + h) * kD + col0;
-    const __nv_bfloat16* cold = EXACT ? nullptr : p.c_old + off;
+    const int64_t c_off = (((live ? r : q0) + c_delta) * p.H + h) * kD + col0;
+    const __nv_bfloat16* cold = EXACT ? nullptr : p.c_old + c_off;
     __nv_bfloat16* dst = (EXACT ? p.o_sal : p.out) + off;
+    // in-place cache update: salient rows are left alone (their old value is still needed, and they are
+    // overwritten with the exactly attended row afterwards)
+    __nv_bfloat16* cdst = nullptr;
+    if (!EXACT && p.c_cache && live) {
+      int lo = 0, hi = n_sal;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (p.idx_q[sal_begin + mid] < r)
+          lo = mid + 1;
+        else
+          hi = mid;
+      }
+      if (!(lo < n_sal && p.idx_q[sal_begin + lo] == r))
+        cdst = p.c_cache + c_off;
+    }
     float dot = 0.f, nn = 0.f, no = 0.f;
     uint4 old_row[8];
 #pragma unroll
@@ -485,6 +508,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           reinterpret_cast<uint4*>(dst + cc)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        if (cdst) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            reinterpret_cast<uint4*>(cdst + cc)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        }
       }
     }
     if (!EXACT) {
@@ -525,7 +553,10 @@ attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, cons
                           int num_salient, const __nv_bfloat16* __restrict__ c_old,
                           const __nv_bfloat16* __restrict__ o_sal, __nv_bfloat16* __restrict__ out,
                           float* __restrict__ stats, uint8_t* __restrict__ mask, float threshold, int width,
-                          int row_blocks, const int32_t* __restrict__ num_salient_dev) {
+                          int row_blocks, const int32_t* __restrict__ num_salient_dev,
+                          __nv_bfloat16* __restrict__ c_cache, const int64_t* __restrict__ c_seq_starts,
+                          const int64_t* __restrict__ c_seq_ids, const int32_t* __restrict__ cu_q,
+                          const int32_t* __restrict__ cu_k, int batch) {
   if (num_salient_dev)
     num_salient = min(num_salient, *num_salient_dev);
   if (static_cast<int>(blockIdx.x) < row_blocks) {
@@ -560,14 +591,31 @@ attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, cons
   if (i >= num_salient)
     return;
   const int r = idx_q[i];
-  const uint4* old_row = reinterpret_cast<const uint4*>(c_old + static_cast<int64_t>(r) * width);
+  int64_t c_row = r;
+  if (c_seq_starts) {
+    // sequence b with cu_q[b] <= r < cu_q[b + 1]; its context rows are the last len_q rows in the cache
+    int lo = 0, hi = batch;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (cu_q[mid + 1] <= r)
+        lo = mid + 1;
+      else
+        hi = mid;
+    }
+    const int b = lo < batch ? lo : batch - 1;
+    c_row = c_seq_starts[c_seq_ids[b]] + ((cu_k[b + 1] - cu_k[b]) - (cu_q[b + 1] - cu_q[b])) + (r - cu_q[b]);
+  }
+  const uint4* old_row = reinterpret_cast<const uint4*>(c_old + c_row * width);
   const uint4* new_row = reinterpret_cast<const uint4*>(o_sal + static_cast<int64_t>(i) * width);
   uint4* out_row = reinterpret_cast<uint4*>(out + static_cast<int64_t>(r) * width);
+  uint4* cache_row = c_cache ? reinterpret_cast<uint4*>(c_cache + c_row * width) : nullptr;
   float dot = 0.f, nn = 0.f, no = 0.f;
   for (int v = threadIdx.x; v < width / 8; v += blockDim.x) {
-    const uint4 ov = __ldg(old_row + v);
+    const uint4 ov = old_row[v];
     const uint4 nv = __ldg(new_row + v);
     out_row[v] = nv;
+    if (cache_row)
+      cache_row[v] = nv;
     const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
     const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nv);
 #pragma unroll
@@ -652,7 +700,8 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
                                   int num_salient, const int32_t* num_salient_dev, float* cosine_stats,
                                   uint8_t* cosine_out, float threshold, void* workspace, size_t workspace_bytes,
-                                  int v_layout, void* stream) {
+                                  int v_layout, const int64_t* c_seq_starts, const int64_t* c_seq_ids,
+                                  int c_update_in_place, void* stream) {
   const int v_mn_major = (v_layout & 1) ? 1 : 0;
   const int v_compact = (v_layout & 2) ? 1 : 0;
   DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "attention_sparse_varlen: head_dim %d (only 128 is built)",
@@ -693,7 +742,14 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   AttnParams p = {};
   p.k = static_cast<const __nv_bfloat16*>(k);
   p.v = static_cast<const __nv_bfloat16*>(v);
+  DYLLM_REQUIRE((c_seq_starts == nullptr) == (c_seq_ids == nullptr) && (!c_update_in_place || c_seq_starts),
+                DYLLM_ERR_INVALID_ARGUMENT,
+                "attention_sparse_varlen: a cache-resident context needs c_seq_starts and c_seq_ids");
   p.c_old = static_cast<const __nv_bfloat16*>(c);
+  p.c_cache = c_update_in_place ? const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(c)) : nullptr;
+  p.c_seq_starts = c_seq_starts;
+  p.c_seq_ids = c_seq_ids;
+  p.idx_q = idx_salient_row_q;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.partial = static_cast<float*>(workspace);
   p.cu_q = cu_seqlens_q;
@@ -719,7 +775,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   attention_finalize_kernel<<<row_blocks + num_salient, 256, 0, s>>>(
       p.partial, num_heads, total_q, idx_salient_row_q, num_salient, p.c_old,
       static_cast<const __nv_bfloat16*>(o_sal), p.out, cosine_stats, cosine_out, threshold, num_heads * kD, row_blocks,
-      num_salient_dev);
+      num_salient_dev, p.c_cache, c_seq_starts, c_seq_ids, cu_seqlens_q, cu_seqlens_k, batch);
   return check_launch("attention_finalize");
 }
 

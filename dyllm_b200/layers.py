@@ -441,17 +441,17 @@ class Attention(nn.Module):
 
         stats = torch.zeros((ctx.total_seqlen, 3), dtype=torch.float32, device=q.device)
         mask = torch.empty((ctx.total_seqlen,), dtype=torch.bool, device=q.device)
-        c_old = (self.context_cache.get_seqs_block(seq_t) if is_q_pruned
-                 else self.context_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs))
-        c_old = c_old.view(-1, H, D)
+        # the previous context is read from, and the new one written back to, the cache arena itself
+        c_arena = self.context_cache.cache.view(-1, H, D)
         rows_k32 = rows_k.to(torch.int32) if is_q_pruned else None
         # algorithmic flops: Q K^T over all keys (sum over sequences of len_q * len_k, equal lengths here)
         flops = 2.0 * ctx.total_seqlen * ctx.max_seqlen_k * H * D
         with profiling.region("delta_attention", flops):
-            new_c = attention_sparse_varlen(q, k, dv, c_old, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
+            new_c = attention_sparse_varlen(q, k, dv, c_arena, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens,
                                             idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=3,
-                                            num_salient_dev=n_dev)
+                                            num_salient_dev=n_dev,
+                                            c_cache=(self.context_cache.seq_start_gpu, seq_t, True))
 
         # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch; the new
         # lists stay on the device together with their length
@@ -461,10 +461,7 @@ class Attention(nn.Module):
             sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,
                                      ctx.cu_promptlens if is_q_pruned else None)
         if is_q_pruned:
-            self.context_cache.reset_block(new_c.flatten(-2, -1), seq_t)
             ctx.idx_salient_row_k = sel.idx_k
-        else:
-            self.context_cache.reset_full(new_c.flatten(-2, -1), seq_t, seq_ids_list=md.running_seqs)
         ctx.idx_salient_row = sel.idx
         ctx.idx_salient_row32 = sel.idx32
         ctx.cu_salientlens = sel.cu_salientlens

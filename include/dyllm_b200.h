@@ -214,6 +214,12 @@ size_t dyllm_attention_sparse_workspace_bytes(int total_q, int num_heads);
  * tensor cores (1 = as gathered, MN-major descriptor; 0 = transposed while gathering; results are
  * identical); bit 1 set means v is compact, [num_salient, num_kv_heads, 128] with row i belonging to
  * key idx_salient_row_k[i], instead of the zero-padded [total_k, ...] tensor (no memset, no scatter).
+ * Cache-resident context (c_seq_starts and c_seq_ids not null): c is then the context cache arena
+ * [cache_rows, num_heads, 128] itself and the old context of query row r of batch entry b is cache row
+ * c_seq_starts[c_seq_ids[b]] + len_k(b) - len_q(b) + (r - cu_seqlens_q[b]) (the last len_q rows of the
+ * sequence), which removes the caller's gather copy; with c_update_in_place != 0 the new context is also
+ * written back to those rows, which removes the caller's write-back copy (the reference's
+ * get_seqs / get_block and reset_full / reset_block around this call, layers/attention.py:107-111,152-170).
  * ref: dyllm/csrc/attention/attention.cpp:64-179 (attention_sparse_varlen),
  *      dyllm/csrc/attention/attention_ops_kernels_sm80.cu:44-590,
  *      dyllm/csrc/attention/attention_aux_kernels.cu:10-110. */
@@ -224,7 +230,8 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                                   const int32_t* idx_salient_row_q, const int32_t* idx_salient_row_k,
                                   int num_salient, const int32_t* num_salient_dev, float* cosine_stats,
                                   uint8_t* cosine_out, float threshold, void* workspace, size_t workspace_bytes,
-                                  int v_layout, void* stream);
+                                  int v_layout, const int64_t* c_seq_starts, const int64_t* c_seq_ids,
+                                  int c_update_in_place, void* stream);
 
 
 /* Delta-V of the step and value-cache update in one pass over the salient rows:

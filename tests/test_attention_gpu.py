@@ -208,3 +208,48 @@ def test_attention_no_salient_rows_with_empty_compact_delta_v(cuda_device):
                                   d(case["cu_q"]), d(case["cu_k"]), case["max_q"], case["max_k"], Tq, d(case["cu_sal"]),
                                   d(case["idx_q"]), stats, mask, TAU, v_layout=3)
     assert torch.equal(out.cpu(), case["c_old"]) and not bool(mask.any())
+
+
+@pytest.mark.parametrize("case_id", [1, 2, 3, 5])
+def test_attention_cache_resident_context_equals_packed_path(cuda_device, case_id):
+    """Reading the old context from the cache arena and writing the new one back in place gives the same
+    bits as gather copy -> kernel -> write-back copy."""
+    from dyllm_b200.attention_ops import attention_sparse_varlen
+
+    batch, prompt, response, H, Hkv, ro, sal = CASES[case_id]
+    case = make_case(batch, prompt, response, H, Hkv, ro, sal, seed=200 + case_id)
+    ref_out, ref_stats, ref_mask = run_gpu(case, cuda_device, 1)
+    # cache arena: sequences stored whole (len_k rows each) in reverse batch order, with a gap in front
+    cu_q, cu_k = case["cu_q"], case["cu_k"]
+    lens_k = (cu_k[1:] - cu_k[:-1]).tolist()
+    lens_q = (cu_q[1:] - cu_q[:-1]).tolist()
+    g = torch.Generator().manual_seed(1)
+    total = sum(lens_k) + 9
+    arena = torch.randn(total, H, 128, generator=g).bfloat16()
+    seq_ids = torch.tensor([7 + 2 * b for b in range(batch)])
+    seq_starts = torch.full((64,), -1, dtype=torch.int64)
+    pos = 9
+    for b in reversed(range(batch)):
+        seq_starts[seq_ids[b]] = pos
+        pos += lens_k[b]
+    for b in range(batch):   # the old context of the query rows = the last len_q rows of each sequence
+        s0 = int(seq_starts[seq_ids[b]]) + lens_k[b] - lens_q[b]
+        arena[s0:s0 + lens_q[b]] = case["c_old"][int(cu_q[b]):int(cu_q[b + 1])]
+    before = arena.clone()
+    d = lambda t: t.to(cuda_device)
+    Tq = case["q"].size(0)
+    stats = torch.zeros(Tq, 3, device=cuda_device)
+    mask = torch.empty(Tq, dtype=torch.bool, device=cuda_device)
+    d_arena = d(arena)
+    out = attention_sparse_varlen(d(case["q"]), d(case["k"]), d(case["dv"]), d_arena, d(case["o_sal"]), d(cu_q), d(cu_k),
+                                  case["max_q"], case["max_k"], Tq, d(case["cu_sal"]), d(case["idx_q"]), stats, mask, TAU,
+                                  ro, d(case["idx_k"]) if ro else None, v_layout=1,
+                                  c_cache=(d(seq_starts), d(seq_ids), True))
+    assert torch.equal(out.cpu(), ref_out) and torch.equal(stats.cpu(), ref_stats) and torch.equal(mask.cpu(), ref_mask)
+    after = d_arena.cpu()
+    touched = torch.zeros(total, dtype=torch.bool)
+    for b in range(batch):
+        s0 = int(seq_starts[seq_ids[b]]) + lens_k[b] - lens_q[b]
+        assert torch.equal(after[s0:s0 + lens_q[b]], ref_out[int(cu_q[b]):int(cu_q[b + 1])])
+        touched[s0:s0 + lens_q[b]] = True
+    assert torch.equal(after[~touched], before[~touched])
