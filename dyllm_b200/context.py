@@ -40,6 +40,9 @@ class Context:
     # estimate of that count (used only to shape launches).
     num_salient_dev: Optional[torch.Tensor] = None
     salient_hint: int = 0
+    # When positive, every layer uses this row-count estimate instead of reading its previous count back
+    # (a step captured into a CUDA graph cannot depend on host-side state).
+    fixed_hint: int = 0
 
     def salient_rows(self):
         """(idx_salient_row, idx_salient_row_k or None) trimmed to the live length (synchronises)."""

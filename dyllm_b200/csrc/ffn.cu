@@ -67,13 +67,17 @@ stage_rows_kernel(const uint4* __restrict__ x, int64_t x_pitch_vecs, const int32
 
 // out[map[m]][n] = bf16(scale[m] * sum_z partial[z][m][n]) in split order (deterministic).
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float* __restrict__ partial, int splits, int split_rows, int n_total, int M,
+splitk_reduce_kernel(const float* __restrict__ partial, int max_splits, int n_tiles, int slots, int num_kt,
+                     int split_rows, int n_total, int M,
                      const int32_t* __restrict__ m_count_dev, __nv_bfloat16* __restrict__ out, int64_t ldc,
                      const int32_t* __restrict__ out_row_map, const float* __restrict__ row_scale,
                      __nv_bfloat16* __restrict__ out2, int64_t ldc2, int split_col) {
   const int m_count = m_count_dev ? min(*m_count_dev, M) : M;
   if (m_count > split_rows)
     return;  // the GEMM wrote its results directly
+  const int splits = effective_splits((m_count + kGemmBM - 1) / kGemmBM, n_tiles, slots, max_splits, num_kt);
+  if (splits == 1)
+    return;
   const int m = blockIdx.y;
   if (m >= m_count)
     return;
@@ -104,6 +108,7 @@ struct Plan {
   int splits;
   bool two_per_sm;   // narrow tiles, half-depth pipeline, two CTAs per SM (weight-streaming regime)
   bool tall;         // 256-row tiles (two accumulators per weight tile) for many rows
+  int slots;         // CTAs resident at once
   dim3 grid;
 };
 
@@ -121,20 +126,18 @@ Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_
   // many rows: the 128-row tile is limited by weight traffic from L2; 256-row tiles halve it
   plan.tall = allow_tall && tile_n == 128 && h > 256 && cdiv_i(h, 2 * kGemmBM) * n_tiles >= sms;
   plan.two_per_sm = tile_n == 64 && mt_h <= 2;
-  const int slots = plan.two_per_sm ? 2 * sms : sms;
+  plan.slots = plan.two_per_sm ? 2 * sms : sms;
+  // the grid carries the splits a single live row tile would use; CTAs of splits that the live count
+  // does not need return at once
   plan.splits = 1;
-  if (!swiglu && can_split && h <= kSplitRows) {
-    const int ctas = mt_h * n_tiles;
-    if (ctas * 2 <= slots) {
-      int s = slots / ctas;
-      s = s > kMaxSplits ? kMaxSplits : s;
-      const int num_kt = K / kGemmBK;
-      s = s > num_kt ? num_kt : s;
-      plan.splits = s < 1 ? 1 : s;
-    }
-  }
+  if (!swiglu && can_split && !plan.tall && h <= kSplitRows)
+    plan.splits = effective_splits(1, n_tiles, plan.slots, kMaxSplits, K / kGemmBK);
   const int bm = plan.tall ? 2 * kGemmBM : kGemmBM;
   int m_groups = cdiv_i(h, bm);
+  // a count above the hint is served by extra grid rows (they return at once when not needed) before
+  // CTAs have to walk over several row tiles
+  if (h <= kSplitRows && m_groups < kSplitRows / kGemmBM)
+    m_groups = kSplitRows / kGemmBM;
   const int mt_all = cdiv_i(M, bm);
   m_groups = m_groups > mt_all ? mt_all : m_groups;
   plan.grid = dim3(n_tiles, m_groups < 1 ? 1 : m_groups, plan.splits);
@@ -199,6 +202,7 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   p.n_total = n;
   p.partial = plan.splits > 1 ? partial : nullptr;
   p.split_rows = kSplitRows;
+  p.split_slots = plan.slots;
 
   CUtensorMap ta, tb;
   int rc;
@@ -235,7 +239,8 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
     return rc;
   const int rows = p.M < kSplitRows ? p.M : kSplitRows;
   dim3 rgrid(cdiv_i(n, 256 * 8), rows);
-  splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(partial, plan.splits, kSplitRows, n, p.M, p.m_count_dev, p.out, p.ldc,
+  splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(partial, plan.splits, n / plan.tile_n, plan.slots, p.K / kGemmBK,
+                                                  kSplitRows, n, p.M, p.m_count_dev, p.out, p.ldc,
                                                   p.out_row_map, p.row_scale, p.out2, p.ldc2, p.split_col);
   return check_launch("splitk_reduce");
 }

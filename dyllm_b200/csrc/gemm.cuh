@@ -40,6 +40,7 @@ struct GemmParams {
   int split_col;
   float* partial;              // split-K: fp32 [gridDim.z][split_rows][n_total]; null = no split-K
   int split_rows;              // split-K is used only while the live row count is <= split_rows
+  int split_slots;             // CTAs the device runs at once; the live split count is derived from it
   int n_total;                 // output columns (row pitch of `partial`)
   int* status_word;
 };
@@ -63,6 +64,20 @@ struct GemmCfg {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns");
 };
+
+// Number of K splits for `live_tiles` row tiles: as many as keep every CTA slot busy, at most
+// `max_splits` (the grid's z extent) and the number of k tiles.  The GEMM and the reduction kernel both
+// derive it from the device-side row count, so one launch shape serves every count.
+__host__ __device__ __forceinline__ int effective_splits(int live_tiles, int n_tiles, int slots, int max_splits,
+                                                         int num_kt) {
+  const int ctas = (live_tiles < 1 ? 1 : live_tiles) * n_tiles;
+  if (ctas * 2 > slots)
+    return 1;
+  int s = slots / ctas;
+  s = s > max_splits ? max_splits : s;
+  s = s > num_kt ? num_kt : s;
+  return s < 1 ? 1 : s;
+}
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
@@ -90,13 +105,16 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   int kt_begin = 0, kt_end = num_kt_all;
   bool write_partial = false;
   if (p.partial != nullptr) {
-    if (m_count <= p.split_rows) {
-      const int per = (num_kt_all + gridDim.z - 1) / gridDim.z;
+    const int splits = m_count <= p.split_rows
+                           ? effective_splits((m_count + BM - 1) / BM, gridDim.x, p.split_slots, gridDim.z, num_kt_all)
+                           : 1;
+    if (static_cast<int>(blockIdx.z) >= splits)
+      return;
+    if (splits > 1) {
+      const int per = (num_kt_all + splits - 1) / splits;
       kt_begin = min(static_cast<int>(blockIdx.z) * per, num_kt_all);
       kt_end = min(kt_begin + per, num_kt_all);
       write_partial = true;
-    } else if (blockIdx.z != 0) {
-      return;
     }
   }
   const int num_kt = kt_end - kt_begin;

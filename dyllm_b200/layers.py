@@ -275,8 +275,11 @@ class LLaDAMLP(nn.Module):
                 cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
-                flops = 6.0 * (hint or cap) * hidden.size(1) * self.down_proj.weight.size(1)
-                with profiling.region("swiglu_ffn", flops):
+                rows = hint or cap
+                width, inter = hidden.size(1), self.down_proj.weight.size(1)
+                # algorithmic bytes: the three weight matrices once, the rows in and out
+                nbytes = 3.0 * width * inter * 2 + 2.0 * rows * width * 2
+                with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
                     ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
                                    num_rows=cap, num_rows_dev=n_dev, rows_hint=hint, out=cm.cache, out_row_map=dest)
         cm.finish(md.finished_seqs)
@@ -388,10 +391,13 @@ class Attention(nn.Module):
         self._hint_event = None
         self._hint = 0
 
-    def _next_hint(self, count_dev: torch.Tensor, capacity: int) -> int:
+    def _next_hint(self, count_dev: torch.Tensor, capacity: int, fixed: int = 0) -> int:
         """Estimate of the salient count this layer has just produced: its value from the previous step
         (read back asynchronously, never waited for), or the capacity when none has arrived yet.  The
-        estimate only shapes launches; kernels take the true count from the device."""
+        estimate only shapes launches; kernels take the true count from the device.  With ``fixed`` the
+        estimate is that constant and no host state is touched (steps captured into a CUDA graph)."""
+        if fixed:
+            return min(fixed, capacity)
         if self._hint_host is None:
             self._hint_host = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._hint_event = torch.cuda.Event()
@@ -435,7 +441,8 @@ class Attention(nn.Module):
 
         # exact attention of the salient query rows (attention.py:76-87)
         max_rows = max(min(ctx.max_salient_per_seq, ctx.max_seqlen_q), 1)
-        with profiling.region("salient_attention", 4.0 * (hint or cap) * ctx.max_seqlen_k * H * D):
+        with profiling.region("salient_attention", 4.0 * (hint or cap) * ctx.max_seqlen_k * H * D,
+                              2.0 * ctx.total_seqlen_k * Hkv * D * 2 + 2.0 * (hint or cap) * H * D * 2):
             o_sal = attention_salient_rows(q, k, v_full, ctx.cu_seqlens_k, ctx.cu_salientlens, idx_q32,
                                            max_rows_per_seq=max_rows, num_salient=cap)
 
@@ -446,7 +453,9 @@ class Attention(nn.Module):
         rows_k32 = rows_k.to(torch.int32) if is_q_pruned else None
         # algorithmic flops: Q K^T over all keys (sum over sequences of len_q * len_k, equal lengths here)
         flops = 2.0 * ctx.total_seqlen * ctx.max_seqlen_k * H * D
-        with profiling.region("delta_attention", flops):
+        # algorithmic bytes: Q and the previous context read, the new context written, K read once
+        nbytes = 3.0 * ctx.total_seqlen * H * D * 2 + ctx.total_seqlen_k * Hkv * D * 2
+        with profiling.region("delta_attention", flops, nbytes):
             new_c = attention_sparse_varlen(q, k, dv, c_arena, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens,
                                             idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=3,
@@ -457,7 +466,7 @@ class Attention(nn.Module):
         # lists stay on the device together with their length
         if _world_size() > 1:
             dist.all_reduce(stats, op=dist.ReduceOp.SUM)
-        with profiling.region("salient_select", 12.0 * ctx.total_seqlen):
+        with profiling.region("salient_select", 0.0, 12.0 * ctx.total_seqlen):
             sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,
                                      ctx.cu_promptlens if is_q_pruned else None)
         if is_q_pruned:
@@ -467,7 +476,7 @@ class Attention(nn.Module):
         ctx.cu_salientlens = sel.cu_salientlens
         ctx.num_salient_dev = sel.count
         ctx.max_salient_per_seq = ctx.max_seqlen_q
-        ctx.salient_hint = self._next_hint(sel.count, ctx.total_seqlen)
+        ctx.salient_hint = self._next_hint(sel.count, ctx.total_seqlen, ctx.fixed_hint)
 
         self.v_cache.finish(md.finished_seqs)
         self.context_cache.finish(md.finished_seqs)

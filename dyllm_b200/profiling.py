@@ -17,15 +17,19 @@ def enable(flag: bool = True) -> None:
     _enabled = flag
 
 
+def enabled() -> bool:
+    return _enabled
+
+
 def reset() -> None:
     _records.clear()
     _counts.clear()
 
 
 @contextlib.contextmanager
-def region(name: str, work: float = 0.0):
+def region(name: str, work: float = 0.0, nbytes: float = 0.0):
     """Times the enclosed launches with CUDA events on the current stream; ``work`` is the algorithmic
-    flop or byte count of the region."""
+    flop count of the region and ``nbytes`` its algorithmic HBM bytes."""
     if not _enabled:
         yield
         return
@@ -36,7 +40,7 @@ def region(name: str, work: float = 0.0):
         yield
     finally:
         end.record()
-        _records[name].append((start, end, work))
+        _records[name].append((start, end, work, nbytes))
 
 
 _counts: dict[str, list] = defaultdict(list)
@@ -57,7 +61,7 @@ def summary() -> dict:
     torch.cuda.synchronize()
     out = {}
     for name, recs in _records.items():
-        total = sum(s.elapsed_time(e) for s, e, _ in recs)
+        total = sum(r[0].elapsed_time(r[1]) for r in recs)
         out[name] = {"launches": len(recs), "total_ms": total, "avg_ms": total / max(len(recs), 1),
-                     "work": sum(w for _, _, w in recs)}
+                     "work": sum(r[2] for r in recs), "bytes": sum(r[3] for r in recs)}
     return out

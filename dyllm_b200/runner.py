@@ -10,11 +10,22 @@ and multi-process control of the reference engine are outside this package.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from types import SimpleNamespace
 from typing import List
 
 import torch
+import torch.distributed as dist
 
+from . import _lib, profiling
 from .context import get_context, get_metadata, set_context, set_metadata
+
+# Row-count estimate baked into the launches of a captured step: the common case is at most one 128-row
+# tile of salient rows per layer; the kernels adapt to the true count on the device.
+GRAPH_ROWS_HINT = 128
+
+
+def _multi_rank() -> bool:
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
 
 
 @dataclass
@@ -121,7 +132,7 @@ class StepRunner:
     """Runs denoising steps of a fixed batch: ``num_full_steps`` dense steps, then sparse steps."""
 
     def __init__(self, model, mask_id: int, block_length: int = 32, steps: int = 256, num_full_steps: int = 8,
-                 refresh_period: int = 4):
+                 refresh_period: int = 4, use_graphs: bool = True, full_logits: bool = False):
         self.model = model
         self.mask_id = mask_id
         self.block_length = block_length
@@ -130,6 +141,15 @@ class StepRunner:
         self.refresh_period = refresh_period
         self.device = next(model.parameters()).device
         self.salient_counts: list[int] = []
+        self.use_graphs = use_graphs
+        # The reference projects every query row onto the vocabulary and then indexes the rows of the
+        # current block (model_runner.py:377, sampler.py:244-315); with full_logits False only the rows the
+        # sampler reads are projected, which yields the same tokens.
+        self.full_logits = full_logits
+        self._states: dict = {}
+        self._graphs: dict = {}
+        self._warm: set = set()
+        self._graph_pool = None
 
     def new_batch(self, prompts: List[List[int]], max_new_tokens: int, first_seq_id: int = 0) -> List[Sequence]:
         seqs = []
@@ -148,8 +168,7 @@ class StepRunner:
             input_ids, positions = prepare_sparse(seqs, self.device, self.refresh_period)
         ctx = get_context()
         hidden = self.model(input_ids, positions)
-        logits = self.model.compute_logits(hidden)
-        return self._unmask(seqs, logits, ctx)
+        return self._unmask(seqs, hidden, ctx)
 
     def generate(self, prompts: List[List[int]], max_new_tokens: int, device_state: bool = True) -> List[List[int]]:
         """Runs all denoising steps of one batch and returns the generated token ids (host lists).
@@ -168,72 +187,143 @@ class StepRunner:
             self.step(seqs)
         return [s.token_ids[s.num_prompt_tokens:] for s in seqs]
 
+    def _device_state(self, B: int, P: int, gen: int, steps_per_block: int, num_transfer: int):
+        """Buffers of the device-resident loop for one batch geometry.  They are allocated once and reused
+        by every generation of that geometry, so that captured graphs stay valid."""
+        key = (B, P, gen, steps_per_block, num_transfer)
+        st = self._states.get(key)
+        if st is not None:
+            return st
+        dev, L, blk_len = self.device, P + gen, self.block_length
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        st = SimpleNamespace(
+            key=key, B=B, P=P, gen=gen, L=L, steps_per_block=steps_per_block, num_transfer=num_transfer,
+            tokens=torch.full((B, L), self.mask_id, dtype=torch.int64, device=dev),
+            last_pos=torch.zeros((B, num_transfer), dtype=torch.int64, device=dev),
+            step_t=torch.zeros((), dtype=torch.int64, device=dev),
+            seq_t=torch.arange(B, dtype=torch.long, device=dev),
+            # step layouts: dense / full-sequence sparse share one, response-only sparse has its own
+            cu_full_l=[b * L for b in range(B + 1)], cu_ro_l=[b * gen for b in range(B + 1)],
+            cu_prompt=i32([b * P for b in range(B + 1)]), cu_sal=i32([b * num_transfer for b in range(B + 1)]),
+            lens_t=i32([L] * B), pos_full=torch.arange(L, device=dev).repeat(B),
+            pos_ro=torch.arange(P, L, device=dev).repeat(B),
+            row_base_full=(torch.arange(B, device=dev) * L).unsqueeze(1),
+            row_base_ro=(torch.arange(B, device=dev) * gen).unsqueeze(1),
+            blk_ar=torch.arange(blk_len, device=dev).unsqueeze(0), fixed_hint=0)
+        st.cu_full, st.cu_ro = i32(st.cu_full_l), i32(st.cu_ro_l)
+        self._states[key] = st
+        return st
+
+    def _device_step(self, st, kind: str) -> None:
+        """One denoising step on the state buffers.  ``kind`` is "full" (dense), "sparse" (full-sequence
+        queries) or "pruned" (response-only queries).  Everything that changes from step to step (the token
+        matrix, the positions unmasked by the previous step, the step counter that selects the current
+        block) lives on the device, so the same sequence of launches serves every step of a kind."""
+        B, P, L, gen, blk_len = st.B, st.P, st.L, st.gen, self.block_length
+        tokens = st.tokens
+        if kind == "full":
+            set_context(True, cu_seqlens_q=st.cu_full, cu_seqlens_q_cpu=st.cu_full_l, cu_seqlens_k=st.cu_full,
+                        max_seqlen_q=L, max_seqlen_k=L, context_lens=st.lens_t, context_lens_cpu=[L] * B,
+                        total_seqlen=B * L, total_seqlen_k=B * L)
+            input_ids, positions = tokens.reshape(-1), st.pos_full
+        else:
+            pruned = kind == "pruned"
+            idx_k = (st.last_pos + st.row_base_full).reshape(-1)
+            idx_q = (st.last_pos - P + st.row_base_ro).reshape(-1) if pruned else idx_k
+            set_context(False, cu_seqlens_q=st.cu_ro if pruned else st.cu_full,
+                        cu_seqlens_q_cpu=st.cu_ro_l if pruned else st.cu_full_l, cu_seqlens_k=st.cu_full,
+                        cu_promptlens=st.cu_prompt, cu_updatedlens=st.cu_sal, cu_salientlens=st.cu_sal,
+                        max_seqlen_q=gen if pruned else L, max_seqlen_k=L, idx_salient_row=idx_q,
+                        idx_salient_row_k=idx_k if pruned else None, idx_salient_row32=idx_q.to(torch.int32),
+                        max_salient_per_seq=st.num_transfer, context_lens=st.lens_t, context_lens_cpu=[L] * B,
+                        total_seqlen_k=B * L, total_seqlen=B * (gen if pruned else L), fixed_hint=st.fixed_hint)
+            input_ids = tokens[:, P:].reshape(-1) if pruned else tokens.reshape(-1)
+            positions = st.pos_ro if pruned else st.pos_full
+        hidden = self.model(input_ids, positions)
+        # confidence rule on the current block (ref: sampler.py:244-315), entirely on the device
+        blk = torch.clamp(st.step_t // st.steps_per_block, max=gen // blk_len - 1)
+        start = P + blk * blk_len                                    # 0-d device tensor
+        if kind == "pruned":
+            rows = st.row_base_ro + (start - P) + st.blk_ar
+        else:
+            rows = st.row_base_full + start + st.blk_ar
+        cand = self._block_logits(hidden, rows.reshape(-1)).float().view(B, blk_len, -1)
+        conf, tok = torch.softmax(cand, dim=-1).max(dim=-1)
+        cols = (start + st.blk_ar).expand(B, -1)
+        still_masked = tokens.gather(1, cols) == self.mask_id
+        conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
+        _, top_i = conf.topk(st.num_transfer, dim=-1)
+        top_i, _ = torch.sort(top_i, dim=-1)          # ascending rows for the kernels
+        new_pos = top_i + start
+        tokens.scatter_(1, new_pos, tok.gather(1, top_i))
+        st.last_pos.copy_(new_pos)
+        st.step_t.add_(1)
+
+    def _run_step(self, st, kind: str) -> None:
+        """Runs one step: eagerly the first time a kind of step is met (allocations, one-time kernel
+        attributes), then captured into a CUDA graph and replayed.  Graphs are not used while region
+        timing is on (events cannot be timed inside a graph) or with more than one rank."""
+        if not self.use_graphs or profiling.enabled() or _multi_rank():
+            self._device_step(st, kind)
+            return
+        key = (st.key, kind)
+        entry = self._graphs.get(key)
+        if entry is None:
+            if key not in self._warm:
+                # same launch shapes as the capture that follows, so that every kernel it needs is loaded
+                self._warm.add(key)
+                st.fixed_hint = GRAPH_ROWS_HINT
+                try:
+                    self._device_step(st, kind)
+                finally:
+                    st.fixed_hint = 0
+                return
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            before = _lib.launch_count
+            st.fixed_hint = GRAPH_ROWS_HINT
+            try:
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    self._device_step(st, kind)
+            finally:
+                st.fixed_hint = 0
+            entry = self._graphs[key] = (graph, _lib.launch_count - before)
+            _lib.launch_count = before
+        entry[0].replay()
+        _lib.launch_count += entry[1]
+
     @torch.inference_mode()
     def _generate_device(self, prompts, gen, steps_per_block, num_transfer):
-        dev = self.device
         B, P = len(prompts), len(prompts[0])
-        L, blk_len = P + gen, self.block_length
+        st = self._device_state(B, P, gen, steps_per_block, num_transfer)
         prompt_t = torch.tensor(prompts, dtype=torch.int64)
         io_bytes["h2d"] += prompt_t.numel() * 8
-        tokens = torch.full((B, L), self.mask_id, dtype=torch.int64, device=dev)
-        tokens[:, :P] = prompt_t.pin_memory().to(dev, non_blocking=True)
+        st.tokens.fill_(self.mask_id)
+        st.tokens[:, :P] = prompt_t.pin_memory().to(self.device, non_blocking=True)
+        st.step_t.zero_()
         seq_ids = list(range(B))
         set_metadata(seq_ids, seq_ids, [])
-        md = get_metadata()
-        md.running_seqs_tensor = torch.tensor(seq_ids, dtype=torch.long, device=dev)
-        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-        # step layouts: dense / full-sequence sparse share one, response-only sparse has its own
-        cu_full_l = [b * L for b in range(B + 1)]
-        cu_ro_l = [b * gen for b in range(B + 1)]
-        cu_full, cu_ro = i32(cu_full_l), i32(cu_ro_l)
-        cu_prompt = i32([b * P for b in range(B + 1)])
-        cu_sal = i32([b * num_transfer for b in range(B + 1)])
-        lens_t = i32([L] * B)
-        pos_full = torch.arange(L, device=dev).repeat(B)
-        pos_ro = torch.arange(P, L, device=dev).repeat(B)
-        row_base_full = (torch.arange(B, device=dev) * L).unsqueeze(1)
-        row_base_ro = (torch.arange(B, device=dev) * gen).unsqueeze(1)
-        blk_ar = torch.arange(blk_len, device=dev).unsqueeze(0)
-        last_pos = None   # [B, num_transfer] positions unmasked in the previous step, ascending per row
+        get_metadata().running_seqs_tensor = st.seq_t
         for step in range(self.steps):
-            is_full = step < self.num_full_steps
-            pruned = (not is_full) and step > self.refresh_period and step % self.refresh_period != 0
-            if is_full:
-                set_context(True, cu_seqlens_q=cu_full, cu_seqlens_q_cpu=cu_full_l, cu_seqlens_k=cu_full, max_seqlen_q=L,
-                            max_seqlen_k=L, context_lens=lens_t, context_lens_cpu=[L] * B, total_seqlen=B * L,
-                            total_seqlen_k=B * L)
-                input_ids, positions = tokens.reshape(-1), pos_full
+            if step < self.num_full_steps:
+                kind = "full"
+            elif step > self.refresh_period and step % self.refresh_period != 0:
+                kind = "pruned"
             else:
-                idx_k = (last_pos + row_base_full).reshape(-1)
-                idx_q = (last_pos - P + row_base_ro).reshape(-1) if pruned else idx_k
-                set_context(False, cu_seqlens_q=cu_ro if pruned else cu_full,
-                            cu_seqlens_q_cpu=cu_ro_l if pruned else cu_full_l, cu_seqlens_k=cu_full,
-                            cu_promptlens=cu_prompt, cu_updatedlens=cu_sal, cu_salientlens=cu_sal,
-                            max_seqlen_q=gen if pruned else L, max_seqlen_k=L, idx_salient_row=idx_q,
-                            idx_salient_row_k=idx_k if pruned else None, idx_salient_row32=idx_q.to(torch.int32),
-                            max_salient_per_seq=num_transfer, context_lens=lens_t, context_lens_cpu=[L] * B,
-                            total_seqlen_k=B * L, total_seqlen=B * (gen if pruned else L))
-                input_ids = tokens[:, P:].reshape(-1) if pruned else tokens.reshape(-1)
-                positions = pos_ro if pruned else pos_full
-            hidden = self.model(input_ids, positions)
-            logits = self.model.compute_logits(hidden)
-            # confidence rule on the current block (ref: sampler.py:244-315), entirely on the device
-            blk = min(step // steps_per_block, gen // blk_len - 1)
-            start = P + blk * blk_len
-            rows = (row_base_ro + (start - P) if (not is_full and pruned) else row_base_full + start) + blk_ar
-            cand = logits.index_select(0, rows.reshape(-1)).float().view(B, blk_len, -1)
-            conf, tok = torch.softmax(cand, dim=-1).max(dim=-1)
-            still_masked = tokens[:, start:start + blk_len] == self.mask_id
-            conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
-            _, top_i = conf.topk(num_transfer, dim=-1)
-            top_i, _ = torch.sort(top_i, dim=-1)          # ascending rows for the kernels
-            last_pos = top_i + start
-            tokens.scatter_(1, last_pos, tok.gather(1, top_i))
-        out = tokens[:, P:].cpu()
+                kind = "sparse"
+            self._run_step(st, kind)
+        out = st.tokens[:, P:].cpu()
         io_bytes["d2h"] += out.numel() * 8
         return out.tolist()
 
-    def _unmask(self, seqs: List[Sequence], logits: torch.Tensor, ctx) -> int:
+    def _block_logits(self, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """Logits of the given query rows."""
+        if self.full_logits:
+            return self.model.compute_logits(hidden).index_select(0, rows)
+        return self.model.compute_logits(hidden.index_select(0, rows))
+
+    def _unmask(self, seqs: List[Sequence], hidden: torch.Tensor, ctx) -> int:
         B = len(seqs)
         gen = seqs[0].max_new_tokens
         steps_per_block = max(1, self.steps * self.block_length // gen)
@@ -250,7 +340,7 @@ class StepRunner:
         rows_t = torch.stack(rows)
         io_bytes["h2d"] += rows_t.numel() * rows_t.element_size()
         rows_t = rows_t.to(self.device)
-        cand = logits.index_select(0, rows_t.flatten()).float().view(B, self.block_length, -1)
+        cand = self._block_logits(hidden, rows_t.flatten()).float().view(B, self.block_length, -1)
         probs = torch.softmax(cand, dim=-1)
         conf, tok = probs.max(dim=-1)
         still_masked = torch.tensor(

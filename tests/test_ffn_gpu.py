@@ -127,6 +127,9 @@ def test_swiglu_ffn_scatters_into_cache_rows(cuda_device):
     (1024, 211, 200, 512, 256),    # device-side count below the bound
     (1024, 700, 100, 512, 256),    # hint too small: each CTA walks over several row tiles; split-K declined on the device
     (512, 26, 26, 4096, 256),      # few rows, few column tiles: split-K
+    (1024, 200, 128, 4096, 256),   # two live row tiles under a one-tile hint: fewer splits, chosen on the device
+    (1024, 400, 128, 4096, 1024),  # four live row tiles: the splits of the grid are all declined
+    (1024, 513, 128, 4096, 256),   # just above the split-K row limit
     (2048, 0, 64, 256, 128),       # nothing live
 ])
 def test_gathered_linear_device_count_hint_and_split_k(cuda_device, a_mode, bound, live, hint, k, n):

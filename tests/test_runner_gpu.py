@@ -22,7 +22,8 @@ def test_device_state_generation_equals_host_driven_generation(cuda_device):
     model.eval()
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(0, 900, (3, 40), generator=g).tolist()
-    sr = runner.StepRunner(model, shape.mask_token_id, block_length=8, steps=32, num_full_steps=4, refresh_period=4)
+    sr = runner.StepRunner(model, shape.mask_token_id, block_length=8, steps=32, num_full_steps=4, refresh_period=4,
+                           use_graphs=False)
     host = sr.generate(prompts, 32, device_state=False)
     dev = sr.generate(prompts, 32, device_state=True)
     assert _lib.load().dyllm_device_status() == 0
@@ -30,3 +31,17 @@ def test_device_state_generation_equals_host_driven_generation(cuda_device):
     assert all(t != shape.mask_token_id for row in dev for t in row)
     # deterministic across runs
     assert sr.generate(prompts, 32, device_state=True) == dev
+
+    # captured steps (CUDA graphs) replay the same launches: first generation warms and captures, the
+    # second one is replay only; launches are still accounted for
+    gr = runner.StepRunner(model, shape.mask_token_id, block_length=8, steps=32, num_full_steps=4, refresh_period=4,
+                           use_graphs=True)
+    first = gr.generate(prompts, 32)
+    assert len(gr._graphs) == 3
+    before = _lib.launch_count
+    second = gr.generate(prompts, 32)
+    assert _lib.launch_count > before
+    assert _lib.load().dyllm_device_status() == 0
+    assert first == dev and second == dev
+    other = torch.randint(0, 900, (3, 40), generator=g).tolist()
+    assert gr.generate(other, 32) == sr.generate(other, 32, device_state=True)
