@@ -10,13 +10,19 @@
 //           tiles, S2 = Q Ksal^T, P = exp2(S2*c - m*c) as bf16, O += P dVsal on the tensor cores;
 //   epilogue  new = C_old + O / rowsum, bf16 store, per-head partial cosine statistics from the fp32
 //           value before rounding.
-// A second small kernel adds the per-head partials in head order (run-to-run identical results),
-// overwrites the salient query rows with the exactly attended rows and writes the threshold mask.
+// Salient query rows take the exactly attended row (o_sal) as their new value in the same epilogue.
+// A second small kernel adds the per-head partials in head order (run-to-run identical results) and
+// writes the threshold mask.
 //
 // One CTA = (sequence, query head, 128 query rows); 10 warps: TMA producer, MMA issuer, 8 softmax warps
-// (two per 32-row lane quarter, each taking half of the columns).  96 KB of shared memory and 256
+// (two per 32-row lane quarter, each taking half of the columns).  104 KB of shared memory and 256
 // tensor-memory columns per CTA, so two CTAs share an SM and one CTA's tensor-core work overlaps the
 // other's exponentials.
+//
+// Pass B works on the salient keys rounded up to a multiple of 16 (the MMA shapes are chosen at run
+// time).  With at most 16 salient keys in the sequence (the common case) their K and dV rows are gathered
+// into a small dedicated buffer while the first tiles are still in flight, so pass B starts as soon as
+// pass A ends.
 #include "common.cuh"
 
 namespace dyllm {
@@ -29,7 +35,10 @@ constexpr int kBKeys = 128;      // keys per tile
 constexpr int kAttnThreads = 320;          // TMA producer warp, MMA warp, eight softmax warps
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one [128][128] bf16 tile = two [128][64] swizzled halves
 constexpr uint32_t kHalfBytes = 128 * 64 * 2;
-constexpr uint32_t kAttnSmem = 3 * kTileBytes + 1024;
+constexpr int kFastSal = 16;                      // salient keys served by the early gather
+constexpr uint32_t kSalHalfBytes = kFastSal * 128;   // one 64-column half of a 16-row tile
+constexpr uint32_t kSalBytes = 2 * kSalHalfBytes;
+constexpr uint32_t kAttnSmem = 3 * kTileBytes + 2 * kSalBytes + 1024;
 // Tensor memory: two S buffers (columns 0..127 and 128..255) during pass A, so that the product of
 // key tile t+1 runs while tile t is being reduced; in pass B the second buffer holds O.
 constexpr uint32_t kAttnTmemCols = 256;
@@ -51,11 +60,12 @@ struct AttnParams {
   const int32_t* cu_k;           // [B + 1]
   const int32_t* cu_sal;         // [B + 1] prefix counts of the salient key list
   const int32_t* idx_k;          // salient key rows (K space), ascending, grouped by sequence
-  int H, Hkv, Tq, Tk, n_qtiles;
+  int H, Hkv, Tq, Tk, n_qtiles, batch, num_items;
   float scale_log2;              // log2(e) / sqrt(D)
   int v_mn_major;                // 1: dV tile kept [keys][d] (MN-major operand); 0: transposed while gathering
   int v_compact;                 // 1: v holds one row per salient key, in list order; 0: v is [Tk, Hkv, D]
-  unsigned long long* trace;     // optional [256][8] phase timestamps (ns) of the first 256 CTAs; null = off
+  unsigned long long* trace;     // optional [1024][16] phase timestamps (ns) of 1024 CTAs from trace_first on; null = off
+  unsigned trace_first;
   int* status_word;
 };
 
@@ -67,8 +77,9 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 #define DYLLM_TRACE(slot)                                                  \
   do {                                                                     \
-    if (p.trace && blockIdx.x < 256 && threadIdx.x == 64)                  \
-      p.trace[blockIdx.x * 8 + (slot)] = global_ns();                      \
+    if (p.trace && item >= static_cast<int>(p.trace_first) && item < static_cast<int>(p.trace_first) + 1024 && \
+        threadIdx.x == 64)                                                 \
+      p.trace[(item - p.trace_first) * 16 + (slot)] = global_ns();         \
   } while (0)
 
 __device__ __forceinline__ float ex2(float x) {
@@ -77,50 +88,124 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Two-wide fp32 arithmetic (one instruction per pair) and a three-input maximum: the softmax warps are
+// bound by instruction issue and by the exponential unit, not by arithmetic throughput.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+      " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n"
+      " add.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// (2^x0, 2^x1) through the two-wide half-precision exponential: one pass of the exponential unit for
+// two values.  Used for the row sums of pass A only (arguments <= 0; the relative error of a term is
+// below 3e-3 and far smaller for the terms near the maximum that dominate the sum); the probabilities
+// that enter the P dV product are computed in fp32.
+__device__ __forceinline__ float2 ex2_pair_f16(float x0, float x1) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(x1), "f"(x0));
+  asm("ex2.approx.f16x2 %0, %0;" : "+r"(h));
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+constexpr bool kPassAHalfExp = false;   // measured: no faster than fp32 exponentials here
+
+// One unit of work: (sequence, query head, tile of 128 query rows).
+struct AttnItem {
+  int h, hk, sal_begin, n_sal, q_end, q0, k_begin, len_k, num_kt, num_st;
+  int64_t c_delta;   // C_old row of query row r: r + c_delta (cache-resident context)
+  bool tile_tma;     // the tile lies completely inside the sequence: context through shared memory
+  bool fast;         // at most kFastSal salient keys: gathered early into their own buffers
+};
+
+// Decodes work item `item`; false when it holds no query rows.  The delta kernel orders items
+// (sequence, head, tile) so that the tiles of one head run at the same time and share its keys in L2;
+// the EXACT kernel puts the tile index first, because most sequences fill only their first tile and
+// items are dealt out to CTAs round-robin.
+template <bool EXACT>
+__device__ __forceinline__ bool decode_item(const AttnParams& p, int item, AttnItem& it) {
+  int q_tile, b;
+  if (EXACT) {
+    const int bh = p.batch * p.H;
+    q_tile = item / bh;
+    it.h = item % p.H;
+    b = (item % bh) / p.H;
+  } else {
+    q_tile = item % p.n_qtiles;
+    it.h = (item / p.n_qtiles) % p.H;
+    b = item / (p.n_qtiles * p.H);
+  }
+  it.sal_begin = p.cu_sal[b];
+  it.n_sal = p.cu_sal[b + 1] - it.sal_begin;
+  const int q_begin = EXACT ? 0 : p.cu_q[b];
+  it.q_end = EXACT ? it.n_sal : p.cu_q[b + 1];   // EXACT: rows are positions in the salient list
+  it.q0 = q_begin + q_tile * kBQ;
+  if (it.q0 >= it.q_end)
+    return false;
+  it.k_begin = p.cu_k[b];
+  it.len_k = p.cu_k[b + 1] - it.k_begin;
+  it.num_kt = (it.len_k + kBKeys - 1) / kBKeys;
+  it.hk = it.h / (p.H / p.Hkv);
+  it.num_st = EXACT ? it.num_kt : (it.n_sal + kBKeys - 1) / kBKeys;   // tiles of pass B
+  it.c_delta = 0;
+  if (!EXACT && p.c_seq_starts)
+    it.c_delta = p.c_seq_starts[p.c_seq_ids[b]] + (it.len_k - (it.q_end - q_begin)) - q_begin;
+  it.tile_tma = !EXACT && it.q0 + kBQ <= it.q_end;
+  it.fast = !EXACT && p.v_mn_major != 0 && it.n_sal > 0 && it.n_sal <= kFastSal;
+  return true;
+}
+
 // EXACT = false: the delta attention described at the top of this file.
 // EXACT = true: plain softmax attention of the salient query rows against the full K / V of their
 // sequence, o_sal[i] = softmax(q[idx_q[i]] K^T / sqrt(D)) V: the query tile is gathered through idx_q,
 // pass B walks over all key tiles (K and V tiles by TMA; V is used as loaded, as an MN-major operand)
 // and the epilogue stores O / rowsum.
+//
+// The kernel is persistent: the grid holds as many CTAs as the device runs at once and CTA i takes the
+// work items i, i + gridDim.x, ...  Tensor memory and the barriers live for the whole kernel; every
+// role counts how often it has used each barrier to know the phase it waits for.
 template <bool EXACT>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
-  const int q_tile = blockIdx.x % p.n_qtiles;
-  const int h = (blockIdx.x / p.n_qtiles) % p.H;
-  const int b = blockIdx.x / (p.n_qtiles * p.H);
-  const int sal_begin = p.cu_sal[b];
-  const int n_sal = p.cu_sal[b + 1] - sal_begin;
-  const int q_begin = EXACT ? 0 : p.cu_q[b];
-  const int q_end = EXACT ? n_sal : p.cu_q[b + 1];   // EXACT: rows are positions in the salient list
-  const int q0 = q_begin + q_tile * kBQ;
-  if (q0 >= q_end)
-    return;
-  const int k_begin = p.cu_k[b], k_end = p.cu_k[b + 1];
-  const int len_k = k_end - k_begin;
-  const int num_kt = (len_k + kBKeys - 1) / kBKeys;
-  const int hk = h / (p.H / p.Hkv);
-  const int num_st = EXACT ? num_kt : (n_sal + kBKeys - 1) / kBKeys;   // tiles of pass B
-  // C_old row of query row r: r + c_delta (cache-resident context: the last len_q rows of the sequence)
-  int64_t c_delta = 0;
-  if (!EXACT && p.c_seq_starts)
-    c_delta = p.c_seq_starts[p.c_seq_ids[b]] + (len_k - (q_end - q_begin)) - q_begin;
-  const bool v_mn_major = EXACT ? true : (p.v_mn_major != 0);
-
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_out,
+                 const __grid_constant__ CUtensorMap tmap_c, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;                      // Q tile
   uint8_t* kv_smem0 = smem + kTileBytes;       // K stage 0 / gathered Ksal, later P
-  uint8_t* kv_smem1 = smem + 2 * kTileBytes;   // K stage 1 / gathered dV
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], b_full, p_full, pv_done, a_done;
+  uint8_t* kv_smem1 = smem + 2 * kTileBytes;   // K stage 1 / gathered dV, later the context tile
+  uint8_t* ks_smem = smem + 3 * kTileBytes;    // early-gathered salient K rows (at most kFastSal)
+  uint8_t* dvs_smem = ks_smem + kSalBytes;     // early-gathered dV rows
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], b_full, p_full, pv_done, a_done, c_full;
+  // delta kernel: buffers handed back to the producer / the MMA warp while the item is still in its epilogue
+  __shared__ uint64_t q_free, kv0_free, kv1_free, o_free;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_src[128];        // source row of each gather slot (-1 = none)
   __shared__ float2 s_ml[2][128];   // (max, sum) of the two column halves of each query row
   __shared__ float4 s_st[128];      // statistics of the second half of each row
+  __shared__ uint16_t s_sal_pos[128];  // 1 + position in the sequence's salient list of this query row, 0 = not salient
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const bool v_mn_major = EXACT ? true : (p.v_mn_major != 0);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -137,6 +222,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(&p_full, 256);
     mbar_init(&pv_done, 1);
     mbar_init(&a_done, 1);
+    mbar_init(&c_full, 1);
+    mbar_init(&q_free, 1);
+    mbar_init(&kv0_free, 1);
+    mbar_init(&kv1_free, 1);
+    mbar_init(&o_free, 256);
     fence_mbar_init();
     if (!EXACT)
       tma_prefetch_desc(&tmap_q);
@@ -155,103 +245,171 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const uint32_t tmem_o = tmem_slot + 128;
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- producer: Q once, K tiles
-    if (!EXACT && lane == 0) {
-      mbar_arrive_expect_tx(&q_full, kTileBytes);
-      tma_load_2d(q_smem, &tmap_q, &q_full, h * kD, q0);
-      tma_load_2d(q_smem + kHalfBytes, &tmap_q, &q_full, h * kD + 64, q0);
-    }
-    for (int kt = 0; kt < num_kt; ++kt) {
-      const int s = kt & 1;
-      mbar_wait(&k_empty[s], ((kt >> 1) & 1) ^ 1, &abort_flag, p.status_word, 301);
+    // ---------------------------------------------------------------- producer: Q (delta kernel), K tiles,
+    // and for the EXACT kernel the K / V tiles of pass B
+    int n_items = 0;            // items started so far
+    int kuse[2] = {0, 0};       // loads issued into each K stage
+    int n_pv = 0;               // P V products waited for (EXACT)
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+      AttnItem it;
+      if (!decode_item<EXACT>(p, item, it))
+        continue;
+      // Delta kernel: the softmax warps hand the buffers back one by one while the previous item is still
+      // in its epilogue (Q after the last product with Q, K stage 0 after the last P dV product, K stage 1
+      // after the stores of the context tile), so the first tiles of this item are in flight early.
+      // EXACT kernel: its last P V product was awaited below.
+      const uint32_t prev = (n_items - 1) & 1;
+      if (!EXACT && n_items > 0)
+        mbar_wait(&q_free, prev, &abort_flag, p.status_word, 314);
       if (lane == 0) {
-        uint8_t* dst = s ? kv_smem1 : kv_smem0;
-        mbar_arrive_expect_tx(&k_full[s], kTileBytes);
-        tma_load_2d(dst, &tmap_k, &k_full[s], hk * kD, k_begin + kt * kBKeys);
-        tma_load_2d(dst + kHalfBytes, &tmap_k, &k_full[s], hk * kD + 64, k_begin + kt * kBKeys);
+        if (!EXACT) {
+          mbar_arrive_expect_tx(&q_full, kTileBytes);
+          tma_load_2d(q_smem, &tmap_q, &q_full, it.h * kD, it.q0);
+          tma_load_2d(q_smem + kHalfBytes, &tmap_q, &q_full, it.h * kD + 64, it.q0);
+          // the query tile of this CTA's next item
+          AttnItem nx;
+          const int next = item + gridDim.x;
+          if (next < p.num_items && decode_item<EXACT>(p, next, nx)) {
+            tma_prefetch_2d(&tmap_q, nx.h * kD, nx.q0);
+            tma_prefetch_2d(&tmap_q, nx.h * kD + 64, nx.q0);
+          }
+        } else {
+          // the value tiles are read once, late, and nothing else has touched them: bring them into L2 now
+          for (int st = 0; st < it.num_st; ++st) {
+            tma_prefetch_2d(&tmap_v, it.hk * kD, it.k_begin + st * kBKeys);
+            tma_prefetch_2d(&tmap_v, it.hk * kD + 64, it.k_begin + st * kBKeys);
+          }
+        }
       }
-      __syncwarp();
-    }
-    if (EXACT) {
-      // pass B: K tile into buffer 0 and V tile into buffer 1 once both are free
-      for (int st = 0; st < num_st; ++st) {
-        if (st == 0)
-          mbar_wait(&a_done, 0, &abort_flag, p.status_word, 311);
-        else
-          mbar_wait(&pv_done, (st - 1) & 1, &abort_flag, p.status_word, 312);
+      for (int kt = 0; kt < it.num_kt; ++kt) {
+        const int s = kt & 1;
+        const int u = kuse[s]++;
+        if (!EXACT && n_items > 0 && kt < 2)
+          mbar_wait(kt == 0 ? &kv0_free : &kv1_free, prev, &abort_flag, p.status_word, 316);
+        mbar_wait(&k_empty[s], (u & 1) ^ 1, &abort_flag, p.status_word, 301);
         if (lane == 0) {
-          mbar_arrive_expect_tx(&b_full, 2 * kTileBytes);
-          tma_load_2d(kv_smem0, &tmap_k, &b_full, hk * kD, k_begin + st * kBKeys);
-          tma_load_2d(kv_smem0 + kHalfBytes, &tmap_k, &b_full, hk * kD + 64, k_begin + st * kBKeys);
-          tma_load_2d(kv_smem1, &tmap_v, &b_full, hk * kD, k_begin + st * kBKeys);
-          tma_load_2d(kv_smem1 + kHalfBytes, &tmap_v, &b_full, hk * kD + 64, k_begin + st * kBKeys);
+          uint8_t* dst = s ? kv_smem1 : kv_smem0;
+          mbar_arrive_expect_tx(&k_full[s], kTileBytes);
+          tma_load_2d(dst, &tmap_k, &k_full[s], it.hk * kD, it.k_begin + kt * kBKeys);
+          tma_load_2d(dst + kHalfBytes, &tmap_k, &k_full[s], it.hk * kD + 64, it.k_begin + kt * kBKeys);
         }
         __syncwarp();
       }
+      if (EXACT) {
+        // pass B: K tile into buffer 0 and V tile into buffer 1 once both are free
+        for (int st = 0; st < it.num_st; ++st) {
+          if (st == 0)
+            mbar_wait(&a_done, n_items & 1, &abort_flag, p.status_word, 311);
+          else
+            mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 312);
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&b_full, 2 * kTileBytes);
+            tma_load_2d(kv_smem0, &tmap_k, &b_full, it.hk * kD, it.k_begin + st * kBKeys);
+            tma_load_2d(kv_smem0 + kHalfBytes, &tmap_k, &b_full, it.hk * kD + 64, it.k_begin + st * kBKeys);
+            tma_load_2d(kv_smem1, &tmap_v, &b_full, it.hk * kD, it.k_begin + st * kBKeys);
+            tma_load_2d(kv_smem1 + kHalfBytes, &tmap_v, &b_full, it.hk * kD + 64, it.k_begin + st * kBKeys);
+          }
+          __syncwarp();
+        }
+        if (it.num_st > 0)   // the last product has read both buffers: the next item may load into them
+          mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 315);
+      } else if (n_items > 0 && it.num_kt < 2) {
+        mbar_wait(&kv1_free, prev, &abort_flag, p.status_word, 317);   // keep in step with every phase
+      }
+      ++n_items;
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
     const uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, v_mn_major ? 1 : 0);
     const uint32_t q_addr = smem_u32(q_smem);
-    mbar_wait(&q_full, 0, &abort_flag, p.status_word, 302);
+    int n_items = 0;
+    int kuse[2] = {0, 0};   // K stages consumed
     int uses[2] = {0, 0};   // how often each S buffer has been handed to the softmax warps
-    for (int t = 0; t < num_kt + num_st; ++t) {
-      const bool sal_tile = t >= num_kt;
-      const int st = t - num_kt;
-      const int sb = sal_tile ? 0 : (t & 1);   // pass B keeps to buffer 0: buffer 1 holds O then
-      const int use = uses[sb]++;
-      const uint32_t tmem_s = tmem_s0 + sb * 128;
-      uint32_t kb_addr;
-      if (!sal_tile) {
-        const int s = t & 1;
-        mbar_wait(&k_full[s], (t >> 1) & 1, &abort_flag, p.status_word, 303);
-        kb_addr = smem_u32(s ? kv_smem1 : kv_smem0);
-      } else {
-        mbar_wait(&b_full, st & 1, &abort_flag, p.status_word, 304);
-        kb_addr = smem_u32(kv_smem0);
-      }
-      mbar_wait(&s_empty[sb], (use & 1) ^ 1, &abort_flag, p.status_word, 305);
-      tc_fence_after_sync();
-      if (lane == 0) {
-        // S = Q K^T: contraction over d in two swizzled halves of 64, four K = 16 steps each
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const uint64_t a_desc = umma_smem_desc_sw128(q_addr + half * kHalfBytes, 16, 1024);
-          const uint64_t b_desc = umma_smem_desc_sw128(kb_addr + half * kHalfBytes, 16, 1024);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem_s, a_desc + 2 * kk, b_desc + 2 * kk, idesc_qk, (half | kk) != 0 ? 1u : 0u);
+    int n_sal_tiles = 0;    // pass-B tiles so far (phases of b_full and p_full)
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+      AttnItem it;
+      if (!decode_item<EXACT>(p, item, it))
+        continue;
+      // pass B of the delta kernel: keys of the tile rounded up to the MMA granularity
+      const uint32_t k_half_stride = it.fast ? kSalHalfBytes : kHalfBytes;
+      mbar_wait(&q_full, n_items & 1, &abort_flag, p.status_word, 302);
+      bool o_waited = EXACT || n_items == 0;
+      for (int t = 0; t < it.num_kt + it.num_st; ++t) {
+        const bool sal_tile = t >= it.num_kt;
+        const int st = t - it.num_kt;
+        const int sb = sal_tile ? 0 : (t & 1);   // pass B keeps to buffer 0: buffer 1 holds O then
+        const int use = uses[sb]++;
+        if (!o_waited && (sb == 1 || sal_tile)) {
+          // columns 128..255 still hold the previous item's O until its epilogue has read them
+          mbar_wait(&o_free, (n_items - 1) & 1, &abort_flag, p.status_word, 318);
+          o_waited = true;
         }
-        if (!sal_tile)
-          umma_commit(&k_empty[t & 1]);
-        umma_commit(&s_full[sb]);
-        if (EXACT && t == num_kt - 1)
-          umma_commit(&a_done);
-      }
-      __syncwarp();
-      if (sal_tile) {
-        // O += P dV over the 128 (zero padded) salient keys of this tile
-        mbar_wait(&p_full, st & 1, &abort_flag, p.status_word, 306);
+        const uint32_t tmem_s = tmem_s0 + sb * 128;
+        uint32_t kb_addr;
+        uint32_t idesc_s = idesc_qk;
+        int n16 = kBKeys;
+        if (!sal_tile) {
+          const int s = t & 1;
+          mbar_wait(&k_full[s], (kuse[s]++) & 1, &abort_flag, p.status_word, 303);
+          kb_addr = smem_u32(s ? kv_smem1 : kv_smem0);
+        } else {
+          mbar_wait(&b_full, n_sal_tiles & 1, &abort_flag, p.status_word, 304);
+          kb_addr = smem_u32(it.fast ? ks_smem : kv_smem0);
+          if (!EXACT) {
+            n16 = (min(kBKeys, it.n_sal - st * kBKeys) + 15) & ~15;
+            idesc_s = umma_idesc_bf16(128, n16, 0, 0);
+          }
+        }
+        mbar_wait(&s_empty[sb], (use & 1) ^ 1, &abort_flag, p.status_word, 305);
         tc_fence_after_sync();
         if (lane == 0) {
-          const uint32_t p_addr = smem_u32(kv_smem0);
-          const uint32_t v_addr = smem_u32(kv_smem1);
+          // S = Q K^T: contraction over d in two swizzled halves of 64, four K = 16 steps each
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t a_desc =
-                umma_smem_desc_sw128(p_addr + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16, 1024);
-            uint64_t b_desc;
-            if (v_mn_major)  // [keys][d]: 16 keys = 2048 bytes per step, d halves 16 KB apart
-              b_desc = umma_smem_desc_sw128(v_addr + kk * 2048, kHalfBytes, 1024);
-            else               // [d][keys]: key halves 16 KB apart, 32 bytes per step inside a half
-              b_desc = umma_smem_desc_sw128(v_addr + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16, 1024);
-            umma_ss(tmem_o, a_desc, b_desc, idesc_pv, (st | kk) != 0 ? 1u : 0u);
+          for (int half = 0; half < 2; ++half) {
+            const uint64_t a_desc = umma_smem_desc_sw128(q_addr + half * kHalfBytes, 16, 1024);
+            const uint64_t b_desc =
+                umma_smem_desc_sw128(kb_addr + half * (sal_tile ? k_half_stride : kHalfBytes), 16, 1024);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ss(tmem_s, a_desc + 2 * kk, b_desc + 2 * kk, idesc_s, (half | kk) != 0 ? 1u : 0u);
           }
-          umma_commit(&pv_done);
+          if (!sal_tile)
+            umma_commit(&k_empty[t & 1]);
+          umma_commit(&s_full[sb]);
+          if (EXACT && t == it.num_kt - 1)
+            umma_commit(&a_done);
         }
         __syncwarp();
+        if (sal_tile) {
+          // O += P dV over the salient keys of this tile (zero padded to n16)
+          mbar_wait(&p_full, n_sal_tiles & 1, &abort_flag, p.status_word, 306);
+          ++n_sal_tiles;
+          tc_fence_after_sync();
+          if (lane == 0) {
+            const uint32_t p_addr = smem_u32(kv_smem0);
+            const uint32_t v_addr = smem_u32(it.fast ? dvs_smem : kv_smem1);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              if (kk >= n16 / 16)
+                break;
+              const uint64_t a_desc =
+                  umma_smem_desc_sw128(p_addr + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16, 1024);
+              uint64_t b_desc;
+              if (v_mn_major)  // [keys][d]: 16 keys = 2048 bytes per step, d halves one half-tile apart
+                b_desc = umma_smem_desc_sw128(v_addr + kk * 2048, k_half_stride, 1024);
+              else               // [d][keys]: key halves 16 KB apart, 32 bytes per step inside a half
+                b_desc = umma_smem_desc_sw128(v_addr + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 16, 1024);
+              umma_ss(tmem_o, a_desc, b_desc, idesc_pv, (st | kk) != 0 ? 1u : 0u);
+            }
+            umma_commit(&pv_done);
+          }
+          __syncwarp();
+        }
       }
+      if (!o_waited)
+        mbar_wait(&o_free, (n_items - 1) & 1, &abort_flag, p.status_word, 319);   // keep in step
+      ++n_items;
     }
   } else {
     // ---------------------------------------------------------------- softmax / gather / epilogue
@@ -265,270 +423,404 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t t_lane = static_cast<uint32_t>(qd * 32) << 16;
     const int col0 = half * 64;
     const float c = p.scale_log2;
-    float m = kNegBig, l = 0.f;
-    DYLLM_TRACE(0);
+    int uses[2] = {0, 0};   // S buffers read so far
+    int n_pv = 0;           // P V products waited for
+    int n_c = 0;            // context tiles loaded
+    for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
+      AttnItem it;
+      if (!decode_item<EXACT>(p, item, it))
+        continue;
+      const int h = it.h, hk = it.hk, q0 = it.q0, q_end = it.q_end, sal_begin = it.sal_begin, n_sal = it.n_sal;
+      const int num_kt = it.num_kt, num_st = it.num_st, len_k = it.len_k;
+      const int64_t c_delta = it.c_delta;
+      const bool tile_tma = it.tile_tma, fast = it.fast;
+      float m = kNegBig, l = 0.f;
+      DYLLM_TRACE(0);
+      if (p.trace && item >= static_cast<int>(p.trace_first) && item < static_cast<int>(p.trace_first) + 1024 &&
+          threadIdx.x == 64) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.trace[(item - p.trace_first) * 16 + 14] = smid;
+      }
 
-    if (!EXACT && q0 + row < q_end) {
-      // bring this thread's half of the C_old row (128 bytes) into L2 now; the epilogue reads it much later
-      const char* crow =
-          reinterpret_cast<const char*>(p.c_old + ((q0 + row + c_delta) * p.H + h) * kD + col0);
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(crow));
-    }
-    // source rows of the first gather (salient key rows, or the query rows of the EXACT variant)
-    if (half == 0) {
-      int src = -1;
-      if (EXACT) {
-        if (q0 + row < q_end)
-          src = p.idx_q[sal_begin + q0 + row];
-      } else if (row < n_sal) {
-        src = p.idx_k[sal_begin + row];
+      if (!EXACT && q0 + row < q_end) {
+        // bring this thread's half of the C_old row (128 bytes) into L2 now; the epilogue reads it much later
+        const char* crow =
+            reinterpret_cast<const char*>(p.c_old + ((q0 + row + c_delta) * p.H + h) * kD + col0);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(crow));
       }
-      s_src[row] = src;
-    }
-    if (EXACT) {
-      // cooperative gather of the query rows (zeros past the list) into the swizzled Q tile
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int item = it * 256 + st_tid;
-        const int r = item >> 4, ch = item & 15;
-        const int src = s_src[r];
-        const uint4 qv = src >= 0
-            ? __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(src) * p.H + h) * kD) + ch) : zero;
-        *reinterpret_cast<uint4*>(q_smem + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = qv;
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&q_full);
-    }
-
-    // pass A: running maximum and sum over this thread's half of the columns of every key tile
-    int uses[2] = {0, 0};
-    for (int kt = 0; kt < num_kt; ++kt) {
-      const int sb = kt & 1;
-      const int use = uses[sb]++;
-      const uint32_t tmem_s = tmem_s0 + sb * 128;
-      mbar_wait(&s_full[sb], use & 1, &abort_flag, p.status_word, 307);
-      tc_fence_after_sync();
-      if (kt == 0)
-        DYLLM_TRACE(7);
-      const int valid = len_k - kt * kBKeys;   // keys of this tile that belong to the sequence
-#pragma unroll 1
-      for (int cc = 0; cc < 64; cc += 32) {
-        const int c0 = col0 + cc;
-        uint32_t sr[32];
-        tmem_ld_32x32(tmem_s + t_lane + c0, sr);
-        tmem_ld_wait();
-        if (cc == 32) {  // last chunk read: the MMA warp may overwrite this S buffer
-          tc_fence_before_sync();
-          mbar_arrive(&s_empty[sb]);
+      // a warp whose 32 query rows all lie past the end of the sequence keeps the barrier protocol going
+      // but computes nothing
+      const bool warp_live = q0 + qd * 32 < q_end;
+      // source rows of the first gather (salient key rows, or the query rows of the EXACT variant)
+      if (half == 0) {
+        int src = -1;
+        if (EXACT) {
+          if (q0 + row < q_end)
+            src = p.idx_q[sal_begin + q0 + row];
+        } else if (row < n_sal) {
+          src = p.idx_k[sal_begin + row];
         }
-        float cmax = kNegBig;
-        if (valid >= kBKeys) {   // whole tile inside the sequence: no masking
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            cmax = fmaxf(cmax, __uint_as_float(sr[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float s = __uint_as_float(sr[i]);
-            s = (c0 + i < valid) ? s : kNegBig;
-            sr[i] = __float_as_uint(s);
-            cmax = fmaxf(cmax, s);
-          }
-        }
-        const float m_new = fmaxf(m, cmax);
-        const float mc = m_new * c;
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          sum += ex2(fmaf(__uint_as_float(sr[i]), c, -mc));
-        l = l * ex2((m - m_new) * c) + sum;
-        m = m_new;
+        s_src[row] = src;
+        s_sal_pos[row] = 0;
       }
-    }
-    // merge the two column halves of each row: m = max, l rescaled to the common maximum
-    s_ml[half][row] = make_float2(m, l);
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    {
-      const float2 other = s_ml[half ^ 1][row];
-      const float m_all = fmaxf(m, other.x);
-      l = l * ex2((m - m_all) * c) + other.y * ex2((other.x - m_all) * c);
-      m = m_all;
-    }
-
-    // pass B: salient keys (EXACT: all keys again, with their values)
-    DYLLM_TRACE(1);
-    const float mc = m * c;
-    for (int st = 0; st < num_st; ++st) {
-      // The buffers are free for tile 0 once the last Q K^T product is complete: s_full of the last
-      // key tile was observed above and is committed after every earlier MMA.  Later tiles wait for the
-      // previous P dV product.
-      if (!EXACT && st > 0) {
-        mbar_wait(&pv_done, (st - 1) & 1, &abort_flag, p.status_word, 308);
-        if (half == 0) {
-          const int j = st * kBKeys + row;
-          s_src[row] = j < n_sal ? p.idx_k[sal_begin + j] : -1;
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-      }
-      const int n_tile = min(kBKeys, (EXACT ? len_k : n_sal) - st * kBKeys);
       if (!EXACT) {
-        // cooperative gather: 128 slots x 16 chunks of the K rows and of the dV rows, zeros past the list
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        // mark the query rows of this tile that are salient (they take the exactly attended values)
+        for (int j = st_tid; j < n_sal; j += 256) {
+          const int rr = p.idx_q[sal_begin + j] - q0;
+          if (rr >= 0 && rr < kBQ)
+            s_sal_pos[rr] = static_cast<uint16_t>(j + 1);
+        }
+        if (fast) {
+          // early gather: 16 slots x 16 chunks of 16 bytes, one per thread, zeros past the list
+          const int r = st_tid >> 4, ch = st_tid & 15;
+          const int src = s_src[r];
+          const uint4 zero = make_uint4(0, 0, 0, 0);
+          const uint4 kv = src >= 0
+              ? __ldg(reinterpret_cast<const uint4*>(p.k + (static_cast<int64_t>(src) * p.Hkv + hk) * kD) + ch) : zero;
+          const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + r) : src;
+          const uint4 vv = src >= 0
+              ? __ldg(reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD) + ch) : zero;
+          *reinterpret_cast<uint4*>(ks_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = kv;
+          *reinterpret_cast<uint4*>(dvs_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = vv;
+          fence_proxy_async_smem();
+          mbar_arrive(&b_full);
+        }
+      }
+      if (EXACT) {
+        // cooperative gather of the query rows (zeros past the list) into the swizzled Q tile
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int item = it * 256 + st_tid;
-          const int r = item >> 4, ch = item & 15;
+        for (int gi = 0; gi < 8; ++gi) {
+          const int slot = gi * 256 + st_tid;
+          const int r = slot >> 4, ch = slot & 15;
           const int src = s_src[r];
-          const bool have = src >= 0;
-          const uint4 kv = have
-              ? __ldg(reinterpret_cast<const uint4*>(p.k + (static_cast<int64_t>(src) * p.Hkv + hk) * kD) + ch) : zero;
-          *reinterpret_cast<uint4*>(kv_smem0 + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = kv;
-          const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + st * kBKeys + r) : src;
-          const uint4 vv = have
-              ? __ldg(reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD) + ch) : zero;
-          if (v_mn_major) {
-            *reinterpret_cast<uint4*>(kv_smem1 + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = vv;
-          } else {
-            // transposed tile [d][key]: element (d, key = r)
-            uint8_t* base = kv_smem1 + (r >> 6) * kHalfBytes + ((r & 7) << 1);
-            const uint32_t key_chunk = (r & 63) >> 3;
-            const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
+          const uint4 qv = src >= 0
+              ? __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(src) * p.H + h) * kD) + ch) : zero;
+          *reinterpret_cast<uint4*>(q_smem + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = qv;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&q_full);
+      }
+
+      // pass A: running maximum and sum over this thread's half of the columns of every key tile
+      for (int kt = 0; kt < num_kt; ++kt) {
+        const int sb = kt & 1;
+        const int use = uses[sb]++;
+        const uint32_t tmem_s = tmem_s0 + sb * 128;
+        mbar_wait(&s_full[sb], use & 1, &abort_flag, p.status_word, 307);
+        tc_fence_after_sync();
+        if (kt == 0)
+          DYLLM_TRACE(7);
+        const int valid = len_k - kt * kBKeys;   // keys of this tile that belong to the sequence
+        if (!warp_live) {
+          tc_fence_before_sync();
+          mbar_arrive(&s_empty[sb]);
+          continue;
+        }
+#pragma unroll 1
+        for (int cc = 0; cc < 64; cc += 32) {
+          const int c0 = col0 + cc;
+          uint32_t sr[32];
+          tmem_ld_32x32(tmem_s + t_lane + c0, sr);
+          tmem_ld_wait();
+          if (cc == 32) {  // last chunk read: the MMA warp may overwrite this S buffer
+            tc_fence_before_sync();
+            mbar_arrive(&s_empty[sb]);
+          }
+          if (valid < kBKeys) {   // keys past the end of the sequence
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const uint32_t d = ch * 8 + i;
-              *reinterpret_cast<uint16_t*>(base + d * 128u + ((key_chunk ^ (d & 7u)) << 4)) = e[i];
+            for (int i = 0; i < 32; ++i)
+              if (c0 + i >= valid)
+                sr[i] = __float_as_uint(kNegBig);
+          }
+          float cmax = kNegBig;
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            cmax = fmax3(cmax, __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+          const float m_new = fmaxf(m, cmax);
+          const float mc = m_new * c;
+          const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
+          float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const float2 x0 =
+                ffma2(make_float2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), c2, nmc2);
+            const float2 x1 =
+                ffma2(make_float2(__uint_as_float(sr[2 * i + 2]), __uint_as_float(sr[2 * i + 3])), c2, nmc2);
+            if (kPassAHalfExp) {
+              acc0 = fadd2(acc0, ex2_pair_f16(x0.x, x0.y));
+              acc1 = fadd2(acc1, ex2_pair_f16(x1.x, x1.y));
+            } else {
+              acc0 = fadd2(acc0, make_float2(ex2(x0.x), ex2(x0.y)));
+              acc1 = fadd2(acc1, make_float2(ex2(x1.x), ex2(x1.y)));
+            }
+          }
+          const float sum = (acc0.x + acc1.x) + (acc0.y + acc1.y);
+          l = l * ex2((m - m_new) * c) + sum;
+          m = m_new;
+        }
+      }
+      // merge the two column halves of each row: m = max, l rescaled to the common maximum
+      s_ml[half][row] = make_float2(m, l);
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      {
+        const float2 other = s_ml[half ^ 1][row];
+        const float m_all = fmaxf(m, other.x);
+        l = l * ex2((m - m_all) * c) + other.y * ex2((other.x - m_all) * c);
+        m = m_all;
+      }
+
+      // pass B: salient keys (EXACT: all keys again, with their values)
+      DYLLM_TRACE(1);
+      const float mc = m * c;
+      // K stage 1 is not used by pass B when the salient rows were gathered early (or there are none):
+      // the previous context tile can already come in.  Otherwise it follows the last P dV product.
+      const bool c_early = fast || num_st == 0;
+      if (!EXACT && st_tid == 0) {
+        if (tile_tma && c_early) {
+          mbar_arrive_expect_tx(&c_full, kTileBytes);
+          tma_load_2d(kv_smem1, &tmap_c, &c_full, h * kD, static_cast<int>(q0 + c_delta));
+          tma_load_2d(kv_smem1 + kHalfBytes, &tmap_c, &c_full, h * kD + 64, static_cast<int>(q0 + c_delta));
+        }
+        if (num_st == 0) {   // no product reads Q or P any more
+          mbar_arrive(&q_free);
+          mbar_arrive(&kv0_free);
+          if (!tile_tma)
+            mbar_arrive(&kv1_free);
+        }
+      }
+      for (int st = 0; st < num_st; ++st) {
+        // The buffers are free for tile 0 once the last Q K^T product is complete: s_full of the last
+        // key tile was observed above and is committed after every earlier MMA.  Later tiles wait for the
+        // previous P dV product.
+        if (!EXACT && st > 0) {
+          mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 308);
+          if (half == 0) {
+            const int j = st * kBKeys + row;
+            s_src[row] = j < n_sal ? p.idx_k[sal_begin + j] : -1;
+          }
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        if (EXACT && st > 0)
+          mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 308);
+        const int n_tile = min(kBKeys, (EXACT ? len_k : n_sal) - st * kBKeys);
+        const int n16 = EXACT ? kBKeys : (n_tile + 15) & ~15;   // columns the MMAs of this tile cover
+        if (!EXACT && !fast) {
+          // cooperative gather of the first n16 slots x 16 chunks of the K rows and of the dV rows, zeros
+          // past the list; slots beyond n16 are read by no MMA
+          const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+          for (int gi = 0; gi < n16 / 16; ++gi) {
+            const int slot = gi * 256 + st_tid;
+            const int r = slot >> 4, ch = slot & 15;
+            const int src = s_src[r];
+            const bool have = src >= 0;
+            const uint4 kv = have
+                ? __ldg(reinterpret_cast<const uint4*>(p.k + (static_cast<int64_t>(src) * p.Hkv + hk) * kD) + ch) : zero;
+            *reinterpret_cast<uint4*>(kv_smem0 + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = kv;
+            const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + st * kBKeys + r) : src;
+            const uint4 vv = have
+                ? __ldg(reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD) + ch) : zero;
+            if (v_mn_major) {
+              *reinterpret_cast<uint4*>(kv_smem1 + (ch >> 3) * kHalfBytes + sw128_offset(r, ch & 7)) = vv;
+            } else {
+              // transposed tile [d][key]: element (d, key = r)
+              uint8_t* base = kv_smem1 + (r >> 6) * kHalfBytes + ((r & 7) << 1);
+              const uint32_t key_chunk = (r & 63) >> 3;
+              const uint16_t* e = reinterpret_cast<const uint16_t*>(&vv);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const uint32_t d = ch * 8 + i;
+                *reinterpret_cast<uint16_t*>(base + d * 128u + ((key_chunk ^ (d & 7u)) << 4)) = e[i];
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&b_full);
+        }
+        // P = exp2(S2 * c - m * c) for the live columns of this thread's half
+        DYLLM_TRACE(2);
+        const int use = uses[0]++;
+        mbar_wait(&s_full[0], use & 1, &abort_flag, p.status_word, 309);
+        tc_fence_after_sync();
+        DYLLM_TRACE(3);
+        if (!EXACT && st == num_st - 1 && st_tid == 0)
+          mbar_arrive(&q_free);   // the last product that reads the query tile is complete
+#pragma unroll 1
+        for (int cc = 0; cc < 64; cc += 32) {
+          const int c0 = col0 + cc;
+          if (c0 >= n16 || !warp_live)
+            continue;   // uniform over the warp: no MMA reads these columns (or these rows are unused)
+          uint32_t sr[32];
+          tmem_ld_32x32(tmem_s0 + t_lane + c0, sr);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = (c0 + 2 * i < n_tile) ? ex2(fmaf(__uint_as_float(sr[2 * i]), c, -mc)) : 0.f;
+            const float p1 = (c0 + 2 * i + 1 < n_tile) ? ex2(fmaf(__uint_as_float(sr[2 * i + 1]), c, -mc)) : 0.f;
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
+            pk[i] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+          uint8_t* pdst = kv_smem0 + (c0 >> 6) * kHalfBytes;
+          const uint32_t chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(pdst + sw128_offset(row, chunk0 + j)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&s_empty[0]);
+        fence_proxy_async_smem();
+        mbar_arrive(&p_full);
+        DYLLM_TRACE(4);
+      }
+      if (num_st > 0) {
+        mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 310);
+        tc_fence_after_sync();
+        if (!EXACT && st_tid == 0) {
+          mbar_arrive(&kv0_free);   // P has been read
+          if (tile_tma && !c_early) {
+            mbar_arrive_expect_tx(&c_full, kTileBytes);
+            tma_load_2d(kv_smem1, &tmap_c, &c_full, h * kD, static_cast<int>(q0 + c_delta));
+            tma_load_2d(kv_smem1 + kHalfBytes, &tmap_c, &c_full, h * kD + 64, static_cast<int>(q0 + c_delta));
+          }
+          if (!tile_tma)
+            mbar_arrive(&kv1_free);   // dV has been read and no context tile will use the buffer
+        }
+      }
+      DYLLM_TRACE(5);
+
+      // epilogue: new = old + O / rowsum for this thread's 64 of the 128 head dimensions (salient rows take
+      // the exactly attended row instead); bf16 store; partial statistics of this head.  The tensor-memory
+      // loads are warp-collective, so every lane issues them; global-memory traffic is predicated on the row
+      // being inside the sequence.
+      const int r = q0 + row;
+      const bool live = r < q_end;
+      const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+      const int64_t off = (static_cast<int64_t>((live ? r : q0) + (EXACT ? sal_begin : 0)) * p.H + h) * kD + col0;
+      const int64_t c_off = (((live ? r : q0) + c_delta) * p.H + h) * kD + col0;
+      __nv_bfloat16* dst = (EXACT ? p.o_sal : p.out) + off;
+      __nv_bfloat16* cdst = (!EXACT && p.c_cache) ? p.c_cache + c_off : nullptr;
+      uint8_t* c_tile = kv_smem1 + half * kHalfBytes;   // tile_tma: this thread's half of the context tile
+      float dot = 0.f, nn = 0.f, no = 0.f;
+      uint4 old_row[8];
+      if (tile_tma) {
+        mbar_wait(&c_full, (n_c++) & 1, &abort_flag, p.status_word, 313);
+        DYLLM_TRACE(8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          old_row[j] = *reinterpret_cast<const uint4*>(c_tile + sw128_offset(row, j));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          old_row[j] = (EXACT || !live) ? make_uint4(0, 0, 0, 0)
+                                        : __ldg(reinterpret_cast<const uint4*>(p.c_old + c_off) + j);
+      }
+      // salient query row: its new value is the exactly attended row
+      const int sal_pos = EXACT ? 0 : s_sal_pos[row];
+      const uint4* sal_src = nullptr;
+      if (!EXACT && sal_pos && live)
+        sal_src = reinterpret_cast<const uint4*>(
+            p.o_sal + (static_cast<int64_t>(sal_begin + sal_pos - 1) * p.H + h) * kD + col0);
+#pragma unroll
+      for (int cc = 0; cc < 64; cc += 32) {
+        uint32_t orr[32];
+        if (num_st > 0) {
+          tmem_ld_32x32(tmem_o + t_lane + col0 + cc, orr);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            orr[i] = 0u;
+        }
+        if (live) {
+          const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(old_row + cc / 8);
+          uint4 sal_row[4];
+          if (sal_src) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              sal_row[j] = __ldg(sal_src + cc / 8 + j);
+          }
+          const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(sal_row);
+          uint32_t pk[16];
+          const float2 il2 = make_float2(inv_l, inv_l);
+          float2 d2 = make_float2(0.f, 0.f), n2 = make_float2(0.f, 0.f), q2 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 of = __bfloat1622float2(o2[i]);
+            float2 nv = ffma2(make_float2(__uint_as_float(orr[2 * i]), __uint_as_float(orr[2 * i + 1])), il2, of);
+            if (sal_src)
+              nv = __bfloat1622float2(x2[i]);
+            d2 = ffma2(nv, of, d2);
+            n2 = ffma2(nv, nv, n2);
+            q2 = ffma2(of, of, q2);
+            __nv_bfloat162 v2 = __floats2bfloat162_rn(nv.x, nv.y);
+            pk[i] = *reinterpret_cast<uint32_t*>(&v2);
+          }
+          dot += d2.x + d2.y;
+          nn += n2.x + n2.y;
+          no += q2.x + q2.y;
+          if (tile_tma) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(c_tile + sw128_offset(row, cc / 8 + j)) =
+                  make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              reinterpret_cast<uint4*>(dst + cc)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            if (cdst) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                reinterpret_cast<uint4*>(cdst + cc)[j] =
+                    make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
             }
           }
         }
-        fence_proxy_async_smem();
-        mbar_arrive(&b_full);
       }
-      // P = exp2(S2 * c - m * c) for the live columns of this thread's half
-      DYLLM_TRACE(2);
-      const int use = uses[0]++;
-      mbar_wait(&s_full[0], use & 1, &abort_flag, p.status_word, 309);
-      tc_fence_after_sync();
-      DYLLM_TRACE(3);
-#pragma unroll 1
-      for (int cc = 0; cc < 64; cc += 32) {
-        const int c0 = col0 + cc;
-        uint32_t sr[32];
-        tmem_ld_32x32(tmem_s0 + t_lane + c0, sr);
-        tmem_ld_wait();
-        if (cc == 32) {
-          tc_fence_before_sync();
-          mbar_arrive(&s_empty[0]);
+      if (!EXACT) {
+        // this thread has read its part of O: the MMA warp may reuse the columns once all have
+        tc_fence_before_sync();
+        mbar_arrive(&o_free);
+        // the two halves of a row add their statistics in a fixed order (half 0 + half 1)
+        if (half == 1)
+          s_st[row] = make_float4(dot, nn, no, 0.f);
+        if (tile_tma)
+          fence_proxy_async_smem();   // the updated tile is read by the TMA stores below
+        DYLLM_TRACE(9);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (tile_tma && st_tid == 0) {
+          tma_store_2d(&tmap_out, kv_smem1, h * kD, q0);
+          tma_store_2d(&tmap_out, kv_smem1 + kHalfBytes, h * kD + 64, q0);
+          if (p.c_cache) {
+            tma_store_2d(&tmap_c, kv_smem1, h * kD, static_cast<int>(q0 + c_delta));
+            tma_store_2d(&tmap_c, kv_smem1 + kHalfBytes, h * kD + 64, static_cast<int>(q0 + c_delta));
+          }
+          tma_store_commit();
         }
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = (c0 + 2 * i < n_tile) ? ex2(fmaf(__uint_as_float(sr[2 * i]), c, -mc)) : 0.f;
-          const float p1 = (c0 + 2 * i + 1 < n_tile) ? ex2(fmaf(__uint_as_float(sr[2 * i + 1]), c, -mc)) : 0.f;
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(p0, p1);
-          pk[i] = *reinterpret_cast<uint32_t*>(&v2);
-        }
-        uint8_t* pdst = kv_smem0 + (c0 >> 6) * kHalfBytes;
-        const uint32_t chunk0 = (c0 & 63) >> 3;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4*>(pdst + sw128_offset(row, chunk0 + j)) =
-              make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&p_full);
-      DYLLM_TRACE(4);
-    }
-    if (num_st > 0) {
-      mbar_wait(&pv_done, (num_st - 1) & 1, &abort_flag, p.status_word, 310);
-      tc_fence_after_sync();
-    }
-    DYLLM_TRACE(5);
-
-    // epilogue: new = old + O / rowsum for this thread's 64 of the 128 head dimensions; bf16 store;
-    // partial statistics of this head.  The tensor-memory loads are warp-collective, so every lane issues
-    // them; only the global-memory traffic is predicated on the row being inside the sequence.
-    const int r = q0 + row;
-    const bool live = r < q_end;
-    const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-    const int64_t off = (static_cast<int64_t>((live ? r : q0) + (EXACT ? sal_begin : 0)) * p.H + h) * kD + col0;
-    const int64_t c_off = (((live ? r : q0) + c_delta) * p.H + h) * kD + col0;
-    const __nv_bfloat16* cold = EXACT ? nullptr : p.c_old + c_off;
-    __nv_bfloat16* dst = (EXACT ? p.o_sal : p.out) + off;
-    // in-place cache update: salient rows are left alone (their old value is still needed, and they are
-    // overwritten with the exactly attended row afterwards)
-    __nv_bfloat16* cdst = nullptr;
-    if (!EXACT && p.c_cache && live) {
-      int lo = 0, hi = n_sal;
-      while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (p.idx_q[sal_begin + mid] < r)
-          lo = mid + 1;
-        else
-          hi = mid;
-      }
-      if (!(lo < n_sal && p.idx_q[sal_begin + lo] == r))
-        cdst = p.c_cache + c_off;
-    }
-    float dot = 0.f, nn = 0.f, no = 0.f;
-    uint4 old_row[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      old_row[j] = (EXACT || !live) ? make_uint4(0, 0, 0, 0) : __ldg(reinterpret_cast<const uint4*>(cold) + j);
-#pragma unroll
-    for (int cc = 0; cc < 64; cc += 32) {
-      uint32_t orr[32];
-      if (num_st > 0) {
-        tmem_ld_32x32(tmem_o + t_lane + col0 + cc, orr);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          orr[i] = 0u;
-      }
-      if (live) {
-        const uint4* oldv = old_row + cc / 8;
-        const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(oldv);
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 of = __bfloat1622float2(o2[i]);
-          const float n0 = of.x + __uint_as_float(orr[2 * i]) * inv_l;
-          const float n1 = of.y + __uint_as_float(orr[2 * i + 1]) * inv_l;
-          dot = fmaf(n0, of.x, dot);
-          dot = fmaf(n1, of.y, dot);
-          nn = fmaf(n0, n0, nn);
-          nn = fmaf(n1, n1, nn);
-          no = fmaf(of.x, of.x, no);
-          no = fmaf(of.y, of.y, no);
-          __nv_bfloat162 v2 = __floats2bfloat162_rn(n0, n1);
-          pk[i] = *reinterpret_cast<uint32_t*>(&v2);
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          reinterpret_cast<uint4*>(dst + cc)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-        if (cdst) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            reinterpret_cast<uint4*>(cdst + cc)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        DYLLM_TRACE(10);
+        if (half == 0 && live) {
+          const float4 o = s_st[row];
+          float* ps = p.partial + (static_cast<int64_t>(h) * p.Tq + r) * 3;
+          ps[0] = dot + o.x;
+          ps[1] = nn + o.y;
+          ps[2] = no + o.z;
         }
       }
-    }
-    if (!EXACT) {
-      // the two halves of a row add their statistics in a fixed order (half 0 + half 1)
-      if (half == 1)
-        s_st[row] = make_float4(dot, nn, no, 0.f);
+      // end of the item: every softmax thread is done with the tensor-memory accumulator and with the
+      // small shared arrays; then the producer may refill the tile buffers
+      tc_fence_before_sync();
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (half == 0 && live) {
-        const float4 o = s_st[row];
-        float* ps = p.partial + (static_cast<int64_t>(h) * p.Tq + r) * 3;
-        ps[0] = dot + o.x;
-        ps[1] = nn + o.y;
-        ps[2] = no + o.z;
+      if (!EXACT && tile_tma && st_tid == 0) {
+        tma_store_wait_read();   // the stores have read the context tile
+        mbar_arrive(&kv1_free);
       }
+      DYLLM_TRACE(6);
     }
-    DYLLM_TRACE(6);
   }
 
   tc_fence_before_sync();
@@ -540,130 +832,37 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 }
 
 // ----------------------------------------------------------------------------------------------
-// finalize: head-ordered reduction of the partial statistics + mask (part A, one thread per row);
-// salient rows take the exactly attended values and statistics recomputed from bf16 (part B, one
-// block per salient row).
+// finalize: head-ordered reduction of the partial statistics + threshold mask, one thread per row.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool mask_rule(float dot, float a, float b, float threshold) {
   return dot * rsqrtf(fmaxf(a, 1e-8f)) * rsqrtf(fmaxf(b, 1e-8f)) < threshold;
 }
 
 __global__ void __launch_bounds__(256)
-attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, const int32_t* __restrict__ idx_q,
-                          int num_salient, const __nv_bfloat16* __restrict__ c_old,
-                          const __nv_bfloat16* __restrict__ o_sal, __nv_bfloat16* __restrict__ out,
-                          float* __restrict__ stats, uint8_t* __restrict__ mask, float threshold, int width,
-                          int row_blocks, const int32_t* __restrict__ num_salient_dev,
-                          __nv_bfloat16* __restrict__ c_cache, const int64_t* __restrict__ c_seq_starts,
-                          const int64_t* __restrict__ c_seq_ids, const int32_t* __restrict__ cu_q,
-                          const int32_t* __restrict__ cu_k, int batch) {
-  if (num_salient_dev)
-    num_salient = min(num_salient, *num_salient_dev);
-  if (static_cast<int>(blockIdx.x) < row_blocks) {
-    const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r >= Tq)
-      return;
-    // salient rows are written by part B
-    int lo = 0, hi = num_salient;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (idx_q[mid] < r)
-        lo = mid + 1;
-      else
-        hi = mid;
-    }
-    if (lo < num_salient && idx_q[lo] == r)
-      return;
-    float s0 = stats[r * 3 + 0], s1 = stats[r * 3 + 1], s2 = stats[r * 3 + 2];
-    for (int h = 0; h < H; ++h) {
-      const float* ps = partial + (static_cast<int64_t>(h) * Tq + r) * 3;
-      s0 += ps[0];
-      s1 += ps[1];
-      s2 += ps[2];
-    }
-    stats[r * 3 + 0] = s0;
-    stats[r * 3 + 1] = s1;
-    stats[r * 3 + 2] = s2;
-    mask[r] = mask_rule(s0, s1, s2, threshold) ? 1 : 0;
+attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, float* __restrict__ stats,
+                          uint8_t* __restrict__ mask, float threshold) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= Tq)
     return;
+  float s0 = stats[r * 3 + 0], s1 = stats[r * 3 + 1], s2 = stats[r * 3 + 2];
+  for (int h = 0; h < H; ++h) {
+    const float* ps = partial + (static_cast<int64_t>(h) * Tq + r) * 3;
+    s0 += ps[0];
+    s1 += ps[1];
+    s2 += ps[2];
   }
-  const int i = blockIdx.x - row_blocks;
-  if (i >= num_salient)
-    return;
-  const int r = idx_q[i];
-  int64_t c_row = r;
-  if (c_seq_starts) {
-    // sequence b with cu_q[b] <= r < cu_q[b + 1]; its context rows are the last len_q rows in the cache
-    int lo = 0, hi = batch;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (cu_q[mid + 1] <= r)
-        lo = mid + 1;
-      else
-        hi = mid;
-    }
-    const int b = lo < batch ? lo : batch - 1;
-    c_row = c_seq_starts[c_seq_ids[b]] + ((cu_k[b + 1] - cu_k[b]) - (cu_q[b + 1] - cu_q[b])) + (r - cu_q[b]);
-  }
-  const uint4* old_row = reinterpret_cast<const uint4*>(c_old + c_row * width);
-  const uint4* new_row = reinterpret_cast<const uint4*>(o_sal + static_cast<int64_t>(i) * width);
-  uint4* out_row = reinterpret_cast<uint4*>(out + static_cast<int64_t>(r) * width);
-  uint4* cache_row = c_cache ? reinterpret_cast<uint4*>(c_cache + c_row * width) : nullptr;
-  float dot = 0.f, nn = 0.f, no = 0.f;
-  for (int v = threadIdx.x; v < width / 8; v += blockDim.x) {
-    const uint4 ov = old_row[v];
-    const uint4 nv = __ldg(new_row + v);
-    out_row[v] = nv;
-    if (cache_row)
-      cache_row[v] = nv;
-    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
-    const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nv);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 of = __bfloat1622float2(o2[j]);
-      const float2 nf = __bfloat1622float2(n2[j]);
-      dot = fmaf(nf.x, of.x, dot);
-      dot = fmaf(nf.y, of.y, dot);
-      nn = fmaf(nf.x, nf.x, nn);
-      nn = fmaf(nf.y, nf.y, nn);
-      no = fmaf(of.x, of.x, no);
-      no = fmaf(of.y, of.y, no);
-    }
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    nn += __shfl_xor_sync(0xffffffffu, nn, off);
-    no += __shfl_xor_sync(0xffffffffu, no, off);
-  }
-  __shared__ float red[8][3];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) {
-    red[warp][0] = dot;
-    red[warp][1] = nn;
-    red[warp][2] = no;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float a = 0.f, bsum = 0.f, cs = 0.f;
-    for (int w = 0; w < 8; ++w) {
-      a += red[w][0];
-      bsum += red[w][1];
-      cs += red[w][2];
-    }
-    stats[r * 3 + 0] = a;
-    stats[r * 3 + 1] = bsum;
-    stats[r * 3 + 2] = cs;
-    mask[r] = mask_rule(a, bsum, cs, threshold) ? 1 : 0;
-  }
+  stats[r * 3 + 0] = s0;
+  stats[r * 3 + 1] = s1;
+  stats[r * 3 + 2] = s2;
+  mask[r] = mask_rule(s0, s1, s2, threshold) ? 1 : 0;
 }
 
 bool g_attn_smem_set[2][64] = {{false}, {false}};
 unsigned long long* g_attn_trace = nullptr;
 
 template <bool EXACT>
-int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
-                     int64_t blocks, cudaStream_t s) {
+int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tout,
+                     const CUtensorMap& tc, const AttnParams& p_in, int64_t items, cudaStream_t s) {
   int dev = 0;
   cudaGetDevice(&dev);
   dev = (dev < 0 || dev >= 64) ? 0 : dev;
@@ -674,9 +873,14 @@ int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
                        cudaGetErrorString(cudaGetLastError()));
     g_attn_smem_set[EXACT ? 1 : 0][dev] = true;
   }
-  DYLLM_REQUIRE(blocks > 0 && blocks < (1ll << 31), DYLLM_ERR_UNSUPPORTED, "attention: grid of %lld blocks",
-                static_cast<long long>(blocks));
-  attention_kernel<EXACT><<<static_cast<unsigned>(blocks), kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, p);
+  DYLLM_REQUIRE(items > 0 && items < (1ll << 31), DYLLM_ERR_UNSUPPORTED, "attention: %lld work items",
+                static_cast<long long>(items));
+  AttnParams p = p_in;
+  p.num_items = static_cast<int>(items);
+  // persistent grid: as many CTAs as the device runs at once (two per SM)
+  const int64_t resident = 2ll * sm_count();
+  const unsigned blocks = static_cast<unsigned>(items < resident ? items : resident);
+  attention_kernel<EXACT><<<blocks, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, tout, tc, p);
   return check_launch(EXACT ? "salient_attention" : "delta_attention");
 }
 
@@ -750,6 +954,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   p.c_seq_starts = c_seq_starts;
   p.c_seq_ids = c_seq_ids;
   p.idx_q = idx_salient_row_q;
+  p.o_sal = const_cast<__nv_bfloat16*>(static_cast<const __nv_bfloat16*>(o_sal));
   p.out = static_cast<__nv_bfloat16*>(out);
   p.partial = static_cast<float*>(workspace);
   p.cu_q = cu_seqlens_q;
@@ -766,16 +971,25 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   p.v_compact = v_compact;
   p.trace = g_attn_trace;
   p.status_word = device_status_word();
+  p.batch = batch;
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
-  rc = launch_attention<false>(tq, tk, tk, p, blocks, s);
+  p.trace_first = blocks > 1536 ? 512u : 0u;   // the middle of the launch when it has several waves
+  // context tiles: the new context [Tq, H*D], and the previous one (packed like Q, or the cache arena,
+  // whose extent this call does not know: full tiles never leave the rows of their sequence)
+  CUtensorMap tout, tc;
+  rc = encode_tmap_2d_bf16(&tout, out, total_q, static_cast<uint64_t>(num_heads) * kD,
+                           static_cast<uint64_t>(num_heads) * kD, kBQ, 64, true);
   if (rc != DYLLM_OK)
     return rc;
-
-  const int row_blocks = cdiv_i(total_q, 256);
-  attention_finalize_kernel<<<row_blocks + num_salient, 256, 0, s>>>(
-      p.partial, num_heads, total_q, idx_salient_row_q, num_salient, p.c_old,
-      static_cast<const __nv_bfloat16*>(o_sal), p.out, cosine_stats, cosine_out, threshold, num_heads * kD, row_blocks,
-      num_salient_dev, p.c_cache, c_seq_starts, c_seq_ids, cu_seqlens_q, cu_seqlens_k, batch);
+  rc = encode_tmap_2d_bf16(&tc, c, c_seq_starts ? (1ull << 30) : static_cast<uint64_t>(total_q),
+                           static_cast<uint64_t>(num_heads) * kD, static_cast<uint64_t>(num_heads) * kD, kBQ, 64, true);
+  if (rc != DYLLM_OK)
+    return rc;
+  rc = launch_attention<false>(tq, tk, tk, tout, tc, p, blocks, s);
+  if (rc != DYLLM_OK)
+    return rc;
+  attention_finalize_kernel<<<cdiv_i(total_q, 256), 256, 0, s>>>(p.partial, num_heads, total_q, cosine_stats,
+                                                                 cosine_out, threshold);
   return check_launch("attention_finalize");
 }
 
@@ -823,8 +1037,9 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(kD));
   p.v_mn_major = 1;
   p.status_word = device_status_word();
+  p.batch = batch;
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
-  return launch_attention<true>(tk, tk, tv, p, blocks, static_cast<cudaStream_t>(stream));
+  return launch_attention<true>(tk, tk, tv, tk, tk, p, blocks, static_cast<cudaStream_t>(stream));
 }
 
 int dyllm_attention_trace(void* device_buffer) {

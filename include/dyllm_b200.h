@@ -252,10 +252,11 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
                                  int total_k, int num_heads, int num_kv_heads, int head_dim,
                                  const int32_t* cu_salientlens, const int32_t* idx_salient_row_q, void* stream);
 
-/* Tracing aid: while a device buffer of 256 * 8 uint64 is registered, each of the first 256 CTAs of
- * dyllm_attention_sparse_varlen stores %globaltimer (ns) at seven phase boundaries (slot 0 start, 7 first
- * logits ready, 1 end of pass A, 2 salient rows gathered, 3 their logits ready, 4 P written, 5 P dV
- * done, 6 end).  Pass null to switch tracing off (the default). */
+/* Tracing aid: while a device buffer of 1024 * 16 uint64 is registered, 1024 consecutive CTAs of
+ * dyllm_attention_sparse_varlen (CTAs 512.. when the grid has more than 1536, else the first ones) store
+ * %globaltimer (ns) at phase boundaries (slot 0 start, 7 first logits ready, 1 end of pass A, 2 salient
+ * rows gathered, 3 their logits ready, 4 P written, 5 P dV done, 8 previous context tile in shared
+ * memory, 9 tile updated, 10 stores issued, 6 end, 14 the SM id).  Pass null to switch tracing off (the default). */
 int dyllm_attention_trace(void* device_buffer);
 
 /* Launch resources of the main attention kernel: [registers, local bytes, static shared bytes,

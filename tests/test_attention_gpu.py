@@ -90,6 +90,8 @@ CASES = [
     (2, 256, 256, 2, 2, False, 0),
     (2, 128, 256, 2, 2, True, 200),   # more than one salient tile
     (2, 300, 212, 4, 4, False, [1, 130]),
+    (2, 256, 256, 4, 4, True, [16, 17]),   # either side of the early-gather limit
+    (3, 200, 56, 4, 2, False, [15, 33, 48]),
 ]
 
 
