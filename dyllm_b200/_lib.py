@@ -58,7 +58,7 @@ KERNELS_PER_CALL = {
     "dyllm_fused_offset": 1,
     "dyllm_cache_get_seqs": 1, "dyllm_cache_get_block": 1, "dyllm_cache_reset_full": 1, "dyllm_cache_reset_block": 1,
     "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 2, "dyllm_swiglu_ffn": 3, "dyllm_cache_dest_rows": 1, "dyllm_moe_route": 1, "dyllm_moe_ffn": 5,
-    "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 1, "dyllm_delta_v_update": 1,
+    "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 2, "dyllm_delta_v_update": 1,
     "dyllm_add_rms_norm": 1, "dyllm_rope_neox": 1,
 }
 launch_count = 0

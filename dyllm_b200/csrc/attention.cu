@@ -36,6 +36,8 @@ constexpr int kAttnThreads = 320;          // TMA producer warp, MMA warp, eight
 constexpr uint32_t kTileBytes = 128 * 128 * 2;   // one [128][128] bf16 tile = two [128][64] swizzled halves
 constexpr uint32_t kHalfBytes = 128 * 64 * 2;
 constexpr int kFastSal = 16;                      // salient keys served by the early gather
+constexpr int kSmallRows = 16;                    // salient query rows per sequence served by salient_rows_small_kernel
+constexpr int kSmallMaxTiles = 15;                // ... 15 * 16 columns of S^T + 16 of O^T = 256 tensor-memory columns
 constexpr uint32_t kSalHalfBytes = kFastSal * 128;   // one 64-column half of a 16-row tile
 constexpr uint32_t kSalBytes = 2 * kSalHalfBytes;
 constexpr uint32_t kAttnSmem = 3 * kTileBytes + 2 * kSalBytes + 1024;
@@ -61,6 +63,7 @@ struct AttnParams {
   const int32_t* cu_sal;         // [B + 1] prefix counts of the salient key list
   const int32_t* idx_k;          // salient key rows (K space), ascending, grouped by sequence
   int H, Hkv, Tq, Tk, n_qtiles, batch, num_items;
+  int skip_small;                // EXACT: sequences with few salient rows are left to salient_rows_small_kernel
   float scale_log2;              // log2(e) / sqrt(D)
   int v_mn_major;                // 1: dV tile kept [keys][d] (MN-major operand); 0: transposed while gathering
   int v_compact;                 // 1: v holds one row per salient key, in list order; 0: v is [Tk, Hkv, D]
@@ -127,6 +130,11 @@ __device__ __forceinline__ float2 ex2_pair_f16(float x0, float x1) {
 
 constexpr bool kPassAHalfExp = false;   // measured: no faster than fp32 exponentials here
 
+// Sequences whose salient query rows are handled by salient_rows_small_kernel.
+__device__ __forceinline__ bool small_rows_item(int n_sal, int num_kt) {
+  return n_sal > 0 && n_sal <= kSmallRows && num_kt <= kSmallMaxTiles;
+}
+
 // One unit of work: (sequence, query head, tile of 128 query rows).
 struct AttnItem {
   int h, hk, sal_begin, n_sal, q_end, q0, k_begin, len_k, num_kt, num_st;
@@ -162,6 +170,8 @@ __device__ __forceinline__ bool decode_item(const AttnParams& p, int item, AttnI
   it.k_begin = p.cu_k[b];
   it.len_k = p.cu_k[b + 1] - it.k_begin;
   it.num_kt = (it.len_k + kBKeys - 1) / kBKeys;
+  if (EXACT && p.skip_small && small_rows_item(it.n_sal, it.num_kt))
+    return false;   // salient_rows_small_kernel takes this sequence
   it.hk = it.h / (p.H / p.Hkv);
   it.num_st = EXACT ? it.num_kt : (it.n_sal + kBKeys - 1) / kBKeys;   // tiles of pass B
   it.c_delta = 0;
@@ -206,6 +216,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const bool v_mn_major = EXACT ? true : (p.v_mn_major != 0);
+
+  if (EXACT && p.skip_small) {
+    // usually every sequence has few salient rows and the other kernel has done all the work: leave
+    // before any set-up
+    int any = 0;
+    for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
+      const int n = p.cu_sal[b + 1] - p.cu_sal[b];
+      const int kt = (p.cu_k[b + 1] - p.cu_k[b] + kBKeys - 1) / kBKeys;
+      any |= (n > 0 && !small_rows_item(n, kt)) ? 1 : 0;
+    }
+    if (!__syncthreads_or(any))
+      return;
+  }
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -832,6 +855,273 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 }
 
 // ----------------------------------------------------------------------------------------------
+// Exact attention of a FEW salient query rows (at most 16 per sequence, the common case):
+//   o_sal[i] = softmax(q[idx_q[i]] K^T / sqrt(D)) V
+// With so few rows a 128-row query tile is almost empty, so the products are transposed: one CTA per
+// (sequence, head) computes S^T = K Q^T tile by tile (M = 128 keys, N = 16 rows) and keeps S^T of the whole
+// sequence in tensor memory (16 columns per key tile); the key and value tiles stream once through a
+// three-slot TMA ring (values follow the keys, so they arrive while the row maxima are being reduced);
+// a thread owns one key of a tile: the maximum over keys is a warp-shuffle + shared-memory reduction,
+// P^T = exp2(S^T c - m c) goes to shared memory as the [16 rows][128 keys] K-major operand of
+// O^T += V^T P^T (V tile used as loaded, as the MN-major A operand; M = 128 head dimensions, N = 16),
+// and O^T / rowsum leaves with 64-byte row segments per warp.  Sequences with more rows or more than
+// kSmallMaxTiles key tiles are left to attention_kernel<true>.
+// ----------------------------------------------------------------------------------------------
+constexpr int kSmallStages = 3;
+constexpr uint32_t kSmallSmem = kSmallStages * kTileBytes + 3 * kSalBytes + 1024;   // ring, Q, two P slots
+
+__global__ void __launch_bounds__(kAttnThreads, 2)
+salient_rows_small_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                          const AttnParams p) {
+  const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const int sal_begin = p.cu_sal[b];
+  const int n_sal = p.cu_sal[b + 1] - sal_begin;
+  const int k_begin = p.cu_k[b];
+  const int len_k = p.cu_k[b + 1] - k_begin;
+  const int num_kt = (len_k + kBKeys - 1) / kBKeys;
+  if (!small_rows_item(n_sal, num_kt))
+    return;
+  const int hk = h / (p.H / p.Hkv);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_smem = smem + kSmallStages * kTileBytes;   // [16 rows][128 d], two 64-column halves
+  uint8_t* p_smem = q_smem + kSalBytes;                 // two slots of [16 rows][128 keys]
+  __shared__ uint64_t full[kSmallStages], empty[kSmallStages], q_full, s_done, p_full[2], p_empty[2], o_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ float s_red[8][kSmallRows];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < kSmallStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(&q_full, 256);
+    mbar_init(&s_done, 1);
+    mbar_init(&p_full[0], 128);
+    mbar_init(&p_full[1], 128);
+    mbar_init(&p_empty[0], 1);
+    mbar_init(&p_empty[1], 1);
+    mbar_init(&o_done, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kAttnTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_st = tmem_slot;                       // S^T of key tile t: columns [16 t, 16 t + 16)
+  const uint32_t tmem_ot = tmem_slot + num_kt * kSmallRows;   // O^T: 16 columns
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer: K tiles, then V tiles
+    for (int i = 0; i < 2 * num_kt; ++i) {
+      const int slot = i % kSmallStages;
+      mbar_wait(&empty[slot], ((i / kSmallStages) & 1) ^ 1, &abort_flag, p.status_word, 331);
+      if (lane == 0) {
+        const CUtensorMap* map = i < num_kt ? &tmap_k : &tmap_v;
+        const int t = i < num_kt ? i : i - num_kt;
+        uint8_t* dst = smem + slot * kTileBytes;
+        mbar_arrive_expect_tx(&full[slot], kTileBytes);
+        tma_load_2d(dst, map, &full[slot], hk * kD, k_begin + t * kBKeys);
+        tma_load_2d(dst + kHalfBytes, map, &full[slot], hk * kD + 64, k_begin + t * kBKeys);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc_s = umma_idesc_bf16(128, kSmallRows, 0, 0);    // K tile (K-major) x Q (K-major)
+    constexpr uint32_t idesc_o = umma_idesc_bf16(128, kSmallRows, 1, 0);    // V tile (MN-major) x P (K-major)
+    const uint32_t q_addr = smem_u32(q_smem);
+    mbar_wait(&q_full, 0, &abort_flag, p.status_word, 332);
+    for (int t = 0; t < num_kt; ++t) {
+      const int slot = t % kSmallStages;
+      mbar_wait(&full[slot], (t / kSmallStages) & 1, &abort_flag, p.status_word, 333);
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t k_addr = smem_u32(smem + slot * kTileBytes);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint64_t a_desc = umma_smem_desc_sw128(k_addr + half * kHalfBytes, 16, 1024);
+          const uint64_t b_desc = umma_smem_desc_sw128(q_addr + half * kSalHalfBytes, 16, 1024);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tmem_st + t * kSmallRows, a_desc + 2 * kk, b_desc + 2 * kk, idesc_s, (half | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[slot]);
+        if (t == num_kt - 1)
+          umma_commit(&s_done);
+      }
+      __syncwarp();
+    }
+    for (int t = 0; t < num_kt; ++t) {
+      const int i = num_kt + t;
+      const int slot = i % kSmallStages;
+      mbar_wait(&full[slot], (i / kSmallStages) & 1, &abort_flag, p.status_word, 334);
+      mbar_wait(&p_full[t & 1], (t >> 1) & 1, &abort_flag, p.status_word, 335);
+      tc_fence_after_sync();
+      if (lane == 0) {
+        const uint32_t v_addr = smem_u32(smem + slot * kTileBytes);
+        const uint32_t p_addr = smem_u32(p_smem + (t & 1) * kSalBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 keys per step: V rows [keys][d] (2048 bytes per step, d halves one half-tile apart),
+          // P rows [16][keys] (32 bytes per step inside a 64-key half)
+          const uint64_t a_desc = umma_smem_desc_sw128(v_addr + kk * 2048, kHalfBytes, 1024);
+          const uint64_t b_desc =
+              umma_smem_desc_sw128(p_addr + (kk >> 2) * kSalHalfBytes + (kk & 3) * 32, 16, 1024);
+          umma_ss(tmem_ot, a_desc, b_desc, idesc_o, (t | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[slot]);
+        umma_commit(&p_empty[t & 1]);
+        if (t == num_kt - 1)
+          umma_commit(&o_done);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax over keys / epilogue
+    const int sw = warp - 2;                 // 0..7
+    const int qd = warp & 3;                 // tensor-memory lane quarter: keys (or head dims) 32 qd .. 32 qd + 31
+    const int half = sw >> 2;                // key tiles t with t % 2 == half; P slot `half`
+    const int st_tid = sw * 32 + lane;
+    const int kl = qd * 32 + lane;           // key inside a tile / head dimension in the epilogue
+    const uint32_t t_lane = static_cast<uint32_t>(qd * 32) << 16;
+    const float c = p.scale_log2;
+
+    {  // gather the query rows: 16 rows x 16 chunks of 16 bytes, one per thread, zeros past the list
+      const int r = st_tid >> 4, ch = st_tid & 15;
+      uint4 qv = make_uint4(0, 0, 0, 0);
+      if (r < n_sal) {
+        const int src = p.idx_q[sal_begin + r];
+        qv = __ldg(reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(src) * p.H + h) * kD) + ch);
+      }
+      *reinterpret_cast<uint4*>(q_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = qv;
+      fence_proxy_async_smem();
+      mbar_arrive(&q_full);
+    }
+
+    // row maxima over all keys
+    mbar_wait(&s_done, 0, &abort_flag, p.status_word, 336);
+    tc_fence_after_sync();
+    float m[kSmallRows];
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r)
+      m[r] = kNegBig;
+    for (int t = half; t < num_kt; t += 2) {
+      uint32_t sr[kSmallRows];
+      tmem_ld_32x16(tmem_st + t_lane + t * kSmallRows, sr);
+      tmem_ld_wait();
+      if (t * kBKeys + kl < len_k) {
+#pragma unroll
+        for (int r = 0; r < kSmallRows; ++r)
+          m[r] = fmaxf(m[r], __uint_as_float(sr[r]));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+        m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], off));
+    }
+    if (lane < kSmallRows) {
+      // lane r publishes row r (a select chain instead of dynamic register indexing)
+      float v = m[0];
+#pragma unroll
+      for (int r = 1; r < kSmallRows; ++r)
+        v = lane == r ? m[r] : v;
+      s_red[sw][lane] = v;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r) {
+      float v = s_red[0][r];
+#pragma unroll
+      for (int w = 1; w < 8; ++w)
+        v = fmaxf(v, s_red[w][r]);
+      m[r] = v * c;   // from here on m holds max * c
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // s_red is reused for the sums
+
+    // P^T tile by tile (unnormalised), row sums on the side
+    float l[kSmallRows];
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r)
+      l[r] = 0.f;
+    uint8_t* p_slot = p_smem + half * kSalBytes;
+    for (int t = half, n = 0; t < num_kt; t += 2, ++n) {
+      uint32_t sr[kSmallRows];
+      tmem_ld_32x16(tmem_st + t_lane + t * kSmallRows, sr);
+      tmem_ld_wait();
+      const bool valid = t * kBKeys + kl < len_k;
+      mbar_wait(&p_empty[half], (n & 1) ^ 1, &abort_flag, p.status_word, 337);
+      // element (row r, key kl): 64-key half kl / 64, 16-byte chunk (kl % 64) / 8, 2 bytes at kl % 8
+      uint8_t* base = p_slot + (kl >> 6) * kSalHalfBytes + ((kl & 7) << 1);
+      const uint32_t chunk = (kl & 63) >> 3;
+#pragma unroll
+      for (int r = 0; r < kSmallRows; ++r) {
+        const float e = valid ? ex2(fmaf(__uint_as_float(sr[r]), c, -m[r])) : 0.f;
+        l[r] += e;
+        *reinterpret_cast<__nv_bfloat16*>(base + r * 128u + ((chunk ^ (r & 7u)) << 4)) = __float2bfloat16_rn(e);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&p_full[half]);
+    }
+    // row sums over all keys
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], off);
+    }
+    if (lane < kSmallRows) {
+      float v = l[0];
+#pragma unroll
+      for (int r = 1; r < kSmallRows; ++r)
+        v = lane == r ? l[r] : v;
+      s_red[sw][lane] = v;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+
+    // epilogue: thread = head dimension kl; the two halves share the rows (8 each)
+    mbar_wait(&o_done, 0, &abort_flag, p.status_word, 338);
+    tc_fence_after_sync();
+    uint32_t orr[kSmallRows];
+    tmem_ld_32x16(tmem_ot + t_lane, orr);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < kSmallRows / 2; ++j) {
+      const int r = half * (kSmallRows / 2) + j;
+      if (r < n_sal) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w)
+          sum += s_red[w][r];
+        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+        // orr is indexed with a compile-time constant in each half
+        const float o = half == 0 ? __uint_as_float(orr[j]) : __uint_as_float(orr[kSmallRows / 2 + j]);
+        p.o_sal[(static_cast<int64_t>(sal_begin + r) * p.H + h) * kD + kl] = __float2bfloat16_rn(o * inv);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_slot, kAttnTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
 // finalize: head-ordered reduction of the partial statistics + threshold mask, one thread per row.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ bool mask_rule(float dot, float a, float b, float threshold) {
@@ -1038,6 +1328,27 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
   p.v_mn_major = 1;
   p.status_word = device_status_word();
   p.batch = batch;
+  // sequences with at most kSmallRows salient rows (and not too many key tiles): transposed kernel, one
+  // CTA per (sequence, head); the general kernel skips them
+  {
+    static bool smem_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev < 0 || dev >= 64) ? 0 : dev;
+    if (!smem_set[dev]) {
+      if (cudaFuncSetAttribute(salient_rows_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kSmallSmem)) != cudaSuccess)
+        return set_error(DYLLM_ERR_CUDA, "attention_salient_rows: cudaFuncSetAttribute failed: %s",
+                         cudaGetErrorString(cudaGetLastError()));
+      smem_set[dev] = true;
+    }
+    salient_rows_small_kernel<<<static_cast<unsigned>(batch) * num_heads, kAttnThreads, kSmallSmem,
+                                static_cast<cudaStream_t>(stream)>>>(tk, tv, p);
+    rc = check_launch("salient_rows_small");
+    if (rc != DYLLM_OK)
+      return rc;
+  }
+  p.skip_small = 1;
   const int64_t blocks = static_cast<int64_t>(batch) * num_heads * p.n_qtiles;
   return launch_attention<true>(tk, tk, tv, tk, tk, p, blocks, static_cast<cudaStream_t>(stream));
 }

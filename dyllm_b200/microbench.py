@@ -183,14 +183,49 @@ def bench_salient_attention(args):
     return ms, 2.0 * k.numel() * 2 + 2.0 * iq.numel() * H * D * 2, "B"
 
 
+def bench_steps(args):
+    """One refresh period of sparse denoising steps (3 response-only + 1 full-sequence) of the 32-layer
+    LLaDA-8B shape at batch 16, launched eagerly after one dense step: the launch sequence of the
+    steady state of a generation, short enough to list launch by launch under a profiler."""
+    from . import runner
+    from .model import LLaDAForDLM, LLaDAShape, init_weights_
+
+    dev = torch.device("cuda")
+    shape = LLaDAShape(num_hidden_layers=args.layers)
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = LLaDAForDLM(shape, 0.99)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    init_weights_(model, seed=0)
+    model.eval()
+    sr = runner.StepRunner(model, shape.mask_token_id, 32, 256, num_full_steps=1, refresh_period=4, use_graphs=False)
+    g = torch.Generator().manual_seed(1)
+    prompts = torch.randint(0, shape.vocab_size - 1024, (B, P), generator=g).tolist()
+    seqs = sr.new_batch(prompts, R)
+    sr.step(seqs)                         # dense step: fills the caches
+    for seq in seqs:                      # continue in the steady state of the refresh schedule
+        seq.processed_steps = 5
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(4):
+        sr.step(seqs)
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / 4, 4.0 * B * (R // 256) , "S"
+
+
 KERNELS = {"stats": bench_stats, "select": bench_select, "scatter": bench_scatter, "get_seqs": bench_get_seqs,
            "ffn": bench_ffn, "kv_proj": bench_kv_proj, "attention": bench_attention,
-           "salient_attention": bench_salient_attention}
+           "salient_attention": bench_salient_attention, "steps": bench_steps}
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", nargs="*", default=list(KERNELS))
+    ap.add_argument("--kernel", nargs="*", default=[k for k in KERNELS if k != "steps"])
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the `steps` case")
     ap.add_argument("--rows", type=int, default=416, help="salient rows in the batch (multiple of 16)")
     ap.add_argument("--select-rows", type=int, default=8 << 20)
     ap.add_argument("--iters", type=int, default=20)
@@ -202,6 +237,9 @@ def main():
     hbm, tf, src = peaks()
     for name in args.kernel:
         ms, work, kind = KERNELS[name](args)
+        if kind == "S":
+            print(json.dumps({"kernel": name, "ms_per_denoising_step": round(ms, 3), "layers": args.layers}), flush=True)
+            continue
         if kind == "B":
             ach, peak, unit = work / ms / 1e6, hbm, "GB/s"
         else:

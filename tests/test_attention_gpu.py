@@ -92,6 +92,9 @@ CASES = [
     (2, 300, 212, 4, 4, False, [1, 130]),
     (2, 256, 256, 4, 4, True, [16, 17]),   # either side of the early-gather limit
     (3, 200, 56, 4, 2, False, [15, 33, 48]),
+    (1, 1700, 220, 2, 2, False, 5),     # 15 key tiles: the longest sequence of the few-rows kernel
+    (1, 1800, 248, 2, 1, False, 9),     # 16 key tiles: few rows, but left to the general kernel
+    (2, 100, 30, 2, 2, True, [16, 1]),  # ragged single key tile
 ]
 
 
