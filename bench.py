@@ -31,9 +31,11 @@ BATCH, PROMPT, GEN, BLOCK, DSTEPS, TAU, FULL_STEPS, REFRESH = 16, 256, 256, 32, 
 METRIC = "generated tokens/s (LLaDA-8B bf16, b=16, gen=256, tau=0.99)"
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of this library's kernels at this
-# workload's shapes, from the ncu captures summarised under profiles/ (full-sequence-query launch for
-# the attention kernel, 48 salient rows for the FFN launches).
-NCU_TRAFFIC_BYTES = {"delta_attention": 254.8e6, "swiglu_ffn": 320.0e6}
+# workload's shapes, from the ncu captures summarised under profiles/: the gathered FFN at 48 salient
+# rows (four launches), the exact attention of the salient rows, and the approximate attention, whose
+# capture is a launch with full-sequence queries (252.2 MB) scaled by the algorithmic bytes to the mix of
+# one full-sequence and three response-only launches that the bench averages over.
+NCU_TRAFFIC_BYTES = {"delta_attention": 181.6e6, "swiglu_ffn": 320.0e6, "salient_attention": 138.4e6}
 
 
 def measured_peaks():

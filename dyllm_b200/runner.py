@@ -132,7 +132,8 @@ class StepRunner:
     """Runs denoising steps of a fixed batch: ``num_full_steps`` dense steps, then sparse steps."""
 
     def __init__(self, model, mask_id: int, block_length: int = 32, steps: int = 256, num_full_steps: int = 8,
-                 refresh_period: int = 4, use_graphs: bool = True, full_logits: bool = False):
+                 refresh_period: int = 4, use_graphs: bool = True, full_logits: bool = False,
+                 graphs_with_tp: bool = True):
         self.model = model
         self.mask_id = mask_id
         self.block_length = block_length
@@ -142,6 +143,7 @@ class StepRunner:
         self.device = next(model.parameters()).device
         self.salient_counts: list[int] = []
         self.use_graphs = use_graphs
+        self.graphs_with_tp = graphs_with_tp   # capture steps that contain NCCL all-reduces as well
         # The reference projects every query row onto the vocabulary and then indexes the rows of the
         # current block (model_runner.py:377, sampler.py:244-315); with full_logits False only the rows the
         # sampler reads are projected, which yields the same tokens.
@@ -262,8 +264,9 @@ class StepRunner:
     def _run_step(self, st, kind: str) -> None:
         """Runs one step: eagerly the first time a kind of step is met (allocations, one-time kernel
         attributes), then captured into a CUDA graph and replayed.  Graphs are not used while region
-        timing is on (events cannot be timed inside a graph) or with more than one rank."""
-        if not self.use_graphs or profiling.enabled() or _multi_rank():
+        timing is on (events cannot be timed inside a graph).  With several ranks every rank runs the
+        same sequence of eager steps, captures and replays, so the all-reduces inside a step line up."""
+        if not self.use_graphs or profiling.enabled() or (_multi_rank() and not self.graphs_with_tp):
             self._device_step(st, kind)
             return
         key = (st.key, kind)
