@@ -133,7 +133,7 @@ class StepRunner:
 
     def __init__(self, model, mask_id: int, block_length: int = 32, steps: int = 256, num_full_steps: int = 8,
                  refresh_period: int = 4, use_graphs: bool = True, full_logits: bool = False,
-                 graphs_with_tp: bool = True):
+                 graphs_with_tp: bool = False):
         self.model = model
         self.mask_id = mask_id
         self.block_length = block_length
@@ -143,7 +143,9 @@ class StepRunner:
         self.device = next(model.parameters()).device
         self.salient_counts: list[int] = []
         self.use_graphs = use_graphs
-        self.graphs_with_tp = graphs_with_tp   # capture steps that contain NCCL all-reduces as well
+        # Capturing steps that contain NCCL all-reduces did not complete on two GPUs (the run stopped making
+        # progress and was ended by its time limit), so several ranks launch eagerly unless this is set.
+        self.graphs_with_tp = graphs_with_tp
         # The reference projects every query row onto the vocabulary and then indexes the rows of the
         # current block (model_runner.py:377, sampler.py:244-315); with full_logits False only the rows the
         # sampler reads are projected, which yields the same tokens.
