@@ -118,6 +118,89 @@ rope_neox_kernel(uint4* __restrict__ x, const int64_t* __restrict__ positions, c
   }
 }
 
+// Confidence of the most likely token of every row of logits: conf = max_j softmax(x)_j = 1 / sum_j
+// exp(x_j - max), token = the first j that attains the maximum.  One CTA per row, one pass over the row
+// with 16-byte loads: every thread keeps a running (max, sum, argmax) and rescales its sum when its
+// maximum grows; the block then merges the 256 triples.
+constexpr int kConfThreads = 256;
+
+__global__ void __launch_bounds__(kConfThreads)
+row_confidence_kernel(const __nv_bfloat16* __restrict__ logits, int vocab, int64_t pitch,
+                      float* __restrict__ conf, int64_t* __restrict__ token) {
+  const __nv_bfloat16* row = logits + static_cast<int64_t>(blockIdx.x) * pitch;
+  float m = -INFINITY, l = 0.f;
+  int arg = 0;
+  const int vecs = vocab / 8;
+  const uint4* row4 = reinterpret_cast<const uint4*>(row);
+  for (int v = threadIdx.x; v < vecs; v += kConfThreads) {
+    const uint4 u = __ldg(row4 + v);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h2[i]);
+      x[2 * i] = f.x;
+      x[2 * i + 1] = f.y;
+    }
+    float vm = x[0];
+    int va = 0;
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+      if (x[i] > vm) {
+        vm = x[i];
+        va = i;
+      }
+    if (vm > m) {
+      l *= __expf(m - vm);   // exp(-inf) = 0 on the first vector
+      m = vm;
+      arg = v * 8 + va;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      l += __expf(x[i] - m);
+  }
+  for (int j = vecs * 8 + threadIdx.x; j < vocab; j += kConfThreads) {   // tail when vocab % 8 != 0
+    const float x = __bfloat162float(row[j]);
+    if (x > m) {
+      l *= __expf(m - x);
+      m = x;
+      arg = j;
+    }
+    l += __expf(x - m);
+  }
+  // merge: larger maximum wins, equal maxima keep the smaller index; sums are rescaled to the winner
+  auto merge = [](float& m1, float& l1, int& a1, float m2, float l2, int a2) {
+    if (m2 > m1 || (m2 == m1 && a2 < a1)) {
+      const float t = m1; m1 = m2; m2 = t;
+      const float tl = l1; l1 = l2; l2 = tl;
+      a1 = a2;
+    }
+    l1 += (m2 == -INFINITY) ? 0.f : l2 * __expf(m2 - m1);
+  };
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
+    const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
+    const int a2 = __shfl_xor_sync(0xffffffffu, arg, off);
+    merge(m, l, arg, m2, l2, a2);
+  }
+  __shared__ float sm[kConfThreads / 32], sl[kConfThreads / 32];
+  __shared__ int sa[kConfThreads / 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    sm[warp] = m;
+    sl[warp] = l;
+    sa[warp] = arg;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kConfThreads / 32; ++w)
+      merge(m, l, arg, sm[w], sl[w], sa[w]);
+    conf[blockIdx.x] = l > 0.f ? 1.0f / l : 0.f;
+    token[blockIdx.x] = arg;
+  }
+}
+
 }  // namespace
 }  // namespace dyllm
 
@@ -172,6 +255,20 @@ int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, c
   rope_neox_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(x), positions, pos_idx,
                                                                         cos_sin, rows, heads, max_pos, num_rows_dev);
   return check_launch("rope_neox");
+}
+
+int dyllm_row_confidence(const void* logits, int rows, int vocab, int64_t pitch, float* conf, int64_t* token,
+                         void* stream) {
+  DYLLM_REQUIRE(rows >= 0 && vocab > 0 && pitch >= vocab, DYLLM_ERR_INVALID_ARGUMENT,
+                "row_confidence: rows %d vocab %d pitch %lld", rows, vocab, static_cast<long long>(pitch));
+  if (rows == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(logits && conf && token, DYLLM_ERR_INVALID_ARGUMENT, "row_confidence: null pointer");
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && pitch % 8 == 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "row_confidence: rows must start on 16-byte boundaries");
+  row_confidence_kernel<<<rows, kConfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), vocab, pitch, conf, token);
+  return check_launch("row_confidence");
 }
 
 }  // extern "C"

@@ -229,6 +229,20 @@ def rope_neox_(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, 
     return x
 
 
+def row_confidence(logits: torch.Tensor):
+    """(max softmax probability fp32 [rows], its token int64 [rows]) of bf16 logits [rows, vocab].
+
+    ref: dyllm/model_executor/layers/sampler.py:286-288.
+    """
+    require_cuda(logits, "logits", torch.bfloat16, 2)
+    rows = logits.size(0)
+    conf = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    token = torch.empty((rows,), dtype=torch.int64, device=logits.device)
+    call("dyllm_row_confidence", ptr(logits), rows, logits.size(1), logits.stride(0), ptr(conf), ptr(token),
+         stream_ptr(logits.device))
+    return conf, token
+
+
 def moe_route(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, renormalize: bool = False,
               idx: torch.Tensor | None = None, num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None):
     """fp32 softmax router with top-k selection; returns (weights fp32 [rows, k], expert ids int32 [rows, k]).

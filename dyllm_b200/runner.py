@@ -16,7 +16,7 @@ from typing import List
 import torch
 import torch.distributed as dist
 
-from . import _lib, profiling
+from . import _lib, ops, profiling
 from .context import get_context, get_metadata, set_context, set_metadata
 
 # Row-count estimate baked into the launches of a captured step: the common case is at most one 128-row
@@ -251,8 +251,7 @@ class StepRunner:
             rows = st.row_base_ro + (start - P) + st.blk_ar
         else:
             rows = st.row_base_full + start + st.blk_ar
-        cand = self._block_logits(hidden, rows.reshape(-1)).float().view(B, blk_len, -1)
-        conf, tok = torch.softmax(cand, dim=-1).max(dim=-1)
+        conf, tok = self._confidence(self._block_logits(hidden, rows.reshape(-1)), B, blk_len)
         cols = (start + st.blk_ar).expand(B, -1)
         still_masked = tokens.gather(1, cols) == self.mask_id
         conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
@@ -328,6 +327,16 @@ class StepRunner:
             return self.model.compute_logits(hidden).index_select(0, rows)
         return self.model.compute_logits(hidden.index_select(0, rows))
 
+    @staticmethod
+    def _confidence(logits: torch.Tensor, B: int, blk_len: int):
+        """Probability and id of the most likely token of every candidate row, as ``[B, blk_len]``
+        (ref: sampler.py:286-288, softmax then max)."""
+        if logits.is_cuda and logits.dtype == torch.bfloat16:
+            conf, tok = ops.row_confidence(logits.contiguous())
+        else:
+            conf, tok = torch.softmax(logits.float(), dim=-1).max(dim=-1)
+        return conf.view(B, blk_len), tok.view(B, blk_len)
+
     def _unmask(self, seqs: List[Sequence], hidden: torch.Tensor, ctx) -> int:
         B = len(seqs)
         gen = seqs[0].max_new_tokens
@@ -345,9 +354,7 @@ class StepRunner:
         rows_t = torch.stack(rows)
         io_bytes["h2d"] += rows_t.numel() * rows_t.element_size()
         rows_t = rows_t.to(self.device)
-        cand = self._block_logits(hidden, rows_t.flatten()).float().view(B, self.block_length, -1)
-        probs = torch.softmax(cand, dim=-1)
-        conf, tok = probs.max(dim=-1)
+        conf, tok = self._confidence(self._block_logits(hidden, rows_t.flatten()), B, self.block_length)
         still_masked = torch.tensor(
             [[seq.token_ids[p] == self.mask_id for p in cand_pos[b]] for b, seq in enumerate(seqs)])
         io_bytes["h2d"] += still_masked.numel()

@@ -308,6 +308,13 @@ int dyllm_moe_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int3
 int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weight, float eps, void* y,
                        void* residual_out, int rows, int width, void* stream);
 
+/* Confidence of the most likely token per row of bf16 logits [rows, vocab] (row pitch in elements,
+ * multiple of 8): conf[r] = max_j softmax(logits[r])_j in fp32, token[r] = the first j attaining the maximum.
+ * Replaces softmax + max over fp32 copies of the candidate logits.
+ * ref: dyllm/model_executor/layers/sampler.py:286-288 (F.softmax, probs.max). */
+int dyllm_row_confidence(const void* logits, int rows, int vocab, int64_t pitch, float* conf, int64_t* token,
+                         void* stream);
+
 /* NeoX-style rotary embedding applied in place to x [rows, heads, 128] (bf16): row r uses the angle
  * table row of positions[pos_idx ? pos_idx[r] : r], clamped to [0, max_pos); cos_sin is fp32
  * [max_pos, 128] = cos(64) | sin(64).  num_rows_dev (nullable) bounds the rows on the device.

@@ -46,3 +46,22 @@ def test_rope_neox(cuda_device, rows, heads):
                          pos_idx=idx.to(cuda_device))
     want = orc.rope(pos[idx], xi, 128, 500000.0, 512)
     torch.testing.assert_close(got.cpu().float(), want.float(), rtol=8e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("rows,vocab", [(7, 126464), (33, 1000), (4, 1021 + 3), (1, 8)])
+def test_row_confidence_matches_softmax_max(cuda_device, rows, vocab):
+    """max softmax probability and its token (ref: sampler.py:286-288), bf16 logits, fp32 arithmetic."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows * 7 + vocab)
+    logits = (torch.randn(rows, vocab, generator=g) * 4.0).bfloat16()
+    logits[0, vocab // 2] = 30.0          # one sharply peaked row
+    if rows > 1:
+        logits[1, 5] = logits[1].max()    # a tie: the first index wins
+    conf, tok = ops.row_confidence(logits.to(cuda_device))
+    want = torch.softmax(logits.double(), dim=-1)
+    want_conf, _ = want.max(dim=-1)
+    assert torch.allclose(conf.cpu().double(), want_conf, rtol=1e-4, atol=1e-7)
+    lf = logits.float()
+    first_max = (lf == lf.max(dim=-1, keepdim=True).values).float().argmax(dim=-1)
+    assert torch.equal(tok.cpu(), first_max)
