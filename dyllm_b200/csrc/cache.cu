@@ -83,6 +83,77 @@ scatter_rows_kernel(uint4* __restrict__ cache, const uint4* __restrict__ new_row
   }
 }
 
+// Everything that follows the K/V projection of the salient rows, in one pass (8 threads per row and
+// head, two 16-byte chunks of K and of V each):
+//   k_cache[row] = rope(k_new[i], position)      (NeoX halves of 64, fp32 table)
+//   dv[i] = v_new[i] - v_cache[row];  v_cache[row] = v_new[i]
+// with row = first cache row of the sequence + (rows_k[i] - cu_k[b]) in each cache.
+__global__ void __launch_bounds__(256)
+kv_cache_update_kernel(const uint4* __restrict__ k_new, const uint4* __restrict__ v_new,
+                       const int64_t* __restrict__ rows_k, const int64_t* __restrict__ positions,
+                       const int64_t* __restrict__ pos_idx, const float* __restrict__ cos_sin, int max_pos,
+                       const int32_t* __restrict__ cu_k, const int64_t* __restrict__ k_starts,
+                       const int64_t* __restrict__ v_starts, const int64_t* __restrict__ seq_ids, int batch,
+                       int num_rows, const int32_t* __restrict__ num_rows_dev, int heads,
+                       uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, uint4* __restrict__ dv) {
+  const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
+  const int64_t total = static_cast<int64_t>(n) * heads * 8;
+  for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int part = static_cast<int>(t & 7);          // which 8 of the 64 rotation pairs
+    const int64_t rh = t >> 3;
+    const int i = static_cast<int>(rh / heads);
+    const int h = static_cast<int>(rh - static_cast<int64_t>(i) * heads);
+    const int64_t r = rows_k[i];
+    const int b = seq_of_row(cu_k, batch, r);
+    const int64_t off = r - static_cast<int64_t>(cu_k[b]);
+    const int64_t sid = seq_ids[b];
+    int64_t pos = positions[pos_idx ? pos_idx[i] : i];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = cos_sin + pos * 128;
+    const int64_t src = rh * 16;                                   // 128 bf16 = 16 vectors per head
+    const int64_t kdst = ((k_starts[sid] + off) * heads + h) * 16;
+    const int64_t vdst = ((v_starts[sid] + off) * heads + h) * 16;
+    {
+      const uint4 a = __ldg(k_new + src + part), bb = __ldg(k_new + src + part + 8);
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
+      uint4 oa, ob;
+      __nv_bfloat162* oa2 = reinterpret_cast<__nv_bfloat162*>(&oa);
+      __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&ob);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x1 = __bfloat1622float2(a2[j]);
+        const float2 x2 = __bfloat1622float2(b2[j]);
+        const int d = part * 8 + 2 * j;
+        const float c0 = __ldg(cs + d), c1 = __ldg(cs + d + 1), s0 = __ldg(cs + 64 + d), s1 = __ldg(cs + 64 + d + 1);
+        oa2[j] = __floats2bfloat162_rn(x1.x * c0 - x2.x * s0, x1.y * c1 - x2.y * s1);
+        ob2[j] = __floats2bfloat162_rn(x2.x * c0 + x1.x * s0, x2.y * c1 + x1.y * s1);
+      }
+      k_cache[kdst + part] = oa;
+      k_cache[kdst + part + 8] = ob;
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int v = part + 8 * c;
+      const uint4 nv = __ldg(v_new + src + v);
+      const uint4 ov = v_cache[vdst + v];
+      uint4 out;
+      const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nv);
+      const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+      __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(n2[j]);
+        const float2 y = __bfloat1622float2(o2[j]);
+        d2[j] = __floats2bfloat162_rn(x.x - y.x, x.y - y.y);
+      }
+      dv[src + v] = out;
+      v_cache[vdst + v] = nv;
+    }
+  }
+}
+
 // dv[i] = v_new[i] - cache[rows[i]]; cache[rows[i]] = v_new[i]; one warp per row.
 __global__ void __launch_bounds__(kCopyWarps * 32)
 delta_v_update_kernel(const uint4* __restrict__ v_new, uint4* __restrict__ cache, const int32_t* __restrict__ rows,
@@ -201,6 +272,34 @@ int dyllm_delta_v_update(const void* v_new, void* cache, const int32_t* rows, in
       static_cast<const uint4*>(v_new), static_cast<uint4*>(cache), rows, num_rows, num_rows_dev, width / 8,
       static_cast<uint4*>(dv));
   return check_launch("delta_v_update");
+}
+
+int dyllm_kv_cache_update(const void* k_new, const void* v_new, const int64_t* rows_k, const int64_t* positions,
+                          const int64_t* pos_idx, const float* cos_sin, int max_pos, const int32_t* cu_seqlens_k,
+                          const int64_t* k_seq_starts, const int64_t* v_seq_starts, const int64_t* seq_ids, int batch,
+                          int num_rows, const int32_t* num_rows_dev, int kv_heads, int head_dim, void* k_cache,
+                          void* v_cache, void* dv, void* stream) {
+  DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "kv_cache_update: head_dim %d (only 128 is built)", head_dim);
+  DYLLM_REQUIRE(batch >= 0 && num_rows >= 0 && kv_heads > 0 && max_pos > 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "kv_cache_update: batch %d rows %d heads %d", batch, num_rows, kv_heads);
+  if (num_rows == 0 || batch == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(k_new && v_new && rows_k && positions && cos_sin && cu_seqlens_k && k_seq_starts && v_seq_starts &&
+                    seq_ids && k_cache && v_cache && dv,
+                DYLLM_ERR_INVALID_ARGUMENT, "kv_cache_update: null pointer");
+  DYLLM_REQUIRE(((reinterpret_cast<uintptr_t>(k_new) | reinterpret_cast<uintptr_t>(v_new) |
+                  reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                  reinterpret_cast<uintptr_t>(dv)) & 15) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "kv_cache_update: buffers must be 16-byte aligned");
+  const int64_t total = static_cast<int64_t>(num_rows) * kv_heads * 8;
+  const int64_t want = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int blocks = static_cast<int>(want < cap ? want : cap);
+  kv_cache_update_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new), rows_k, positions, pos_idx, cos_sin, max_pos,
+      cu_seqlens_k, k_seq_starts, v_seq_starts, seq_ids, batch, num_rows, num_rows_dev, kv_heads,
+      static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache), static_cast<uint4*>(dv));
+  return check_launch("kv_cache_update");
 }
 
 int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t* row_idx, const void* cu_seqlens,

@@ -410,9 +410,10 @@ class Attention(nn.Module):
         self._hint_event.record()
         return min(self._hint, capacity) if self._hint else capacity
 
-    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, dv: torch.Tensor | None = None) -> torch.Tensor:
         """Dense step: q, k, v hold every row.  Sparse step: ``q`` every query row, ``k`` the packed full
-        key tensor, ``v`` the new value rows of the step's salient tokens (reference convention)."""
+        key tensor, ``v`` the new value rows of the step's salient tokens (reference convention).  ``dv``:
+        the caller has already formed delta-V and updated the value cache (``ops.kv_cache_update``)."""
         ctx, md = get_context(), get_metadata()
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         seq_t = md.running_seqs_tensor
@@ -433,10 +434,11 @@ class Attention(nn.Module):
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
 
         # delta-V and value-cache update in one pass over the salient rows (attention.py:67-74,89-96)
-        dv = torch.empty((cap, Hkv, D), dtype=v.dtype, device=v.device)
-        if cap:
-            dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, self.v_cache.seq_start_gpu, seq_t, n_dev)
-            ops.delta_v_update(v.view(cap, Hkv * D), self.v_cache.cache, dest, dv.view(cap, Hkv * D), n_dev)
+        if dv is None:
+            dv = torch.empty((cap, Hkv, D), dtype=v.dtype, device=v.device)
+            if cap:
+                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, self.v_cache.seq_start_gpu, seq_t, n_dev)
+                ops.delta_v_update(v.view(cap, Hkv * D), self.v_cache.cache, dest, dv.view(cap, Hkv * D), n_dev)
         v_full = self.v_cache.get_seqs(seq_t, allow_view=True, seq_ids_list=md.running_seqs).view(-1, Hkv, D)
 
         # exact attention of the salient query rows (attention.py:76-87)

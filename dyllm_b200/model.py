@@ -76,18 +76,21 @@ class LLaDAAttention(nn.Module):
             cap = ctx.idx_salient_row.numel()   # capacity; the live count may sit on the device
             n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
             q = self.rotary_emb.rotate(positions, q)
+            dv = None
             if cap:
                 k_new, v_new = self.kv_proj.forward_gathered(hidden_states, ctx.idx_salient_row32, cap, n_dev, hint,
                                                              split_col=self.kv_size)
-                ops.rope_neox_(k_new.view(cap, Hkv, D), positions, self.rotary_emb.cos_sin_cache.view(-1, D),
-                               pos_idx=ctx.idx_salient_row, num_rows_dev=n_dev)
                 rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
-                self.k_cache.scatter_update(md.running_seqs_tensor, rows_k, k_new, n_dev)
                 v_new = v_new.view(cap, Hkv, D)
+                # rotary embedding of the new keys, K-cache scatter, delta-V and V-cache update in one launch
+                dv = ops.kv_cache_update(k_new.view(cap, Hkv, D), v_new, rows_k, positions, ctx.idx_salient_row,
+                                         self.rotary_emb.cos_sin_cache.view(-1, D), ctx.cu_seqlens_k,
+                                         self.k_cache.seq_start_gpu, self.attn.v_cache.seq_start_gpu,
+                                         md.running_seqs_tensor, self.k_cache.cache, self.attn.v_cache.cache, n_dev)
             else:
                 v_new = torch.empty((0, Hkv, D), dtype=q.dtype, device=q.device)
             k_full = self.k_cache.get_seqs(md.running_seqs_tensor, allow_view=True, seq_ids_list=md.running_seqs)
-            o = self.attn(q, k_full.view(-1, Hkv, D), v_new)
+            o = self.attn(q, k_full.view(-1, Hkv, D), v_new, dv=dv)
         out = self.o_proj(o.flatten(-2, -1))
         self.k_cache.finish(md.finished_seqs)
         return out

@@ -196,6 +196,35 @@ def delta_v_update(v_new: torch.Tensor, cache: torch.Tensor, rows: torch.Tensor,
     return dv
 
 
+def kv_cache_update(k_new: torch.Tensor, v_new: torch.Tensor, rows_k: torch.Tensor, positions: torch.Tensor,
+                    pos_idx: torch.Tensor | None, cos_sin: torch.Tensor, cu_seqlens_k: torch.Tensor,
+                    k_seq_starts: torch.Tensor, v_seq_starts: torch.Tensor, seq_ids: torch.Tensor,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, num_rows_dev: torch.Tensor | None = None,
+                    dv: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotary embedding of the new K rows + K-cache scatter + delta-V + V-cache update in one launch;
+    returns dV ``[rows, kv_heads, 128]``.
+
+    ref: dyllm/model_executor/models/llada.py:108-118; dyllm/model_executor/layers/attention.py:67-74,89-96.
+    """
+    require_cuda(k_new, "k_new", torch.bfloat16, 3)
+    require_cuda(v_new, "v_new", torch.bfloat16, 3)
+    require_cuda(rows_k, "rows_k", torch.int64, 1)
+    require_cuda(positions, "positions", torch.int64, 1)
+    require_cuda(cos_sin, "cos_sin", torch.float32)
+    require_cuda(cu_seqlens_k, "cu_seqlens_k", torch.int32, 1)
+    require_cuda(k_cache, "k_cache", torch.bfloat16, 2)
+    require_cuda(v_cache, "v_cache", torch.bfloat16, 2)
+    if dv is None:
+        dv = torch.empty_like(v_new)
+    n = k_new.size(0)
+    if n == 0:
+        return dv
+    call("dyllm_kv_cache_update", ptr(k_new), ptr(v_new), ptr(rows_k), ptr(positions), ptr(pos_idx), ptr(cos_sin),
+         cos_sin.size(0), ptr(cu_seqlens_k), ptr(k_seq_starts), ptr(v_seq_starts), ptr(seq_ids), seq_ids.numel(), n,
+         ptr(num_rows_dev), k_new.size(1), k_new.size(2), ptr(k_cache), ptr(v_cache), ptr(dv), stream_ptr(k_new.device))
+    return dv
+
+
 def add_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
     """RMSNorm with the residual add fused in; returns ``y`` or ``(y, new_residual)``.
 

@@ -300,6 +300,20 @@ int dyllm_moe_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int3
  * Row-wise kernels around the path (every query row, HBM-bound)
  * ---------------------------------------------------------------------------------------------- */
 
+/* Everything between the K/V projection of the salient rows and the attention kernels, in one launch:
+ *   k_cache[row_k(i)] = rope_neox(k_new[i], positions[pos_idx ? pos_idx[i] : i])
+ *   dv[i] = v_new[i] - v_cache[row_v(i)];  v_cache[row_v(i)] = v_new[i]
+ * k_new, v_new, dv: [num_rows, kv_heads, 128] bf16; rows_k: packed K-space rows (as for scatter_update);
+ * row_x(i) = x_seq_starts[seq_ids[b]] + (rows_k[i] - cu_seqlens_k[b]) for the sequence b that holds the row;
+ * cos_sin: fp32 [max_pos, 128]; num_rows_dev (nullable) bounds the rows on the device.
+ * ref: dyllm/model_executor/models/llada.py:108-118 (rotary embedding of the new keys, k_cache.scatter_update)
+ * and dyllm/model_executor/layers/attention.py:67-74,89-96 (delta-V, v_cache.scatter_update). */
+int dyllm_kv_cache_update(const void* k_new, const void* v_new, const int64_t* rows_k, const int64_t* positions,
+                          const int64_t* pos_idx, const float* cos_sin, int max_pos, const int32_t* cu_seqlens_k,
+                          const int64_t* k_seq_starts, const int64_t* v_seq_starts, const int64_t* seq_ids, int batch,
+                          int num_rows, const int32_t* num_rows_dev, int kv_heads, int head_dim, void* k_cache,
+                          void* v_cache, void* dv, void* stream);
+
 /* RMSNorm with the residual add fused in (bf16 in / out, fp32 statistics):
  *   s = x + residual_in (residual_in null = 0);  residual_out = bf16(s) (nullable);
  *   y = bf16( bf16(s * rsqrt(mean(s^2) + eps)) * weight ).

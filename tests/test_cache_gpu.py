@@ -93,3 +93,46 @@ def test_errors_are_runtime_errors(cuda_device):
         C.get_seqs_cuda(d(cache)[:, :3].contiguous(), d(ss), d(cu), d(ids), 4)  # row not a multiple of 16 bytes
     with pytest.raises(RuntimeError):
         C.reset_full_cuda(d(cache), d(cache)[:, :4].contiguous(), d(ss), d(cu), d(ids), 4)
+
+
+@pytest.mark.parametrize("live", [37, 0])
+def test_kv_cache_update_equals_the_separate_steps(cuda_device, live):
+    """rope of the new keys + K-cache scatter + delta-V + V-cache update in one launch gives the same bits
+    as rope_neox_ / scatter_update_cuda / cache_dest_rows / delta_v_update one after the other."""
+    from dyllm_b200 import cache as C
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(5)
+    B, L, Hkv, D, cap = 3, 96, 2, 128, 64
+    dev = cuda_device
+    cu = (torch.arange(B + 1) * L).to(torch.int32).to(dev)
+    seq_ids = torch.tensor([2, 0, 1], device=dev)
+    k_starts = torch.tensor([L, 2 * L + 8, 0], device=dev)          # per sequence id; the two caches differ
+    v_starts = torch.tensor([2 * L, 0, L + 5], device=dev)
+    k_cache = torch.randn(3 * L + 16, Hkv * D, generator=g).bfloat16().to(dev)
+    v_cache = torch.randn(3 * L + 16, Hkv * D, generator=g).bfloat16().to(dev)
+    rows_k = torch.sort(torch.randperm(B * L, generator=g)[:cap]).values.to(dev)
+    positions = torch.randint(0, 300, (B * L,), generator=g).to(dev)
+    pos_idx = torch.randint(0, B * L, (cap,), generator=g).to(dev)
+    k_new = torch.randn(cap, Hkv, D, generator=g).bfloat16().to(dev)
+    v_new = torch.randn(cap, Hkv, D, generator=g).bfloat16().to(dev)
+    t = torch.arange(512, dtype=torch.float)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+    f = torch.einsum("i,j->ij", t, inv)
+    cos_sin = torch.cat((f.cos(), f.sin()), dim=-1).to(dev)
+    n_dev = torch.tensor([live], dtype=torch.int32, device=dev)
+
+    k1, v1 = k_cache.clone(), v_cache.clone()
+    kr = ops.rope_neox_(k_new.clone(), positions, cos_sin, pos_idx=pos_idx, num_rows_dev=n_dev)
+    C.scatter_update_cuda(k1, kr.view(cap, -1), rows_k, cu, k_starts, seq_ids, n_dev)
+    dest = ops.cache_dest_rows(rows_k, cu, v_starts, seq_ids, n_dev)
+    dv1 = torch.zeros(cap, Hkv * D, dtype=torch.bfloat16, device=dev)
+    ops.delta_v_update(v_new.view(cap, -1), v1, dest, dv1, n_dev)
+
+    k2, v2 = k_cache.clone(), v_cache.clone()
+    dv2 = torch.zeros(cap, Hkv, D, dtype=torch.bfloat16, device=dev)
+    ops.kv_cache_update(k_new, v_new, rows_k, positions, pos_idx, cos_sin, cu, k_starts, v_starts, seq_ids, k2, v2,
+                        n_dev, dv=dv2)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.equal(dv1.view(cap, Hkv, D)[:live], dv2[:live])
+    assert bool((dv2[live:] == 0).all())
