@@ -77,8 +77,21 @@ class CacheManager:
                 return self._arena[start : start + ctx.total_seqlen_k]
         return get_seqs_cuda(self.cache, self.seq_start_gpu, ctx.cu_seqlens_k, seq_ids, total)
 
-    def get_seqs_block(self, seq_ids: torch.Tensor) -> torch.Tensor:
+    def get_seqs_block(self, seq_ids: torch.Tensor, allow_view: bool = False,
+                       seq_ids_list: Optional[List[int]] = None) -> torch.Tensor:
+        """The last ``len_q`` rows of every running sequence, packed.  With ``allow_view``, when the
+        sequences lie back to back in batch order and have equal lengths, a strided
+        ``[batch, len_q, hidden]`` view of the cache is returned instead of a copy."""
         ctx = get_context()
+        if allow_view and ctx.context_lens_cpu and ctx.cu_seqlens_q_cpu:
+            lens = ctx.context_lens_cpu
+            cu_q = ctx.cu_seqlens_q_cpu
+            n = len(lens)
+            len_k, len_q = lens[0], cu_q[1] - cu_q[0]
+            uniform = all(l == len_k for l in lens) and all(cu_q[i + 1] - cu_q[i] == len_q for i in range(n))
+            start = self.contiguous_start(seq_ids_list) if uniform else -1
+            if start >= 0 and start + n * len_k <= self._rows and 0 < len_q <= len_k:
+                return self._arena[start : start + n * len_k].view(n, len_k, self.hidden_dim)[:, len_k - len_q :, :]
         return get_block_cuda(self.cache, self.seq_start_gpu, ctx.cu_seqlens_k, ctx.cu_seqlens_q, seq_ids,
                               ctx.total_seqlen)
 

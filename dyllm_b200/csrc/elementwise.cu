@@ -13,9 +13,13 @@ constexpr int kNormThreads = 256;
 template <int VPT>
 __global__ void __launch_bounds__(kNormThreads)
 add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
-                    uint4* __restrict__ y, uint4* __restrict__ res_out, int vecs, float inv_width, float eps) {
+                    uint4* __restrict__ y, uint4* __restrict__ res_out, int vecs, float inv_width, float eps,
+                    int x_seg_rows, int64_t x_seg_pitch_rows) {
   const int64_t row = blockIdx.x;
-  const uint4* xr = x + row * vecs;
+  // x may consist of equal segments of rows that lie x_seg_pitch_rows apart (a block of every sequence
+  // read straight out of a cache); everything else is packed
+  const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
+  const uint4* xr = x + x_row * vecs;
   const uint4* rr = res_in ? res_in + row * vecs : nullptr;
   float vals[VPT][8];
   float ss = 0.f;
@@ -210,7 +214,17 @@ extern "C" {
 
 int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weight, float eps, void* y,
                        void* residual_out, int rows, int width, void* stream) {
+  return dyllm_add_rms_norm_segmented(x, rows > 0 ? rows : 1, rows > 0 ? rows : 1, residual_in, weight, eps, y,
+                                      residual_out, rows, width, stream);
+}
+
+int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
+                                 const void* weight, float eps, void* y, void* residual_out, int rows, int width,
+                                 void* stream) {
   DYLLM_REQUIRE(rows >= 0 && width > 0, DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm: rows %d width %d", rows, width);
+  DYLLM_REQUIRE(x_seg_rows > 0 && x_seg_pitch_rows >= x_seg_rows, DYLLM_ERR_INVALID_ARGUMENT,
+                "add_rms_norm: segments of %d rows, %lld rows apart", x_seg_rows,
+                static_cast<long long>(x_seg_pitch_rows));
   DYLLM_REQUIRE(width % 8 == 0 && width <= 8 * kNormThreads * 4, DYLLM_ERR_UNSUPPORTED,
                 "add_rms_norm: width %d must be a multiple of 8 and at most %d", width, 8 * kNormThreads * 4);
   if (rows == 0)
@@ -230,10 +244,10 @@ int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weigh
   uint4* rop = static_cast<uint4*>(residual_out);
   const float inv = 1.0f / static_cast<float>(width);
   switch (vpt) {
-    case 1: add_rms_norm_kernel<1><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
-    case 2: add_rms_norm_kernel<2><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
-    case 3: add_rms_norm_kernel<3><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
-    default: add_rms_norm_kernel<4><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps); break;
+    case 1: add_rms_norm_kernel<1><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    case 2: add_rms_norm_kernel<2><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    case 3: add_rms_norm_kernel<3><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    default: add_rms_norm_kernel<4><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
   }
   return check_launch("add_rms_norm");
 }

@@ -162,8 +162,12 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size))
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
-        if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and self.weight.dtype == torch.bfloat16:
-            return ops.add_rms_norm(x.contiguous(), self.weight, self.eps, residual)
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            if x.dim() == 2:
+                return ops.add_rms_norm(x.contiguous(), self.weight, self.eps, residual)
+            if x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.size(2):
+                # equal blocks of rows inside a cache: read in place, packed outputs
+                return ops.add_rms_norm(x, self.weight, self.eps, residual)
         orig = x.dtype
         xf = x.float()
         if residual is not None:
@@ -220,12 +224,17 @@ class MLPcache(nn.Module):
     def __init__(self, hidden_dim: int = 0):
         super().__init__()
         self.cache_manager = CacheManager(hidden_dim=hidden_dim)
+        # When set (by a model whose next operation is this package's RMSNorm), response-only steps return
+        # a strided [batch, len_q, hidden] view of the cache instead of a packed copy.
+        self.block_view = False
 
     def result(self) -> torch.Tensor:
         """The full ``[T_q, hidden]`` activation of the step after the cache has been updated."""
         ctx, md = get_context(), get_metadata()
         if not ctx.is_full and ctx.idx_salient_row_k is not None:
-            return self.cache_manager.get_seqs_block(md.running_seqs_tensor)
+            # may be a strided [batch, len_q, hidden] view of the cache (the norm that follows reads it in place)
+            return self.cache_manager.get_seqs_block(md.running_seqs_tensor, allow_view=self.block_view,
+                                                     seq_ids_list=md.running_seqs)
         return self.cache_manager.get_seqs(md.running_seqs_tensor, allow_view=True, seq_ids_list=md.running_seqs)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -130,6 +130,10 @@ class LLaDAModel(nn.Module):
         rope = RotaryEmbedding(config.head_dim, config.head_dim, config.max_sequence_length, config.rope_theta)
         self.layers = nn.ModuleList([LLaDADecoderLayer(config, threshold, rope) for _ in range(config.num_hidden_layers)])
         self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        # every layer's output goes straight into an RMSNorm of this package (the next layer's or the final
+        # one), which reads a block of every sequence out of the FFN-output cache in place
+        for layer in self.layers:
+            layer.mlp.cache_update.block_view = True
 
     def forward(self, input_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         hidden_states = self.embed_tokens(input_ids)

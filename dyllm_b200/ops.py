@@ -226,19 +226,34 @@ def kv_cache_update(k_new: torch.Tensor, v_new: torch.Tensor, rows_k: torch.Tens
 
 
 def add_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None = None):
-    """RMSNorm with the residual add fused in; returns ``y`` or ``(y, new_residual)``.
+    """RMSNorm with the residual add fused in; returns ``y`` or ``(y, new_residual)`` as packed 2-D tensors.
+
+    ``x`` is ``[rows, width]`` contiguous, or ``[segments, seg_rows, width]`` whose rows are contiguous and
+    whose segments lie a whole number of rows apart (a view of a block of every sequence inside a cache).
 
     ref: dyllm/model_executor/layers/layernorm.py:17-53.
     """
-    require_cuda(x, "x", torch.bfloat16, 2)
+    if not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.bfloat16:
+        raise RuntimeError("x must be a CUDA bfloat16 tensor")
     require_cuda(weight, "weight", torch.bfloat16, 1)
-    y = torch.empty_like(x)
+    width = x.size(-1)
+    if x.dim() == 2:
+        require_cuda(x, "x", torch.bfloat16, 2)
+        rows, seg_rows, seg_pitch = x.size(0), max(x.size(0), 1), max(x.size(0), 1)
+    elif x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == width and x.stride(0) % width == 0 \
+            and x.stride(0) >= x.size(1) * width:
+        rows, seg_rows, seg_pitch = x.size(0) * x.size(1), x.size(1), x.stride(0) // width
+    else:
+        raise RuntimeError("x must be [rows, width] contiguous or [segments, rows, width] with contiguous rows")
+    y = torch.empty((rows, width), dtype=x.dtype, device=x.device)
     res_out = None
     if residual is not None:
         require_cuda(residual, "residual", torch.bfloat16, 2)
-        res_out = torch.empty_like(x)
-    call("dyllm_add_rms_norm", ptr(x), ptr(residual), ptr(weight), float(eps), ptr(y), ptr(res_out), x.size(0),
-         x.size(1), stream_ptr(x.device))
+        if residual.shape != y.shape:
+            raise RuntimeError("residual must be [rows, width]")
+        res_out = torch.empty_like(y)
+    call("dyllm_add_rms_norm_segmented", ptr(x), seg_rows, seg_pitch, ptr(residual), ptr(weight), float(eps), ptr(y),
+         ptr(res_out), rows, width, stream_ptr(x.device))
     return y if residual is None else (y, res_out)
 
 

@@ -322,6 +322,14 @@ int dyllm_kv_cache_update(const void* k_new, const void* v_new, const int64_t* r
 int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weight, float eps, void* y,
                        void* residual_out, int rows, int width, void* stream);
 
+/* The same with x given as equal segments: packed row r is row
+ * (r / x_seg_rows) * x_seg_pitch_rows + r % x_seg_rows of x.  This reads a block of every sequence (for
+ * example the response rows) straight out of an activation cache whose sequences have equal lengths,
+ * instead of a packed copy made by dyllm_cache_get_block.  residual_in, y, residual_out are packed. */
+int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
+                                 const void* weight, float eps, void* y, void* residual_out, int rows, int width,
+                                 void* stream);
+
 /* Confidence of the most likely token per row of bf16 logits [rows, vocab] (row pitch in elements,
  * multiple of 8): conf[r] = max_j softmax(logits[r])_j in fp32, token[r] = the first j attaining the maximum.
  * Replaces softmax + max over fp32 copies of the candidate logits.

@@ -65,3 +65,21 @@ def test_row_confidence_matches_softmax_max(cuda_device, rows, vocab):
     lf = logits.float()
     first_max = (lf == lf.max(dim=-1, keepdim=True).values).float().argmax(dim=-1)
     assert torch.equal(tok.cpu(), first_max)
+
+
+def test_add_rms_norm_reads_equal_blocks_in_place(cuda_device):
+    """x given as a strided [segments, rows, width] view (the last rows of every sequence inside a cache)
+    gives the same bits as the packed copy."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(11)
+    B, L, R, W = 5, 48, 20, 512
+    cache = torch.randn(B * L + 7, W, generator=g).bfloat16().to(cuda_device)
+    w = (1.0 + 0.1 * torch.randn(W, generator=g)).bfloat16().to(cuda_device)
+    res = torch.randn(B * R, W, generator=g).bfloat16().to(cuda_device)
+    view = cache[3 : 3 + B * L].view(B, L, W)[:, L - R :, :]
+    packed = view.reshape(B * R, W).contiguous()
+    y1, r1 = ops.add_rms_norm(packed, w, 1e-5, res)
+    y2, r2 = ops.add_rms_norm(view, w, 1e-5, res)
+    assert torch.equal(y1, y2) and torch.equal(r1, r2)
+    assert torch.equal(ops.add_rms_norm(packed, w, 1e-5), ops.add_rms_norm(view, w, 1e-5))
