@@ -9,6 +9,7 @@ and multi-process control of the reference engine are outside this package.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from types import SimpleNamespace
 from typing import List
@@ -133,7 +134,7 @@ class StepRunner:
 
     def __init__(self, model, mask_id: int, block_length: int = 32, steps: int = 256, num_full_steps: int = 8,
                  refresh_period: int = 4, use_graphs: bool = True, full_logits: bool = False,
-                 graphs_with_tp: bool = False):
+                 graphs_with_tp: bool | None = None):
         self.model = model
         self.mask_id = mask_id
         self.block_length = block_length
@@ -144,7 +145,10 @@ class StepRunner:
         self.salient_counts: list[int] = []
         self.use_graphs = use_graphs
         # Capturing steps that contain NCCL all-reduces did not complete on two GPUs (the run stopped making
-        # progress and was ended by its time limit), so several ranks launch eagerly unless this is set.
+        # progress and was ended by its time limit, with the default and with the thread-local capture error
+        # mode), so several ranks launch eagerly unless this is set (or DYLLM_GRAPHS_WITH_TP=1).
+        if graphs_with_tp is None:
+            graphs_with_tp = os.environ.get("DYLLM_GRAPHS_WITH_TP", "0") == "1"
         self.graphs_with_tp = graphs_with_tp
         # The reference projects every query row onto the vocabulary and then indexes the rows of the
         # current block (model_runner.py:377, sampler.py:244-315); with full_logits False only the rows the
