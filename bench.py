@@ -194,8 +194,9 @@ def config_dict(n_gpus: int):
                         "step as in the reference code), tau 0.99",
             "global_batch": BATCH, "prompt_len": PROMPT, "gen_len": GEN, "parallelism": f"tp{n_gpus}",
             "l2": "inputs_larger_than_l2 (16 GB of weights streamed per denoising step)",
-            "step_driver": "device-resident loop; at one GPU each denoising step replays a captured CUDA graph; "
-                           "the vocabulary projection runs on the rows the sampler reads (current block)"}
+            "step_driver": "device-resident loop; each denoising step replays a captured CUDA graph (with several "
+                           "ranks: a chain of graphs with the NCCL all-reduces issued between them); the "
+                           "vocabulary projection runs on the rows the sampler reads (current block)"}
 
 
 # ----------------------------------------------------------------------------------------------

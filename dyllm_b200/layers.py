@@ -31,6 +31,25 @@ def _rank() -> int:
     return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
 
 
+# A step driver that captures the launches of a step into CUDA graphs installs a hook here: every SUM
+# all-reduce of the layers goes through it, so that the driver can close the graph it is capturing, issue
+# the collective outside any capture and open the next graph.
+_all_reduce_hook = None
+
+
+def set_all_reduce_hook(hook) -> None:
+    global _all_reduce_hook
+    _all_reduce_hook = hook
+
+
+def all_reduce_sum(t: torch.Tensor) -> None:
+    """In-place SUM all-reduce over the tensor-parallel group."""
+    if _all_reduce_hook is not None:
+        _all_reduce_hook(t)
+    else:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+
+
 def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.Tensor:
     """SUM all-reduce of the 12-byte-per-token statistics, then ``cosine < threshold``.
 
@@ -38,7 +57,7 @@ def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.
     statistics live on a GPU.
     """
     if _world_size() > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+        all_reduce_sum(stats)
     if stats.is_cuda and stats.dim() == 2:
         return ops.cosine_mask(stats, threshold)
     dot = stats[..., 0]
@@ -148,7 +167,7 @@ class RowParallelLinear(LinearBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
         if self.tp_size > 1:
-            dist.all_reduce(y)
+            all_reduce_sum(y)
         return y
 
 
@@ -263,7 +282,7 @@ class LLaDAMLP(nn.Module):
         gathered salient rows of a sparse step)."""
         y = ops.swiglu_ffn(x, self.gate_up_proj.weight, self.down_proj.weight)
         if self.down_proj.tp_size > 1:
-            dist.all_reduce(y)
+            all_reduce_sum(y)
         return self.cache_update(y)
 
     def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -280,7 +299,7 @@ class LLaDAMLP(nn.Module):
             if self.down_proj.tp_size > 1:
                 y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
                                    num_rows=cap, num_rows_dev=n_dev, rows_hint=hint)
-                dist.all_reduce(y)
+                all_reduce_sum(y)
                 cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
@@ -340,7 +359,7 @@ class LLaDAMoESparseBlock(nn.Module):
         """Reference calling convention: ``x`` holds the rows to process."""
         y = self._experts(x, None, x.size(0), None, 0)
         if _world_size() > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM)
+            all_reduce_sum(y)
         return self.cache_update(y)
 
     def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
@@ -354,7 +373,7 @@ class LLaDAMoESparseBlock(nn.Module):
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
             if _world_size() > 1:
                 y = self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint)
-                dist.all_reduce(y, op=dist.ReduceOp.SUM)
+                all_reduce_sum(y)
                 cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
@@ -476,7 +495,7 @@ class Attention(nn.Module):
         # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch; the new
         # lists stay on the device together with their length
         if _world_size() > 1:
-            dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+            all_reduce_sum(stats)
         with profiling.region("salient_select", 0.0, 12.0 * ctx.total_seqlen):
             sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,
                                      ctx.cu_promptlens if is_q_pruned else None)

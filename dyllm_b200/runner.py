@@ -25,6 +25,57 @@ from .context import get_context, get_metadata, set_context, set_metadata
 GRAPH_ROWS_HINT = 128
 
 
+class _SegmentedCapture:
+    """Captures a step that contains collectives as a chain of CUDA graphs with the collectives between
+    them: a graph is closed at every all-reduce, the all-reduce is issued eagerly (outside any capture) and
+    the next graph is opened.  Replay walks the chain; the host then makes one call per graph and per
+    collective instead of one per kernel."""
+
+    def __init__(self, pool):
+        self.pool = pool
+        self.items: list = []          # ("graph", CUDAGraph) | ("reduce", tensor)
+        self.stream = torch.cuda.Stream()
+        self._graph = None
+
+    def _begin(self) -> None:
+        self._graph = torch.cuda.CUDAGraph()
+        self._graph.capture_begin(pool=self.pool)
+
+    def _end(self) -> None:
+        self._graph.capture_end()
+        self.items.append(("graph", self._graph))
+        self._graph = None
+
+    def on_all_reduce(self, t: torch.Tensor) -> None:
+        self._end()
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)     # keeps the ranks in step; the data is not meaningful yet
+        self.items.append(("reduce", t))
+        self._begin()
+
+    def capture(self, fn) -> None:
+        from . import layers
+
+        torch.cuda.synchronize()
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            layers.set_all_reduce_hook(self.on_all_reduce)
+            self._begin()
+            try:
+                fn()
+            finally:
+                layers.set_all_reduce_hook(None)
+                if self._graph is not None:
+                    self._end()
+        torch.cuda.current_stream().wait_stream(self.stream)
+
+    def replay(self) -> None:
+        for kind, obj in self.items:
+            if kind == "graph":
+                obj.replay()
+            else:
+                dist.all_reduce(obj, op=dist.ReduceOp.SUM)
+
+
 def _multi_rank() -> bool:
     return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
 
@@ -144,11 +195,13 @@ class StepRunner:
         self.device = next(model.parameters()).device
         self.salient_counts: list[int] = []
         self.use_graphs = use_graphs
-        # Capturing steps that contain NCCL all-reduces did not complete on two GPUs (the run stopped making
-        # progress and was ended by its time limit, with the default and with the thread-local capture error
-        # mode), so several ranks launch eagerly unless this is set (or DYLLM_GRAPHS_WITH_TP=1).
+        # A captured step with the NCCL all-reduces inside did not complete on two GPUs (the run stopped
+        # making progress, with the default and with the thread-local capture error mode).  With several
+        # ranks a step is therefore captured as a chain of graphs with the all-reduces issued eagerly between
+        # them (_SegmentedCapture); graphs_with_tp=False (or DYLLM_GRAPHS_WITH_TP=0) launches every kernel
+        # eagerly instead.
         if graphs_with_tp is None:
-            graphs_with_tp = os.environ.get("DYLLM_GRAPHS_WITH_TP", "0") == "1"
+            graphs_with_tp = os.environ.get("DYLLM_GRAPHS_WITH_TP", "1") != "0"
         self.graphs_with_tp = graphs_with_tp
         # The reference projects every query row onto the vocabulary and then indexes the rows of the
         # current block (model_runner.py:377, sampler.py:244-315); with full_logits False only the rows the
@@ -286,14 +339,18 @@ class StepRunner:
                 finally:
                     st.fixed_hint = 0
                 return
-            graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             before = _lib.launch_count
             st.fixed_hint = GRAPH_ROWS_HINT
             try:
-                with torch.cuda.graph(graph, pool=self._graph_pool):
-                    self._device_step(st, kind)
+                if _multi_rank():
+                    graph = _SegmentedCapture(self._graph_pool)
+                    graph.capture(lambda: self._device_step(st, kind))
+                else:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, pool=self._graph_pool):
+                        self._device_step(st, kind)
             finally:
                 st.fixed_hint = 0
             entry = self._graphs[key] = (graph, _lib.launch_count - before)
