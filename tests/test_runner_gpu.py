@@ -45,3 +45,50 @@ def test_device_state_generation_equals_host_driven_generation(cuda_device):
     assert first == dev and second == dev
     other = torch.randint(0, 900, (3, 40), generator=g).tolist()
     assert gr.generate(other, 32) == sr.generate(other, 32, device_state=True)
+
+
+_SEGMENT_SCRIPT = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, os.getcwd())
+torch.cuda.set_device(0)
+dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % int(sys.argv[1]), rank=0, world_size=1,
+                        device_id=torch.device("cuda:0"))
+from dyllm_b200 import layers, runner
+x = torch.arange(8, dtype=torch.float32, device="cuda")
+out = torch.zeros(8, device="cuda")
+def step():
+    a = x * 2
+    layers.all_reduce_sum(a)      # world size 1: identity, but it cuts the capture
+    b = a + 1
+    layers.all_reduce_sum(b)
+    out.copy_(b * 3)
+seg = runner._SegmentedCapture(torch.cuda.graph_pool_handle())
+seg.capture(step)
+kinds = [k for k, _ in seg.items]
+assert kinds == ["graph", "reduce", "graph", "reduce", "graph"], kinds
+for scale in (1.0, 5.0):
+    x.copy_(torch.arange(8, dtype=torch.float32) * scale)
+    seg.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out.cpu(), (torch.arange(8, dtype=torch.float32) * scale * 2 + 1) * 3)
+assert layers._all_reduce_hook is None
+dist.destroy_process_group()
+print("segments ok")
+"""
+
+
+def test_segmented_capture_cuts_graphs_at_collectives(cuda_device, tmp_path):
+    """A step with collectives is captured as graph / all-reduce / graph ...; replay follows new inputs."""
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = tmp_path / "segments.py"
+    script.write_text(_SEGMENT_SCRIPT)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, str(script), str(port)], cwd=root, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "segments ok" in res.stdout, res.stdout + res.stderr
