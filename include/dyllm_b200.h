@@ -200,9 +200,9 @@ size_t dyllm_attention_sparse_workspace_bytes(int total_q, int num_heads);
 /* out[r] = bf16( c[r] + softmax(q_r K^T / sqrt(D)) V ) for all total_q query rows, where V is the
  * delta-V tensor of the step: it must be zero on every key row that is not listed in
  * idx_salient_row_k (the reference's caller builds it that way; only the listed rows are read).
- * Rows listed in idx_salient_row_q are then replaced by o_sal, and
- *   cosine_stats[r] += {dot(new, c), |new|^2, |c|^2}   (fp32 value before rounding; caller zero-fills)
- *   cosine_stats[r]  = the same from the bf16 o_sal row for the replaced rows
+ * Rows listed in idx_salient_row_q take the o_sal row as their new value instead, and
+ *   cosine_stats[r] += {dot(new, c), |new|^2, |c|^2}   (caller zero-fills; new is the fp32 value before
+ *                      rounding, or the bf16 o_sal row for the replaced rows)
  *   cosine_out[r]    = cosine(cosine_stats[r]) < threshold
  * q, c, out: [total_q, num_heads, 128]; k, v: [total_k, num_kv_heads, 128]; o_sal: [num_salient,
  * num_heads, 128]; all bf16.  idx_salient_row_q (query space) and idx_salient_row_k (key space) hold
