@@ -46,13 +46,26 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_attention_sparse_varlen": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P, I, P, P, P, F, P, Z, I, P, P, I, P]),
     "dyllm_attention_salient_rows": (I, [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P]),
     "dyllm_attention_kernel_info": (I, [I, P]),
-    "dyllm_attention_trace": (I, [P]),
     "dyllm_delta_v_update": (I, [P, P, P, I, P, I, P, P]),
     "dyllm_add_rms_norm": (I, [P, P, P, F, P, P, I, I, P]),
     "dyllm_add_rms_norm_segmented": (I, [P, I, c_int64, P, P, F, P, P, I, I, P]),
     "dyllm_rope_neox": (I, [P, P, P, P, I, P, I, I, I, P]),
     "dyllm_row_confidence": (I, [P, I, I, c_int64, P, P, P]),
     "dyllm_kv_cache_update": (I, [P, P, P, P, P, P, I, P, P, P, P, I, I, P, I, I, P, P, P, P]),
+    "dyllm_tp_comm_create": (I, [I, I, Z, P]),
+    "dyllm_tp_comm_region_bytes": (Z, [P]),
+    "dyllm_tp_comm_region": (P, [P]),
+    "dyllm_tp_comm_ipc_handle": (I, [P, P]),
+    "dyllm_tp_comm_open_ipc": (I, [P, P]),
+    "dyllm_tp_comm_open_local": (I, [P, P]),
+    "dyllm_tp_comm_set_wait_ms": (I, [P, I]),
+    "dyllm_tp_comm_destroy": (I, [P]),
+    "dyllm_tp_push_rows": (I, [P, P, I, I, P, I, P]),
+    "dyllm_tp_reduce_rows": (I, [P, I, I, P, I, P, c_int64, P, P]),
+    "dyllm_tp_allreduce_rows": (I, [P, P, I, I, P, I, P, c_int64, P, P]),
+    "dyllm_tp_push_f32": (I, [P, P, I, P]),
+    "dyllm_tp_reduce_f32": (I, [P, P, I, P]),
+    "dyllm_tp_allreduce_f32": (I, [P, P, I, P]),
 }
 
 # kernels of this library launched by one call of each entry point (for launch accounting)
@@ -63,6 +76,8 @@ KERNELS_PER_CALL = {
     "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 2, "dyllm_swiglu_ffn": 3, "dyllm_cache_dest_rows": 1, "dyllm_moe_route": 1, "dyllm_moe_ffn": 5,
     "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 2, "dyllm_delta_v_update": 1,
     "dyllm_add_rms_norm": 1, "dyllm_add_rms_norm_segmented": 1, "dyllm_rope_neox": 1, "dyllm_row_confidence": 1, "dyllm_kv_cache_update": 1,
+    "dyllm_tp_push_rows": 1, "dyllm_tp_reduce_rows": 1, "dyllm_tp_allreduce_rows": 2, "dyllm_tp_push_f32": 1,
+    "dyllm_tp_reduce_f32": 1, "dyllm_tp_allreduce_f32": 2,
 }
 launch_count = 0
 

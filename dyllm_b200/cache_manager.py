@@ -140,6 +140,14 @@ class CacheManager:
         self.seq_start_gpu[seq_id] = -1
         self.seq_len_gpu[seq_id] = 0
 
+    def clear(self) -> None:
+        """Forgets every sequence (the arena is kept for reuse)."""
+        self._seq_to_start.clear()
+        self._seq_to_len.clear()
+        self._rows = 0
+        self.seq_start_gpu.fill_(-1)
+        self.seq_len_gpu.zero_()
+
     def _allocate_new_seqs(self, new_ids: List[int], new_lengths: List[int]) -> None:
         total = sum(new_lengths)
         if total == 0:
@@ -166,7 +174,12 @@ class CacheManager:
             seq_ids_list = seq_ids.cpu().tolist()
         new_ids, new_lens = [], []
         for i, sid in enumerate(seq_ids_list):
-            if sid not in self._seq_to_start:
+            known = self._seq_to_len.get(sid)
+            if known is not None and known != ctx.context_lens_cpu[i]:
+                # the id is being reused for a sequence of another length: its old range cannot hold it
+                self.remove_seq(sid)
+                known = None
+            if known is None:
                 new_ids.append(sid)
                 new_lens.append(ctx.context_lens_cpu[i])
         if new_ids:

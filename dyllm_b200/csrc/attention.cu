@@ -78,12 +78,18 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
+// Phase tracer (development aid): compiled in only with -DDYLLM_ATTN_TRACE, which also exports
+// dyllm_attention_trace(buffer) to register a device buffer of 1024 * 16 uint64 time stamps.
+#ifdef DYLLM_ATTN_TRACE
 #define DYLLM_TRACE(slot)                                                  \
   do {                                                                     \
     if (p.trace && item >= static_cast<int>(p.trace_first) && item < static_cast<int>(p.trace_first) + 1024 && \
         threadIdx.x == 64)                                                 \
       p.trace[(item - p.trace_first) * 16 + (slot)] = global_ns();         \
   } while (0)
+#else
+#define DYLLM_TRACE(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -459,12 +465,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const bool tile_tma = it.tile_tma, fast = it.fast;
       float m = kNegBig, l = 0.f;
       DYLLM_TRACE(0);
+#ifdef DYLLM_ATTN_TRACE
       if (p.trace && item >= static_cast<int>(p.trace_first) && item < static_cast<int>(p.trace_first) + 1024 &&
           threadIdx.x == 64) {
         unsigned smid;
         asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
         p.trace[(item - p.trace_first) * 16 + 14] = smid;
       }
+#endif
 
       if (!EXACT && q0 + row < q_end) {
         // bring this thread's half of the C_old row (128 bytes) into L2 now; the epilogue reads it much later
@@ -1353,10 +1361,12 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
   return launch_attention<true>(tk, tk, tv, tk, tk, p, blocks, static_cast<cudaStream_t>(stream));
 }
 
+#ifdef DYLLM_ATTN_TRACE
 int dyllm_attention_trace(void* device_buffer) {
   g_attn_trace = static_cast<unsigned long long*>(device_buffer);
   return DYLLM_OK;
 }
+#endif
 
 int dyllm_attention_kernel_info(int dim, int64_t* info10) {
   DYLLM_REQUIRE(info10, DYLLM_ERR_INVALID_ARGUMENT, "attention_kernel_info: null output");

@@ -5,6 +5,8 @@
 // either through a small staging copy (rows gathered once into a compact buffer, then plain TMA boxes)
 // or directly by TMA gather4.  Launch shapes are chosen from a row-count hint; the live row count is
 // read on the device, so no host synchronisation is needed.
+#include <atomic>
+
 #include "gemm.cuh"
 
 namespace dyllm {
@@ -19,16 +21,16 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
   using Cfg = GemmCfg<BNH, SWIGLU, STAGES, MT>;
   auto kernel = gathered_gemm_kernel<BNH, SWIGLU, A_MODE, STAGES, MINB, MT>;
   // one flag per kernel instantiation and device: the opt-in shared-memory size is a per-function attribute
-  static bool smem_set[64] = {false};
+  static std::atomic<bool> smem_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
   dev = (dev < 0 || dev >= 64) ? 0 : dev;
-  if (!smem_set[dev]) {
+  if (!smem_set[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(Cfg::SMEM_BYTES)) != cudaSuccess)
       return set_error(DYLLM_ERR_CUDA, "cudaFuncSetAttribute(%u bytes of shared memory) failed: %s", Cfg::SMEM_BYTES,
                        cudaGetErrorString(cudaGetLastError()));
-    smem_set[dev] = true;
+    smem_set[dev].store(true, std::memory_order_release);
   }
   kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
   return check_launch("gathered_gemm");

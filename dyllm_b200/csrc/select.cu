@@ -4,6 +4,8 @@
 //   context_stats   reads 2 * width * 2 bytes per row, writes 12
 //   cosine_mask     reads 12 bytes per row, writes 1
 //   salient_select  reads 12 bytes per row once, writes 8 (+4, +8) bytes per selected row
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dyllm {
@@ -387,7 +389,8 @@ constexpr size_t kStaticSelectBytes =
 static __device__ __align__(256) unsigned char g_static_select_scratch[kStaticSelectBytes];
 
 namespace {
-void* g_static_select_ptr[64] = {nullptr};
+// written once per device; atomic so that host threads may make their first call at the same time
+std::atomic<void*> g_static_select_ptr[64];
 }
 
 // Returns the device address of the static scratch array on the current device (set up on first use).
@@ -395,15 +398,15 @@ int static_select_scratch(void** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
     return set_error(DYLLM_ERR_CUDA, "salient_select_static: no usable current device");
-  if (!g_static_select_ptr[dev]) {
-    void* ptr = nullptr;
+  void* ptr = g_static_select_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_select_scratch);
     if (err != cudaSuccess || !ptr)
       return set_error(DYLLM_ERR_CUDA, "salient_select_static: cudaGetSymbolAddress failed: %s",
                        cudaGetErrorString(err));
-    g_static_select_ptr[dev] = ptr;
+    g_static_select_ptr[dev].store(ptr, std::memory_order_release);  // every thread finds the same address
   }
-  *out = g_static_select_ptr[dev];
+  *out = ptr;
   return DYLLM_OK;
 }
 

@@ -43,11 +43,50 @@ def set_all_reduce_hook(hook) -> None:
 
 
 def all_reduce_sum(t: torch.Tensor) -> None:
-    """In-place SUM all-reduce over the tensor-parallel group."""
+    """In-place SUM all-reduce over the tensor-parallel group (NCCL)."""
     if _all_reduce_hook is not None:
         _all_reduce_hook(t)
     else:
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
+
+
+# The peer-memory exchange (tp_comm.TpComm) of this rank, when one has been set up: it carries the two small
+# all-reduces of a sparse layer whose size depends on the device-side salient count (statistics, FFN rows).
+_tp_comm = None
+
+
+def set_tp_comm(comm) -> None:
+    global _tp_comm
+    _tp_comm = comm
+
+
+def get_tp_comm():
+    return _tp_comm
+
+
+def all_reduce_stats(stats: torch.Tensor) -> None:
+    """SUM all-reduce of the ``[T_q, 3]`` fp32 statistics (12 bytes per token)."""
+    if _tp_comm is not None and stats.is_cuda:
+        _tp_comm.all_reduce_f32_(stats)
+    else:
+        all_reduce_sum(stats)
+
+
+def all_reduce_salient_rows(y: torch.Tensor, count_dev, cache_manager, seq_ids, rows_k) -> None:
+    """SUM all-reduce of the live rows of the compact ``[capacity, hidden]`` FFN output ``y`` and scatter of
+    the sums into the FFN-output cache (ref: linear.py:216-220 followed by mlp_cache_manage.py:24-40).  With
+    the peer-memory exchange only the live rows cross NVLink and the scatter is the reduce kernel's store;
+    without it the dead rows are cleared and the whole buffer goes through NCCL."""
+    ctx = get_context()
+    if _tp_comm is not None:
+        dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cache_manager.seq_start_gpu, seq_ids, count_dev)
+        _tp_comm.all_reduce_rows(y, count_dev, out=cache_manager.cache, out_row_map=dest)
+        return
+    if count_dev is not None:
+        dead = torch.arange(y.size(0), device=y.device).unsqueeze(1) >= count_dev
+        y.masked_fill_(dead, 0.0)          # rows past the live count were never written
+    all_reduce_sum(y)
+    cache_manager.scatter_update(seq_ids, rows_k, y, count_dev)
 
 
 def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.Tensor:
@@ -57,13 +96,8 @@ def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.
     statistics live on a GPU.
     """
     if _world_size() > 1:
-        all_reduce_sum(stats)
-    if stats.is_cuda and stats.dim() == 2:
-        return ops.cosine_mask(stats, threshold)
-    dot = stats[..., 0]
-    a = stats[..., 1].clamp_min(1e-8)
-    b = stats[..., 2].clamp_min(1e-8)
-    return dot * torch.rsqrt(a) * torch.rsqrt(b) < threshold
+        all_reduce_stats(stats)
+    return ops.cosine_mask(stats, threshold)      # raises unless the statistics are fp32 [rows, 3] on a GPU
 
 
 def divide(numerator: int, denominator: int) -> int:
@@ -87,6 +121,17 @@ class LinearBase(nn.Module):
             self.bias.weight_loader = self.weight_loader
         else:
             self.register_parameter("bias", None)
+
+    def full_shape(self, param: nn.Parameter) -> tuple:
+        """Shape of the unsharded checkpoint tensor behind ``param``."""
+        shape = list(param.shape)
+        if self.tp_dim is not None and param.dim() > self.tp_dim and not (param.dim() == 1 and self.tp_dim == 1):
+            shape[self.tp_dim] *= self.tp_size
+        return tuple(shape)
+
+    def load_full(self, param: nn.Parameter, full: torch.Tensor) -> None:
+        """Keeps this rank's shard of an unsharded tensor (what the loaders do shard by shard)."""
+        self.weight_loader(param, full)
 
 
 class ReplicatedLinear(LinearBase):
@@ -138,6 +183,12 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
         dst = param.data.narrow(self.tp_dim, offset, size)
         dst.copy_(loaded_weight.chunk(self.tp_size, self.tp_dim)[self.tp_rank])
 
+    def load_full(self, param: nn.Parameter, full: torch.Tensor) -> None:
+        pos = 0
+        for i, size in enumerate(self.output_sizes):
+            self.weight_loader(param, full.narrow(0, pos, size), i)
+            pos += size
+
 
 class KVParallelLinear(ColumnParallelLinear):
     def __init__(self, hidden_size: int, head_size: int, total_num_kv_heads: int, bias: bool = False):
@@ -151,6 +202,11 @@ class KVParallelLinear(ColumnParallelLinear):
         offset = 0 if loaded_shard_id == "k" else size
         dst = param.data.narrow(self.tp_dim, offset, size)
         dst.copy_(loaded_weight.chunk(self.tp_size, self.tp_dim)[self.tp_rank])
+
+    def load_full(self, param: nn.Parameter, full: torch.Tensor) -> None:
+        half = full.size(0) // 2
+        self.weight_loader(param, full.narrow(0, 0, half), "k")
+        self.weight_loader(param, full.narrow(0, half, half), "v")
 
 
 class RowParallelLinear(LinearBase):
@@ -181,25 +237,11 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(hidden_size))
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
-            if x.dim() == 2:
-                return ops.add_rms_norm(x.contiguous(), self.weight, self.eps, residual)
-            if x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == x.size(2):
-                # equal blocks of rows inside a cache: read in place, packed outputs
-                return ops.add_rms_norm(x, self.weight, self.eps, residual)
-        orig = x.dtype
-        xf = x.float()
-        if residual is not None:
-            xf = xf + residual.float()
-            residual = xf.to(orig)
-        var = xf.pow(2).mean(dim=-1, keepdim=True)
-        y = (xf * torch.rsqrt(var + self.eps)).to(orig) * self.weight
-        return y if residual is None else (y, residual)
-
-
-def apply_rotary_emb(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    x1, x2 = torch.chunk(x.float(), 2, dim=-1)
-    return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
+        # bf16 on a GPU only (ops.add_rms_norm raises otherwise).  A 3-D input is a view of equal blocks of
+        # rows inside a cache: it is read in place and the outputs are packed.
+        if x.dim() == 2:
+            x = x.contiguous()
+        return ops.add_rms_norm(x, self.weight, self.eps, residual)
 
 
 class RotaryEmbedding(nn.Module):
@@ -219,12 +261,8 @@ class RotaryEmbedding(nn.Module):
     def rotate(self, positions: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         if self._cos_sin_cache.device != x.device:
             self._cos_sin_cache = self._cos_sin_cache.to(x.device)
-        if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and x.size(2) == 128 and x.is_contiguous():
-            # in place on the freshly projected tensor
-            return ops.rope_neox_(x, positions, self._cos_sin_cache.view(-1, 128))
-        positions = torch.clamp(positions, 0, self._cos_sin_cache.size(0) - 1)
-        cos, sin = self._cos_sin_cache[positions].chunk(2, dim=-1)
-        return apply_rotary_emb(x, cos, sin)
+        # in place on the freshly projected [rows, heads, 128] bf16 tensor (the kernel wrapper raises otherwise)
+        return ops.rope_neox_(x.contiguous(), positions, self._cos_sin_cache.view(-1, x.size(-1)))
 
     def forward(self, positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor):
         return self.rotate(positions, query), self.rotate(positions, key)
@@ -296,17 +334,18 @@ class LLaDAMLP(nn.Module):
         cm = self.cache_update.cache_manager
         if cap:
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
+            rows = hint or cap
+            width, inter = hidden.size(1), self.down_proj.weight.size(1)
+            # algorithmic bytes: the three weight matrices (this rank's shards) once, the rows in and out
+            nbytes = 3.0 * width * inter * 2 + 2.0 * rows * width * 2
             if self.down_proj.tp_size > 1:
-                y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
-                                   num_rows=cap, num_rows_dev=n_dev, rows_hint=hint)
-                all_reduce_sum(y)
-                cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
+                with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
+                    y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
+                                       num_rows=cap, num_rows_dev=n_dev, rows_hint=hint)
+                with profiling.region("ffn_all_reduce", 0.0, 2.0 * rows * width * 2):
+                    all_reduce_salient_rows(y, n_dev, cm, md.running_seqs_tensor, rows_k)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
-                rows = hint or cap
-                width, inter = hidden.size(1), self.down_proj.weight.size(1)
-                # algorithmic bytes: the three weight matrices once, the rows in and out
-                nbytes = 3.0 * width * inter * 2 + 2.0 * rows * width * 2
                 with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
                     ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
                                    num_rows=cap, num_rows_dev=n_dev, rows_hint=hint, out=cm.cache, out_row_map=dest)
@@ -350,6 +389,30 @@ class LLaDAMoESparseBlock(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(self.num_local_experts, H, self.local_intermediate_size))
         self.cache_update = MLPcache(H)
 
+    def full_shape(self, param: nn.Parameter) -> tuple:
+        """Shape of the unsharded expert tensor behind ``gate_up_proj`` / ``down_proj``."""
+        if param is self.gate_up_proj:
+            return (self.num_experts, 2 * self.intermediate_size, self.hidden_size)
+        if param is self.down_proj:
+            return (self.num_experts, self.hidden_size, self.intermediate_size)
+        return tuple(param.shape)
+
+    def load_full(self, param: nn.Parameter, full: torch.Tensor) -> None:
+        """This rank's share of an unsharded expert tensor: a contiguous range of experts under expert
+        parallelism, else a slice of every expert's intermediate dimension (gate and up rows separately)
+        (ref: dyllm/model_executor/models/lladamoe.py:69-83)."""
+        if self.expert_parallel:
+            param.data.copy_(full.narrow(0, self.expert_start, self.num_local_experts))
+            return
+        world, rank, I, Il = _world_size(), _rank(), self.intermediate_size, self.local_intermediate_size
+        if param is self.gate_up_proj:
+            param.data[:, :Il].copy_(full[:, rank * Il:(rank + 1) * Il])
+            param.data[:, Il:].copy_(full[:, I + rank * Il: I + (rank + 1) * Il])
+        elif param is self.down_proj:
+            param.data.copy_(full[:, :, rank * Il:(rank + 1) * Il])
+        else:
+            param.data.copy_(full)
+
     def _experts(self, x, idx32, num_rows, n_dev, hint, out=None, out_row_map=None):
         w, ids = ops.moe_route(x, self.gate.weight, self.top_k, self.renormalize, idx32, num_rows, n_dev)
         return ops.moe_ffn(x, self.gate_up_proj, self.down_proj, w, ids, self.expert_start, idx32, num_rows, n_dev,
@@ -373,8 +436,7 @@ class LLaDAMoESparseBlock(nn.Module):
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
             if _world_size() > 1:
                 y = self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint)
-                all_reduce_sum(y)
-                cm.scatter_update(md.running_seqs_tensor, rows_k, y, n_dev)
+                all_reduce_salient_rows(y, n_dev, cm, md.running_seqs_tensor, rows_k)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
                 self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
@@ -408,6 +470,10 @@ def _dense_attention(q, k, v, ctx, scale):
 class Attention(nn.Module):
     def __init__(self, num_heads, head_dim, scale, num_kv_heads, threshold: float = 0.99):
         super().__init__()
+        if head_dim != 128 or abs(scale - head_dim ** -0.5) > 1e-6 * scale:
+            # the sm_100a attention kernels are built for head_dim 128 and the reference kernel's own scale
+            # (1/sqrt(head_dim), dyllm/csrc/attention/attention_ops_kernels_sm80.cu:166)
+            raise ValueError(f"Attention supports head_dim 128 with scale head_dim**-0.5; got {head_dim}, {scale}")
         self.num_heads = num_heads
         self.head_dim = head_dim
         self.scale = scale
@@ -495,7 +561,7 @@ class Attention(nn.Module):
         # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch; the new
         # lists stay on the device together with their length
         if _world_size() > 1:
-            all_reduce_sum(stats)
+            all_reduce_stats(stats)
         with profiling.region("salient_select", 0.0, 12.0 * ctx.total_seqlen):
             sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,
                                      ctx.cu_promptlens if is_q_pruned else None)

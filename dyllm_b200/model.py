@@ -159,13 +159,24 @@ class LLaDAForDLM(nn.Module):
 
 
 def init_weights_(module: nn.Module, seed: int = 0, std: float = 0.02) -> None:
-    """Seeded N(0, std) for every matrix, ones for the norm weights (random-init stand-in for a checkpoint)."""
+    """Seeded random-init stand-in for a checkpoint: N(0, std) for every matrix and bias of the UNSHARDED
+    model, drawn in parameter order, ones for the norm weights.  Under tensor / expert parallelism every rank
+    draws the same unsharded tensors and keeps its shard through the layers' loaders, so the sharded model
+    computes the same function as the single-GPU one (and one rank draws exactly the single-GPU values)."""
     gens: dict = {}
+    owner = {id(p): m for m in module.modules() for p in m.parameters(recurse=False)}
     for name, p in module.named_parameters():
-        if p.dim() >= 2:
-            g = gens.get(p.device)
-            if g is None:
-                g = gens[p.device] = torch.Generator(device=p.device).manual_seed(seed)
+        if p.dim() < 2 and not name.endswith("bias"):
+            p.data.fill_(1.0)
+            continue
+        g = gens.get(p.device)
+        if g is None:
+            g = gens[p.device] = torch.Generator(device=p.device).manual_seed(seed)
+        m = owner[id(p)]
+        full_shape = m.full_shape(p) if hasattr(m, "full_shape") else tuple(p.shape)
+        if full_shape == tuple(p.shape):
             p.data.normal_(0.0, std, generator=g)
         else:
-            p.data.fill_(1.0)
+            full = torch.empty(full_shape, dtype=p.dtype, device=p.device).normal_(0.0, std, generator=g)
+            m.load_full(p, full)
+            del full

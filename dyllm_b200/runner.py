@@ -195,14 +195,17 @@ class StepRunner:
         self.device = next(model.parameters()).device
         self.salient_counts: list[int] = []
         self.use_graphs = use_graphs
-        # A captured step with the NCCL all-reduces inside did not complete on two GPUs (the run stopped
-        # making progress, with the default and with the thread-local capture error mode).  With several
-        # ranks a step is therefore captured as a chain of graphs with the all-reduces issued eagerly between
-        # them (_SegmentedCapture); graphs_with_tp=False (or DYLLM_GRAPHS_WITH_TP=0) launches every kernel
-        # eagerly instead.
+        # With several ranks a step is captured whole, NCCL all-reduces and peer-memory exchanges included
+        # (DYLLM_TP_GRAPHS=whole, the default).  NCCL keeps a communicator alive for as long as a graph that
+        # captured one of its collectives exists, and destroying the process group waits for that: call
+        # release_graphs() before dist.destroy_process_group().  DYLLM_TP_GRAPHS=segmented captures a chain of
+        # graphs cut at every NCCL all-reduce (issued eagerly between them); graphs_with_tp=False or
+        # DYLLM_TP_GRAPHS=off launches every kernel eagerly.
+        mode = os.environ.get("DYLLM_TP_GRAPHS", "whole")
         if graphs_with_tp is None:
-            graphs_with_tp = os.environ.get("DYLLM_GRAPHS_WITH_TP", "1") != "0"
+            graphs_with_tp = mode != "off"
         self.graphs_with_tp = graphs_with_tp
+        self.tp_graph_mode = mode if mode in ("whole", "segmented") else "whole"
         # The reference projects every query row onto the vocabulary and then indexes the rows of the
         # current block (model_runner.py:377, sampler.py:244-315); with full_logits False only the rows the
         # sampler reads are projected, which yields the same tokens.
@@ -211,6 +214,38 @@ class StepRunner:
         self._graphs: dict = {}
         self._warm: set = set()
         self._graph_pool = None
+        self._geometry = None
+
+    def _set_geometry(self, key) -> None:
+        """Called at the start of every generation with (batch, sequence lengths).  Sequence ids are reused
+        from one generation to the next, so when the geometry changes the activation caches forget the
+        previous batch (its ranges have other lengths) and every captured graph is dropped: a graph holds
+        the addresses and row offsets of the geometry it was captured for, and the cache arenas may move
+        when they grow."""
+        if key == self._geometry:
+            return
+        if self._geometry is not None:
+            from .cache_manager import CacheManager
+
+            torch.cuda.synchronize(self.device)
+            self.release_graphs()
+            self._states.clear()
+            for module in self.model.modules():
+                for value in vars(module).values():
+                    if isinstance(value, CacheManager):
+                        value.clear()
+        self._geometry = key
+
+    def release_graphs(self) -> None:
+        """Destroys every captured graph (needed before the process group is destroyed when the graphs
+        hold collectives, and whenever the buffers they address go away)."""
+        import gc
+
+        self._graphs.clear()
+        self._warm.clear()
+        gc.collect()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     def new_batch(self, prompts: List[List[int]], max_new_tokens: int, first_seq_id: int = 0) -> List[Sequence]:
         seqs = []
@@ -241,7 +276,12 @@ class StepRunner:
         gen = max_new_tokens
         steps_per_block = max(1, self.steps * self.block_length // gen)
         num_transfer = max(1, self.block_length // steps_per_block)
-        if device_state and len(lens) == 1 and self.steps * num_transfer == gen and gen % self.block_length == 0:
+        self._set_geometry((tuple(len(p) for p in prompts), gen))
+        # the device-resident loop unmasks exactly num_transfer tokens per step: every block must be filled by
+        # its own steps_per_block steps, and the blocks' steps must add up to the step count
+        exact = (gen % self.block_length == 0 and steps_per_block * num_transfer == self.block_length
+                 and steps_per_block * (gen // self.block_length) == self.steps)
+        if device_state and len(lens) == 1 and exact:
             return self._generate_device(prompts, gen, steps_per_block, num_transfer)
         seqs = self.new_batch(prompts, max_new_tokens)
         for _ in range(self.steps):
@@ -344,12 +384,14 @@ class StepRunner:
             before = _lib.launch_count
             st.fixed_hint = GRAPH_ROWS_HINT
             try:
-                if _multi_rank():
+                if _multi_rank() and self.tp_graph_mode == "segmented":
                     graph = _SegmentedCapture(self._graph_pool)
                     graph.capture(lambda: self._device_step(st, kind))
                 else:
                     graph = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(graph, pool=self._graph_pool):
+                    # thread-local: NCCL's watchdog thread may query events while this thread captures
+                    with torch.cuda.graph(graph, pool=self._graph_pool,
+                                          capture_error_mode="thread_local" if _multi_rank() else "global"):
                         self._device_step(st, kind)
             finally:
                 st.fixed_hint = 0
@@ -392,10 +434,7 @@ class StepRunner:
     def _confidence(logits: torch.Tensor, B: int, blk_len: int):
         """Probability and id of the most likely token of every candidate row, as ``[B, blk_len]``
         (ref: sampler.py:286-288, softmax then max)."""
-        if logits.is_cuda and logits.dtype == torch.bfloat16:
-            conf, tok = ops.row_confidence(logits.contiguous())
-        else:
-            conf, tok = torch.softmax(logits.float(), dim=-1).max(dim=-1)
+        conf, tok = ops.row_confidence(logits.contiguous())     # bf16 logits on a GPU; raises otherwise
         return conf.view(B, blk_len), tok.view(B, blk_len)
 
     def _unmask(self, seqs: List[Sequence], hidden: torch.Tensor, ctx) -> int:

@@ -252,13 +252,6 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
                                  int total_k, int num_heads, int num_kv_heads, int head_dim,
                                  const int32_t* cu_salientlens, const int32_t* idx_salient_row_q, void* stream);
 
-/* Tracing aid: while a device buffer of 1024 * 16 uint64 is registered, 1024 consecutive CTAs of
- * dyllm_attention_sparse_varlen (CTAs 512.. when the grid has more than 1536, else the first ones) store
- * %globaltimer (ns) at phase boundaries (slot 0 start, 7 first logits ready, 1 end of pass A, 2 salient
- * rows gathered, 3 their logits ready, 4 P written, 5 P dV done, 8 previous context tile in shared
- * memory, 9 tile updated, 10 stores issued, 6 end, 14 the SM id).  Pass null to switch tracing off (the default). */
-int dyllm_attention_trace(void* device_buffer);
-
 /* Launch resources of the main attention kernel: [registers, local bytes, static shared bytes,
  * dynamic shared bytes, threads per block, resident blocks per SM, query rows per block, keys per
  * tile, head-dim split, ok].  ref: dyllm/csrc/attention/attention.cpp:184-208. */
@@ -343,6 +336,61 @@ int dyllm_row_confidence(const void* logits, int rows, int vocab, int64_t pitch,
  * ref: dyllm/model_executor/layers/rotary_embedding.py:8-54. */
 int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, const float* cos_sin, int rows,
                     const int32_t* num_rows_dev, int heads, int head_dim, int max_pos, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Tensor-parallel SUM exchange of the small per-layer tensors over peer memory (NVLink)
+ *
+ * One communicator per rank (process) and GPU.  Every rank owns a region of
+ * 1024 + 2 * world * slot_bytes bytes; all regions are mapped into every process (CUDA IPC), or handed
+ * over as plain pointers when several ranks are emulated inside one process.  An exchange is a `push`
+ * (each rank stores its partial tensor into its slot of every rank's region and raises a flag there; only
+ * stores cross NVLink) followed by a `reduce` (each rank waits for the flags of its own region and adds
+ * the slots in rank order in fp32, so that all ranks hold bit-identical results).  Both are ordinary
+ * kernels on the caller's stream: they read the live row count on the device and can be captured into a
+ * CUDA graph.  Every rank must issue the same sequence of exchanges.  A flag wait gives up after a time
+ * limit (default 2 s): the kernel then skips its sums, dyllm_device_status() reports 0x7E00 + the rank
+ * whose flag was missing, and the device stays usable.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* Creates the communicator of `rank` (0 <= rank < world <= 8) on the current device and allocates its
+ * region (set-up time; this is the one call of this group that allocates).  slot_bytes (multiple of 256)
+ * bounds the bytes one rank contributes to one exchange. */
+int dyllm_tp_comm_create(int rank, int world, size_t slot_bytes, void** comm_out);
+/* Size and device address of the local region. */
+size_t dyllm_tp_comm_region_bytes(void* comm);
+void* dyllm_tp_comm_region(void* comm);
+/* 64-byte CUDA IPC handle of the local region, to be sent to the other ranks (any transport). */
+int dyllm_tp_comm_ipc_handle(void* comm, void* handle64);
+/* Maps the other ranks' regions from their handles (world * 64 bytes, indexed by rank).  All ranks must
+ * synchronise with each other after this call and before their first exchange. */
+int dyllm_tp_comm_open_ipc(void* comm, const void* handles);
+/* The same for ranks that live in one process: regions[r] = dyllm_tp_comm_region(comm of rank r). */
+int dyllm_tp_comm_open_local(void* comm, void* const* regions);
+/* Time limit of a flag wait. */
+int dyllm_tp_comm_set_wait_ms(void* comm, int milliseconds);
+/* Synchronises the device, unmaps the peers' regions and frees the local one. */
+int dyllm_tp_comm_destroy(void* comm);
+
+/* SUM all-reduce of the live rows [row_offset, min(row_offset + max_rows, *count_dev)) of a compact bf16
+ * [rows, width] tensor whose first row is row `row_offset` (count_dev null = max_rows rows), written to
+ * out[map[row_offset + m]] (out_row_map null = row_offset + m; negative entries drop the row; ldo = row
+ * pitch of out in elements).  width % 8 == 0, max_rows * width * 2 <= slot_bytes.  The count must be the
+ * same on every rank.  dyllm_tp_allreduce_rows = dyllm_tp_push_rows + dyllm_tp_reduce_rows.
+ * ref: dyllm/model_executor/layers/linear.py:216-220 (all_reduce after the row-parallel down projection),
+ *      dyllm/model_executor/models/lladamoe.py:103-104,141 (expert outputs),
+ *      dyllm/model_executor/layers/mlp_cache_manage.py:24-40 (scatter into the FFN-output cache). */
+int dyllm_tp_push_rows(void* comm, const void* src, int width, int max_rows, const int32_t* count_dev,
+                       int row_offset, void* stream);
+int dyllm_tp_reduce_rows(void* comm, int width, int max_rows, const int32_t* count_dev, int row_offset, void* out,
+                         int64_t ldo, const int32_t* out_row_map, void* stream);
+int dyllm_tp_allreduce_rows(void* comm, const void* src, int width, int max_rows, const int32_t* count_dev,
+                            int row_offset, void* out, int64_t ldo, const int32_t* out_row_map, void* stream);
+
+/* In-place SUM all-reduce of n fp32 values (the [rows, 3] cosine statistics, 12 bytes per token).
+ * ref: dyllm/distributed/parallel_state.py:60-61. */
+int dyllm_tp_push_f32(void* comm, const float* src, int n, void* stream);
+int dyllm_tp_reduce_f32(void* comm, float* out, int n, void* stream);
+int dyllm_tp_allreduce_f32(void* comm, float* inout, int n, void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,7 +23,8 @@ def _worker(rank, world, port, out_queue):
     c_old, c_new = orc.make_context_pair(300, 512, 0.99, 0.15, seed=4)
     shard = 512 // world
     stats = orc.context_stats(c_old[:, rank * shard:(rank + 1) * shard], c_new[:, rank * shard:(rank + 1) * shard])
-    mask = layers.tensor_parallel_cosine_mask(stats, 0.99)     # all-reduces in place
+    layers.all_reduce_sum(stats)                               # the 12-byte-per-token exchange, in place
+    mask = orc.cosine_mask(stats, 0.99)                        # CPU ranks: the decision comes from the checker
     full = orc.cosine_mask(orc.context_stats(c_old, c_new), 0.99)
     ok_mask = bool(torch.equal(mask, full))
 
@@ -50,7 +51,35 @@ def _worker(rank, world, port, out_queue):
     with torch.no_grad():
         y = row(x[:, rank * 16:(rank + 1) * 16])
     ok_sum = torch.allclose(y, x @ w.t(), atol=1e-5)
-    out_queue.put((rank, ok_mask, bool(ok_col), bool(ok_merged), bool(ok_kv), bool(ok_row), bool(ok_sum)))
+    # seeded random init: every rank's shards are slices of the tensors the single-rank model draws
+    from dyllm_b200 import cache_manager, model
+    cache_manager.CacheManager.__init__.__defaults__ = (64, torch.float32, torch.device("cpu"))
+    cfg = model.LLaDAShape(hidden_size=256, num_attention_heads=4, n_kv_heads=2, mlp_hidden_size=512,
+                           num_hidden_layers=1, vocab_size=512, max_sequence_length=64)
+    real = (layers._world_size, layers._rank)
+    layers._world_size, layers._rank = (lambda: 1), (lambda: 0)
+    model._world_size = layers._world_size
+    try:
+        single = model.LLaDAForDLM(cfg, 0.99)
+    finally:
+        layers._world_size, layers._rank = real
+        model._world_size = real[0]
+    model.init_weights_(single, seed=3)
+    sharded = model.LLaDAForDLM(cfg, 0.99)
+    model.init_weights_(sharded, seed=3)
+    a1, a2 = single.model.layers[0].self_attn, sharded.model.layers[0].self_attn
+    m1, m2 = single.model.layers[0].mlp, sharded.model.layers[0].mlp
+    sl = lambda t, n, d=0: t.narrow(d, rank * n, n)
+    ok_init = (torch.equal(a2.q_proj.weight, sl(a1.q_proj.weight, 256))
+               and torch.equal(a2.kv_proj.weight[:128], sl(a1.kv_proj.weight[:256], 128))
+               and torch.equal(a2.kv_proj.weight[128:], sl(a1.kv_proj.weight[256:], 128))
+               and torch.equal(a2.o_proj.weight, sl(a1.o_proj.weight, 256, 1))
+               and torch.equal(m2.gate_up_proj.weight[:256], sl(m1.gate_up_proj.weight[:512], 256))
+               and torch.equal(m2.gate_up_proj.weight[256:], sl(m1.gate_up_proj.weight[512:], 256))
+               and torch.equal(m2.down_proj.weight, sl(m1.down_proj.weight, 256, 1))
+               and torch.equal(sharded.lm_head.weight, single.lm_head.weight)
+               and torch.equal(sharded.model.embed_tokens.weight, single.model.embed_tokens.weight))
+    out_queue.put((rank, ok_mask, bool(ok_col), bool(ok_merged), bool(ok_kv), bool(ok_row), bool(ok_sum), bool(ok_init)))
     dist.destroy_process_group()
 
 

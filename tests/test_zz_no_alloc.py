@@ -40,13 +40,22 @@ def _case(rows_per_seq, batch, seed, dev):
 
 def test_no_alloc_selection_matches_workspace_selection_twice(cuda_device):
     from dyllm_b200 import _lib, ops
+    from oracle import dyllm_oracle as orc
 
-    # two calls in a row with different sizes: the second must not see the first one's descriptors
-    for rows_per_seq, batch, seed in ((4096, 16, 1), (777, 5, 2)):
+    # calls in a row with different sizes: a later one must not see an earlier one's descriptors.  The
+    # first case lies above 64 Ki rows, where the selection switches to its wide-tile instance.
+    for rows_per_seq, batch, seed in ((9000, 16, 3), (4096, 16, 1), (777, 5, 2)):
         stats, cu_q, cu_p = _case(rows_per_seq, batch, seed, cuda_device)
         want = ops.salient_select(stats, 0.99, cu_q, cu_p, want_mask=True)
         got = _select_static(stats, 0.99, cu_q, cu_p)
         n = int(want.count.item())
+        # ... and against the CPU restatement of the reference directly
+        ref = orc.salient_select(stats.cpu(), 0.99, cu_q.cpu(), cu_p.cpu())
+        assert ref["count"] == int(got["count"].item())
+        assert torch.equal(got["idx"][:n].cpu(), ref["idx"])
+        assert torch.equal(got["idx_k"][:n].cpu(), ref["idx_k"])
+        assert torch.equal(got["cu_sal"].cpu(), ref["cu_salientlens"])
+        assert torch.equal(got["mask"].cpu(), ref["mask"])
         assert n > 0 and int(got["count"].item()) == n
         assert torch.equal(got["idx"][:n], want.idx[:n])
         assert torch.equal(got["idx32"][:n], want.idx32[:n])
