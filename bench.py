@@ -1,13 +1,18 @@
 #!/usr/bin/env python
-"""Throughput of the saliency path on the LLaDA-8B configuration: generated tokens/s at batch 16,
-prompt 256, generation length 256, block 32, 256 denoising steps, threshold 0.99, random-init bf16
-weights and uniform-random prompt ids (synthetic stand-ins for a checkpoint and a dataset).
+"""Throughput of the saliency path: generated tokens/s of complete generations (dense warm-up steps, then
+sparse steps with the reference's period-4 full-sequence refresh), random-init bf16 weights and
+uniform-random prompt ids (synthetic stand-ins for a checkpoint and a dataset).
 
-    python bench.py --gpus N --steps K --warmup W            this library (one process per GPU, TP over NCCL)
+    python bench.py --gpus N --steps K --warmup W            this library (one process per GPU, TP over NVLink)
     python bench.py --impl reference ...                      CPU restatement of the reference path on the host cores
+    python bench.py --config {1,3,4,5} [--tau T | --dense] [--ep]   the other named workloads
 
-One "step" is one complete generation of the batch (256 denoising steps: 8 dense, 248 sparse with the
-reference's period-4 full-sequence refresh), so tokens/s = steps * batch * gen_len / time.
+--config 1 (default): LLaDA-8B shape, batch 16, prompt 256, gen 256, block 32, 256 denoising steps, tau 0.99.
+--config 3: Dream-7B shape (28 query / 4 KV heads, biased q/k/v), batch 32; tensor parallel 2 or 4.
+--config 4: LLaDA-MoE-7B-A1B shape (64 experts, top-8), batch 32; --ep = whole experts per rank.
+--config 5: LLaDA-8B shape, batch 64, prompt 512, gen 512, block 64; sweep --tau 0.95 / 0.99 / 0.995 and --dense.
+
+One "step" is one complete generation of the batch, so tokens/s = steps * batch * gen_len / time.
 Prints one JSON line (rank 0).
 """
 
@@ -16,6 +21,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import tempfile
@@ -27,15 +33,36 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-BATCH, PROMPT, GEN, BLOCK, DSTEPS, TAU, FULL_STEPS, REFRESH = 16, 256, 256, 32, 256, 0.99, 8, 4
-METRIC = "generated tokens/s (LLaDA-8B bf16, b=16, gen=256, tau=0.99)"
+REFRESH = 4
+CONFIGS = {
+    1: dict(family="llada", batch=16, prompt=256, gen=256, block=32, steps=256, full=8, tau=0.99,
+            label="configs[1]: LLaDA-8B shape, 32 layers"),
+    3: dict(family="dream", batch=32, prompt=256, gen=256, block=32, steps=256, full=8, tau=0.99,
+            label="configs[2]: Dream-7B shape, 28 layers, 28 query / 4 KV heads, qkv bias"),
+    4: dict(family="lladamoe", batch=32, prompt=256, gen=256, block=32, steps=256, full=8, tau=0.99,
+            label="configs[3]: LLaDA-MoE-7B-A1B shape, 16 layers, 64 experts top-8"),
+    5: dict(family="llada", batch=64, prompt=512, gen=512, block=64, steps=512, full=8, tau=0.99,
+            label="configs[4]: LLaDA-8B shape, 32 layers, at scale"),
+}
+MODEL_NAMES = {"llada": "LLaDA-8B", "dream": "Dream-7B", "lladamoe": "LLaDA-MoE-7B-A1B"}
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of this library's kernels at this
-# workload's shapes, from the ncu captures summarised under profiles/: the gathered FFN at 48 salient
-# rows (four launches), the exact attention of the salient rows, and the approximate attention, whose
-# capture is a launch with full-sequence queries (252.2 MB) scaled by the algorithmic bytes to the mix of
-# one full-sequence and three response-only launches that the bench averages over.
-NCU_TRAFFIC_BYTES = {"delta_attention": 181.6e6, "swiglu_ffn": 320.0e6, "salient_attention": 138.4e6}
+
+def metric_name(cfg, tau):
+    mode = "dense" if tau is None else f"tau={tau:g}"
+    return f"generated tokens/s ({MODEL_NAMES[cfg['family']]} bf16, b={cfg['batch']}, gen={cfg['gen']}, {mode})"
+
+
+def ncu_traffic_bytes():
+    """DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of this library's kernels at the
+    default workload's shapes, read from the table of profiles/ncu_dram_traffic.md (one ncu capture each)."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "ncu_dram_traffic.md")
+    if os.path.exists(path):
+        for line in open(path):
+            m = re.match(r"\|\s*`?(\w+)`?\s*\|\s*([0-9.]+)\s*MB\s*\|", line)
+            if m:
+                out[m.group(1)] = float(m.group(2)) * 1e6
+    return out
 
 
 def measured_peaks():
@@ -100,109 +127,214 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------------
-# CPU restatement of one layer-step of the path (checker code, timed as the reported CPU baseline)
+# CPU restatement of the path (checker code, timed as the reported CPU baseline)
 # ----------------------------------------------------------------------------------------------
-def cpu_layer_step_seconds(n_seqs: int, repeats: int, threads: int):
-    """Times the oracle's restatement of one sparse layer-step (RMSNorm, q/kv/o projections, rotary
-    embedding, delta-V, salient-row attention, approximate attention, statistics, mask, compaction, gathered
-    SwiGLU FFN, cache scatter) at the LLaDA-8B layer shape for `n_seqs` sequences of 512 tokens with ~10 %
-    salient response rows.  Returns seconds per layer-step for those sequences."""
+def layer_shape(cfg):
+    """(hidden, heads, kv heads, FFN intermediate, layers, experts, top-k) of a workload's model."""
+    if cfg["family"] == "dream":
+        return 3584, 28, 4, 18944, 28, 0, 0
+    if cfg["family"] == "lladamoe":
+        return 2048, 16, 16, 1024, 16, 64, 8
+    return 4096, 32, 32, 12288, 32, 0, 0
+
+
+def cpu_layer_step_seconds(cfg, kind: str, n_seqs: int, sal_per_seq: int, repeats: int, threads: int):
+    """Times the oracle's restatement of ONE layer-step of the path for `n_seqs` sequences on the host cores and
+    returns (seconds per layer-step, seconds per stage).  `kind`: "dense" (all rows through attention and FFN),
+    "sparse" (full-sequence queries) or "pruned" (response-only queries); the sparse kinds process
+    `sal_per_seq` salient response rows per sequence.  Stages: norms + q/o projections + rotary embedding
+    ("rowwise"), K/V projection + cache update ("kv"), exact attention of the salient rows ("salient_attention"),
+    approximate attention + statistics ("delta_attention"), mask + compaction ("select"), FFN ("ffn")."""
     from oracle import dyllm_oracle as orc
 
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(0)
-    hid, H, D, I, L = 4096, 32, 128, 12288, PROMPT + GEN
-    T = n_seqs * L
-    w = {k: torch.randn(s, generator=g) * 0.02 for k, s in
-         dict(q=(H * D, hid), kv=(2 * H * D, hid), o=(hid, H * D), gu=(2 * I, hid), down=(hid, I)).items()}
-    x = torch.randn(T, hid, generator=g)
-    res = torch.randn(T, hid, generator=g)
-    k_cache = torch.randn(T, H, D, generator=g)
-    v_cache = torch.randn(T, H, D, generator=g)
-    c_cache = torch.randn(T, H, D, generator=g)
-    ffn_cache = torch.randn(T, hid, generator=g)
-    cu = torch.arange(n_seqs + 1, dtype=torch.int32) * L
-    idx = torch.cat([torch.sort(torch.randperm(GEN, generator=g)[:26]).values + b * L + PROMPT for b in range(n_seqs)])
-    cu_sal = torch.arange(n_seqs + 1, dtype=torch.int32) * 26
-    pos = torch.arange(L).repeat(n_seqs)
+    hid, H, Hkv, I, _, E, topk = layer_shape(cfg)
+    D, P, R = 128, cfg["prompt"], cfg["gen"]
+    L = P + R
+    lq = R if kind == "pruned" else L
+    Tk, Tq = n_seqs * L, n_seqs * lq
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.02
+    w = dict(q=rnd(H * D, hid), kv=rnd(2 * Hkv * D, hid), o=rnd(hid, H * D))
+    if E:
+        w.update(router=rnd(E, hid), w1=rnd(E, 2 * I, hid), w2=rnd(E, hid, I))
+    else:
+        w.update(gu=rnd(2 * I, hid), down=rnd(hid, I))
+    x = torch.randn(Tq, hid, generator=g)
+    res = torch.randn(Tq, hid, generator=g)
+    k_cache = torch.randn(Tk, Hkv, D, generator=g)
+    v_cache = torch.randn(Tk, Hkv, D, generator=g)
+    c_cache = torch.randn(Tq, H, D, generator=g)
+    ffn_cache = torch.randn(Tq, hid, generator=g)
+    ar = torch.arange(n_seqs + 1, dtype=torch.int32)
+    cu_q, cu_k, cu_sal = ar * lq, ar * L, ar * sal_per_seq
+    sal_off = [torch.sort(torch.randperm(R, generator=g)[:sal_per_seq]).values for _ in range(n_seqs)]
+    idx_k = torch.cat([o + b * L + P for b, o in enumerate(sal_off)])
+    idx_q = torch.cat([o + b * lq + (0 if kind == "pruned" else P) for b, o in enumerate(sal_off)])
+    pos_q = (torch.arange(P, L) if kind == "pruned" else torch.arange(L)).repeat(n_seqs)
+    pos_k = torch.arange(L).repeat(n_seqs)
     ones = torch.ones(hid)
+    stages: dict = {}
+
+    def timed(name, fn):
+        t0 = time.perf_counter()
+        out = fn()
+        stages[name] = stages.get(name, 0.0) + time.perf_counter() - t0
+        return out
+
+    def ffn(rows_x):
+        if E:
+            tw, ti = orc.moe_gate(rows_x, w["router"], topk)
+            return orc.naive_experts(rows_x, w["w1"], w["w2"], tw, ti, round_bf16=False)
+        return orc.swiglu_ffn(rows_x, w["gu"], w["down"], round_bf16=False)
 
     def one_step():
-        h, r = orc.rms_norm(x, ones, 1e-5, residual=res)
-        q = orc.rope(pos, (h @ w["q"].t()).view(T, H, D), D, 500000.0, 4096)
-        kv = h[idx] @ w["kv"].t()
-        k_new = orc.rope(pos[idx], kv[:, : H * D].reshape(-1, H, D), D, 500000.0, 4096)
-        v_new = kv[:, H * D:].reshape(-1, H, D)
-        k_cache[idx] = k_new
-        dv = torch.zeros_like(v_cache)
-        dv[idx] = v_new - v_cache[idx]
-        v_cache[idx] = v_new
-        o_sal = orc.exact_attention_varlen(q[idx], k_cache, v_cache, cu_sal, cu)
-        new_c, stats, _ = orc.attention_sparse_varlen(q, k_cache, dv, c_cache, o_sal, cu, cu, cu_sal, idx, TAU,
-                                                      round_p_bf16=False)
-        sel = orc.salient_select(stats, TAU, cu)
+        h, r = timed("rowwise", lambda: orc.rms_norm(x, ones, 1e-5, residual=res))
+        q = timed("rowwise", lambda: orc.rope(pos_q, (h @ w["q"].t()).view(Tq, H, D), D, 500000.0, 4096))
+        if kind == "dense":
+            def kv_all():
+                kv = h @ w["kv"].t()
+                k_cache.copy_(orc.rope(pos_k, kv[:, : Hkv * D].reshape(-1, Hkv, D), D, 500000.0, 4096))
+                v_cache.copy_(kv[:, Hkv * D:].reshape(-1, Hkv, D))
+            timed("kv", kv_all)
+            new_c = timed("salient_attention", lambda: orc.exact_attention_varlen(q, k_cache, v_cache, cu_q, cu_k))
+            c_cache.copy_(new_c)
+            a = timed("rowwise", lambda: new_c.flatten(1) @ w["o"].t())
+            h2, _ = timed("rowwise", lambda: orc.rms_norm(a, ones, 1e-5, residual=r))
+            ffn_cache.copy_(timed("ffn", lambda: ffn(h2)))
+            return Tq
+
+        def kv_salient():
+            kv = h[idx_q] @ w["kv"].t()
+            k_cache[idx_k] = orc.rope(pos_k[idx_k], kv[:, : Hkv * D].reshape(-1, Hkv, D), D, 500000.0, 4096)
+            dv = torch.zeros_like(v_cache)
+            dv[idx_k] = orc.delta_v_update(kv[:, Hkv * D:].reshape(-1, Hkv, D), v_cache, idx_k)
+            return dv
+        dv = timed("kv", kv_salient)
+        o_sal = timed("salient_attention", lambda: orc.exact_attention_varlen(q[idx_q], k_cache, v_cache, cu_sal, cu_k))
+        new_c, stats, _ = timed("delta_attention", lambda: orc.attention_sparse_varlen(
+            q, k_cache, dv, c_cache, o_sal, cu_q, cu_k, cu_sal, idx_q, cfg["tau"], round_p_bf16=False))
+        sel = timed("select", lambda: orc.salient_select(stats, cfg["tau"], cu_q))
         c_cache.copy_(new_c.float())
-        a = new_c.float().flatten(1) @ w["o"].t()
-        h2, _ = orc.rms_norm(a, ones, 1e-5, residual=r)
-        rows = sel["idx"] if sel["count"] else idx
-        ffn_cache[rows] = orc.swiglu_ffn(h2[rows], w["gu"], w["down"], round_bf16=False)
+        a = timed("rowwise", lambda: new_c.float().flatten(1) @ w["o"].t())
+        h2, _ = timed("rowwise", lambda: orc.rms_norm(a, ones, 1e-5, residual=r))
+        rows = sel["idx"] if sel["count"] else idx_q
+        ffn_cache[rows] = timed("ffn", lambda: ffn(h2[rows]))
         return int(rows.numel())
 
     one_step()  # warm-up
+    stages.clear()
     t0 = time.perf_counter()
     for _ in range(repeats):
         one_step()
-    return (time.perf_counter() - t0) / repeats
+    total = (time.perf_counter() - t0) / repeats
+    return total, {k: v / repeats for k, v in stages.items()}
 
 
-def cpu_tokens_per_s(sec_per_layer_step: float, n_seqs: int, layers: int = 32) -> float:
-    # whole job = DSTEPS denoising steps x layers x (BATCH / n_seqs) samples
-    total = sec_per_layer_step * (BATCH / n_seqs) * layers * DSTEPS
-    return BATCH * GEN / total
+def step_mix(cfg, dense_only=False):
+    """(dense, full-sequence sparse, response-only sparse) denoising steps of one generation, as the
+    reference schedules them (dyllm/engine/scheduler.py:29-75, dyllm/engine/model_runner.py:211-222)."""
+    if dense_only:
+        return cfg["steps"], 0, 0
+    dense = min(cfg["full"], cfg["steps"])
+    sparse = sum(1 for p in range(dense + 1, cfg["steps"] + 1) if not (p > REFRESH and p % REFRESH != 0))
+    return dense, sparse, cfg["steps"] - dense - sparse
 
 
-def run_reference_arm(args):
+def cpu_baseline(cfg, tau, threads: int, repeats: int, n_seqs: int = 1, sal_per_seq: int = 3):
+    """CPU tokens/s of the whole job, extrapolated from layer-steps of each kind timed on `n_seqs` sequences."""
+    layers = layer_shape(cfg)[4]
+    mix = dict(zip(("dense", "sparse", "pruned"), step_mix(cfg, tau is None)))
+    per_kind, stages = {}, {}
+    for kind, n in mix.items():
+        if n:
+            per_kind[kind], st = cpu_layer_step_seconds(cfg, kind, n_seqs, sal_per_seq, repeats if kind != "dense" else 1, threads)
+            stages[kind] = {k: round(v, 4) for k, v in st.items()}
+    total = sum(per_kind[k] * mix[k] for k in per_kind) * layers * (cfg["batch"] / n_seqs)
+    value = cfg["batch"] * cfg["gen"] / total
+    sample = (f"one layer-step of each kind of the restated path (fp32 torch on {threads} host threads) for {n_seqs} of "
+              f"{cfg['batch']} sequences with {sal_per_seq} salient rows per sequence (the GPU arm's measured mean): "
+              + ", ".join(f"{k} {per_kind[k]:.2f} s x{mix[k]} steps" for k in per_kind)
+              + f"; extrapolated x{layers} layers x{cfg['batch'] // n_seqs} sequences; embedding, lm_head and sampler not included")
+    return value, sample, stages, sum(per_kind.values())
+
+
+def run_reference_arm(args, cfg, tau):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    n_seqs = 2
-    times = []
+    values, sample, stages, secs = [], "", {}, 0.0
     for _ in range(args.warmup):
-        cpu_layer_step_seconds(n_seqs, 1, threads)
+        cpu_layer_step_seconds(cfg, "pruned", 1, 3, 1, threads)
     for _ in range(args.steps):
-        times.append(cpu_layer_step_seconds(n_seqs, 8, threads))
-    sec = sum(times) / len(times)
-    value = cpu_tokens_per_s(sec, n_seqs)
-    sample = (f"one sparse layer-step of the restated path (fp32 torch on CPU) for {n_seqs} of {BATCH} sequences per step, "
-              f"extrapolated x{BATCH // n_seqs} sequences x32 layers x{DSTEPS} denoising steps; embedding, lm_head and "
-              f"sampler not included")
+        v, sample, stages, secs = cpu_baseline(cfg, tau, threads, repeats=2)
+        values.append(v)
+    value = sum(values) / len(values)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": metric_name(cfg, tau), "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_dict(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": config_dict(cfg, tau, args.gpus, args),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+                         "stage_seconds_per_layer_step": stages},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def config_dict(n_gpus: int):
-    return {"workload": "configs[1]: LLaDA-8B shape, 32 layers, batch 16, prompt 256 uniform-random ids, gen 256, "
-                        "block 32, 256 denoising steps (8 dense + 248 sparse, full-sequence refresh every 4th sparse "
-                        "step as in the reference code), tau 0.99",
-            "global_batch": BATCH, "prompt_len": PROMPT, "gen_len": GEN, "parallelism": f"tp{n_gpus}",
-            "l2": "inputs_larger_than_l2 (16 GB of weights streamed per denoising step)",
-            "step_driver": "device-resident loop; each denoising step replays a captured CUDA graph (with several "
-                           "ranks: a chain of graphs with the NCCL all-reduces issued between them); the "
-                           "vocabulary projection runs on the rows the sampler reads (current block)"}
+def config_dict(cfg, tau, n_gpus: int, args):
+    dense, sparse, pruned = step_mix(cfg, tau is None)
+    par = f"tp{n_gpus}" + (f"+ep{n_gpus}" if getattr(args, "ep", False) and n_gpus > 1 else "")
+    return {"workload": f"{cfg['label']}, batch {cfg['batch']}, prompt {cfg['prompt']} uniform-random ids, gen {cfg['gen']}, "
+                        f"block {cfg['block']}, {cfg['steps']} denoising steps ({dense} dense + {sparse} full-sequence sparse + "
+                        f"{pruned} response-only sparse, refresh period 4 as in the reference code), "
+                        + ("dense comparator (no sparse steps)" if tau is None else f"tau {tau:g}"),
+            "global_batch": cfg["batch"], "prompt_len": cfg["prompt"], "gen_len": cfg["gen"], "parallelism": par,
+            "l2": "inputs_larger_than_l2 (the weights streamed per denoising step exceed the 126 MB L2 many times)",
+            "step_driver": "device-resident loop; each denoising step replays one captured CUDA graph (with several "
+                           "ranks the graph holds the NCCL o_proj all-reduces and the peer-memory exchanges of the "
+                           "statistics and FFN rows); the vocabulary projection runs on the rows the sampler reads"}
 
 
 # ----------------------------------------------------------------------------------------------
 # this library
 # ----------------------------------------------------------------------------------------------
-def run_ours(args):
+def build_model(cfg, tau, dev, layers_override, ep: bool):
+    from dyllm_b200 import model as M
+
+    thr = 0.99 if tau is None else tau
+    fam = cfg["family"]
+    if fam == "dream":
+        shape = M.DreamShape()
+        ctor = lambda: M.DreamForDLM(shape, thr)
+    elif fam == "lladamoe":
+        shape = M.LLaDAMoEShape()
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        ctor = lambda: M.LLaDAMoEForDLM(shape, thr, world if ep else 1)
+    else:
+        shape = M.LLaDAShape()
+        ctor = lambda: M.LLaDAForDLM(shape, thr)
+    if layers_override:
+        shape.num_hidden_layers = layers_override
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = ctor()
+    finally:
+        torch.set_default_dtype(torch.float32)
+    M.init_weights_(model, seed=0)
+    return model.eval(), shape
+
+
+def _exit_after(seconds: float):
+    """Teardown guard: the JSON line is out; if releasing the process group still blocks, leave anyway."""
+    t = threading.Timer(seconds, lambda: os._exit(0))
+    t.daemon = True
+    t.start()
+
+
+def run_ours(args, cfg, tau):
     import torch.distributed as dist
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -213,20 +345,34 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from dyllm_b200 import _lib, profiling, runner
-    from dyllm_b200.model import LLaDAForDLM, LLaDAShape, init_weights_
+    from dyllm_b200 import _lib, layers, profiling, runner
 
     _lib.load()
-    shape = LLaDAShape(num_hidden_layers=args.layers)
-    torch.set_default_dtype(torch.bfloat16)
-    with torch.device(dev):
-        model = LLaDAForDLM(shape, TAU)
-    torch.set_default_dtype(torch.float32)
-    init_weights_(model, seed=0)
-    model.eval()
-    sr = runner.StepRunner(model, shape.mask_token_id, BLOCK, args.denoise_steps, args.full_steps, REFRESH)
+    B, P, GEN = cfg["batch"], cfg["prompt"], cfg["gen"]
+    comm, exchange = None, "none"
+    if world > 1:
+        exchange = "nccl"
+        if args.tp_exchange == "peer":
+            from dyllm_b200.tp_comm import TpComm
+
+            hidden = layer_shape(cfg)[0]
+            slot_rows = min(B * (P + GEN), 32768)
+            comm = TpComm.from_process_group(dev, slot_bytes=slot_rows * hidden * 2)
+            layers.set_tp_comm(comm)
+            exchange = "peer-memory stores over NVLink (statistics, FFN rows) + NCCL (o_proj)"
+
+    tp_parity = None
+    if world > 1 and not args.no_tp_parity:
+        from dyllm_b200 import tp_selfcheck
+
+        tp_parity = tp_selfcheck.run(dev, 0.99)
+
+    model, shape = build_model(cfg, tau, dev, args.layers, args.ep)
+    dsteps = args.denoise_steps or cfg["steps"]
+    full_steps = dsteps if tau is None else (args.full_steps if args.full_steps is not None else cfg["full"])
+    sr = runner.StepRunner(model, shape.mask_token_id, cfg["block"], dsteps, full_steps, REFRESH)
     g = torch.Generator().manual_seed(1)
-    prompts = torch.randint(0, shape.vocab_size - 1024, (BATCH, PROMPT), generator=g).tolist()
+    prompts = torch.randint(0, shape.vocab_size - 1024, (B, P), generator=g).tolist()
 
     def barrier():
         if world > 1:
@@ -267,7 +413,8 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_s = float(e2e_s.item())
-    assert len(out_tokens) == BATCH and len(out_tokens[0]) == GEN
+    io_per_gen = {k: v // e2e_gens for k, v in runner.io_bytes.items()}   # read before the profiling pass adds to it
+    assert len(out_tokens) == B and len(out_tokens[0]) == GEN
 
     # ---- per-kernel durations: one more generation of the same workload with CUDA events around this
     # library's main kernels (events cannot be timed inside a graph, so this pass launches eagerly) ----
@@ -283,13 +430,23 @@ def run_ours(args):
     counts = profiling.counts()
     profiling.enable(False)
 
-    if rank != 0:
+    def teardown():
+        sr.release_graphs()          # graphs that captured NCCL kernels keep the communicator alive
+        if comm is not None:
+            layers.set_tp_comm(None)
+            comm.close()
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
+
+    if rank != 0:
+        _exit_after(120.0)
+        teardown()
         return
 
-    value = args.steps * BATCH * GEN / (total_ms / 1e3)
+    value = args.steps * B * GEN / (total_ms / 1e3)
     peaks = measured_peaks()
+    traffic = ncu_traffic_bytes() if args.config == 1 and world == 1 else {}
     # dominant kernel of this library; its bound is the roofline that gives the longer time
     mine = {k: v for k, v in prof.items() if v["launches"]}
     dominant = max(mine, key=lambda k: mine[k]["total_ms"]) if mine else None
@@ -299,7 +456,7 @@ def run_ours(args):
         secs = d["total_ms"] / 1e3
         t_hbm = d["bytes"] / (peaks["hbm_gbs"] * 1e9)
         t_tensor = d["work"] / (peaks["tflops"] * 1e12)
-        common = {"traffic": NCU_TRAFFIC_BYTES.get(dominant), "avg_launch_ms": d["avg_ms"], "launches": d["launches"],
+        common = {"traffic": traffic.get(dominant), "avg_launch_ms": d["avg_ms"], "launches": d["launches"],
                   "algorithmic_bytes_per_launch": d["bytes"] / d["launches"],
                   "algorithmic_flops_per_launch": d["work"] / d["launches"],
                   "timed_in": "one generation of the same workload launched eagerly with CUDA events around the "
@@ -313,33 +470,40 @@ def run_ours(args):
             roofline = {"kernel": dominant, "bound": "tensor", "achieved": tflops, "peak": peaks["tflops"],
                         "unit": "TFLOP/s", "frac": tflops / peaks["tflops"],
                         "peak_source": f"{peaks['source']} (sustained bf16)", **common}
-    kernels = {k: {"avg_ms": round(v["avg_ms"], 4), "launches": v["launches"],
-                   "share_of_step": round(v["total_ms"] / instr_ms, 4)} for k, v in mine.items()}
+    kernels = {}
+    for k, v in mine.items():
+        secs = v["total_ms"] / 1e3
+        kernels[k] = {"avg_ms": round(v["avg_ms"], 4), "launches": v["launches"],
+                      "share_of_step": round(v["total_ms"] / instr_ms, 4),
+                      "tflops": round(v["work"] / secs / 1e12, 1) if v["work"] else None,
+                      "gbs": round(v["bytes"] / secs / 1e9, 1) if v["bytes"] else None}
     sal = counts.get("salient_rows", [])
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        n_seqs = 2
-        sec = cpu_layer_step_seconds(n_seqs, 30, threads)
-        cpu = {"value": cpu_tokens_per_s(sec, n_seqs, args.layers), "unit": "tokens/s", "cores": threads, "kind": "port",
-               "sample": f"30 sparse layer-steps of the restated path for {n_seqs} of {BATCH} sequences "
-                         f"({sec:.2f} s each), extrapolated to {args.layers} layers x {DSTEPS} steps x {BATCH} sequences; "
-                         f"embedding, lm_head and sampler not included"}
+        mean_sal = max(1, round((sum(sal) / len(sal)) / B)) if sal else 3
+        v, sample, stages, _ = cpu_baseline(cfg, tau, threads, repeats=3, sal_per_seq=mean_sal)
+        cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample,
+               "stage_seconds_per_layer_step": stages}
+    cfg_d = config_dict(cfg, tau, world, args)
+    cfg_d["tp_exchange"] = exchange
     line = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": metric_name(cfg, tau), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(world),
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_d,
         "clocks": clocks, "gpu_launches": launches,
-        "e2e": {"value": e2e_gens * BATCH * GEN / e2e_s, "unit": "tokens/s",
-                "h2d_bytes_per_step": runner.io_bytes["h2d"] // e2e_gens, "d2h_bytes_per_step": runner.io_bytes["d2h"] // e2e_gens},
+        "e2e": {"value": e2e_gens * B * GEN / e2e_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": io_per_gen["h2d"], "d2h_bytes_per_step": io_per_gen["d2h"]},
         "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels,
         "salient_rows_per_layer": {"mean": (sum(sal) / len(sal)) if sal else None, "max": max(sal) if sal else None},
     }
-    if args.layers != 32 or args.denoise_steps != DSTEPS or args.full_steps != FULL_STEPS:
+    if tp_parity is not None:
+        line["tp_parity"] = tp_parity
+    if args.layers or args.denoise_steps or args.full_steps is not None:
         line["invalid_reduced_config"] = True
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    _exit_after(120.0)
+    teardown()
 
 
 def main():
@@ -348,15 +512,26 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=32, help="debug only: fewer layers marks the line invalid")
-    ap.add_argument("--denoise-steps", type=int, default=DSTEPS, help="debug only")
-    ap.add_argument("--full-steps", type=int, default=FULL_STEPS, help="debug only: dense steps per generation")
+    ap.add_argument("--config", type=int, default=1, choices=sorted(CONFIGS))
+    ap.add_argument("--tau", type=float, default=None, help="salient threshold (default: the workload's, 0.99)")
+    ap.add_argument("--dense", action="store_true", help="the tau=None comparator: every denoising step dense")
+    ap.add_argument("--ep", action="store_true", help="config 4: whole experts per rank (expert parallelism)")
+    ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
+                    help="carrier of the small per-layer all-reduces under tensor parallelism")
+    ap.add_argument("--no-tp-parity", action="store_true", help="skip the sharded-vs-unsharded layer self-check")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers marks the line invalid")
+    ap.add_argument("--denoise-steps", type=int, default=0, help="debug only")
+    ap.add_argument("--full-steps", type=int, default=None, help="debug only: dense steps per generation")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    cfg = dict(CONFIGS[args.config])
+    tau = None if args.dense else (args.tau if args.tau is not None else cfg["tau"])
+    if tau is not None:
+        cfg["tau"] = tau
     if args.impl == "reference":
-        run_reference_arm(args)
+        run_reference_arm(args, cfg, tau)
     else:
-        run_ours(args)
+        run_ours(args, cfg, tau)
 
 
 if __name__ == "__main__":

@@ -18,8 +18,8 @@ from torch import nn
 from . import ops
 from .cache_manager import CacheManager
 from .context import get_context, get_metadata
-from .layers import (Attention, ColumnParallelLinear, KVParallelLinear, LLaDAMLP, RMSNorm, RotaryEmbedding,
-                     RowParallelLinear, _world_size)
+from .layers import (Attention, ColumnParallelLinear, KVParallelLinear, LLaDAMLP, LLaDAMoESparseBlock, RMSNorm,
+                     RotaryEmbedding, RowParallelLinear, _world_size)
 
 
 @dataclass
@@ -42,7 +42,8 @@ class LLaDAShape:
 class LLaDAAttention(nn.Module):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, max_position: int, head_dim: int,
                  rms_norm_eps: float = 1e-06, qkv_bias: bool = False, rope_theta: float = 10000.0,
-                 rope_scaling: tuple | None = None, threshold: float = 0.99, rotary_emb: RotaryEmbedding | None = None):
+                 rope_scaling: tuple | None = None, threshold: float = 0.99, rotary_emb: RotaryEmbedding | None = None,
+                 qk_layernorm: bool = False):
         super().__init__()
         tp = _world_size()
         self.total_num_heads = num_heads
@@ -56,6 +57,9 @@ class LLaDAAttention(nn.Module):
         self.q_proj = ColumnParallelLinear(hidden_size, self.total_num_heads * self.head_dim, bias=qkv_bias)
         self.kv_proj = KVParallelLinear(hidden_size, self.head_dim, self.total_num_kv_heads, bias=qkv_bias)
         self.o_proj = RowParallelLinear(self.total_num_heads * self.head_dim, hidden_size, bias=False)
+        # per-head RMSNorm of the projected queries and keys (LLaDA-MoE; ref: lladamoe.py:175-176,195-207)
+        self.q_norm = RMSNorm(self.head_dim, eps=rms_norm_eps) if qk_layernorm else None
+        self.k_norm = RMSNorm(self.head_dim, eps=rms_norm_eps) if qk_layernorm else None
         self.k_cache = CacheManager(self.num_kv_heads * self.head_dim)
         assert rope_scaling is None
         self.rotary_emb = rotary_emb or RotaryEmbedding(self.head_dim, self.head_dim, max_position, rope_theta)
@@ -64,10 +68,15 @@ class LLaDAAttention(nn.Module):
     def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
         ctx, md = get_context(), get_metadata()
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
-        q = self.q_proj(hidden_states).view(-1, H, D)
+        q = self.q_proj(hidden_states)
+        if self.q_norm is not None:
+            q = self.q_norm(q.view(-1, D))
+        q = q.view(-1, H, D)
         if ctx.is_full:
             kv = self.kv_proj(hidden_states)
             k, v = kv.split([self.kv_size, self.kv_size], dim=-1)
+            if self.k_norm is not None:
+                k = self.k_norm(k.reshape(-1, D))
             k, v = k.reshape(-1, Hkv, D), v.reshape(-1, Hkv, D)
             q, k = self.rotary_emb(positions, q, k)
             self.k_cache.reset_full(k.flatten(-2, -1), md.running_seqs_tensor, seq_ids_list=md.running_seqs)
@@ -81,6 +90,8 @@ class LLaDAAttention(nn.Module):
                 k_new, v_new = self.kv_proj.forward_gathered(hidden_states, ctx.idx_salient_row32, cap, n_dev, hint,
                                                              split_col=self.kv_size)
                 rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
+                if self.k_norm is not None:
+                    k_new = self.k_norm(k_new.view(-1, D))       # rows past the live count hold nothing of value
                 v_new = v_new.view(cap, Hkv, D)
                 # rotary embedding of the new keys, K-cache scatter, delta-V and V-cache update in one launch
                 dv = ops.kv_cache_update(k_new.view(cap, Hkv, D), v_new, rows_k, positions, ctx.idx_salient_row,
@@ -149,6 +160,198 @@ class LLaDAForDLM(nn.Module):
         super().__init__()
         self.config = config
         self.model = LLaDAModel(config, threshold)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+
+    def forward(self, input_ids, positions):
+        return self.model(input_ids, positions)
+
+    def compute_logits(self, hidden_states):
+        return self.lm_head(hidden_states)
+
+
+# --------------------------------------------------------------------------------------------------
+# Dream (ref: dyllm/model_executor/models/dream.py): grouped-query attention with biased q/k/v projections
+# --------------------------------------------------------------------------------------------------
+@dataclass
+class DreamShape:
+    """The fields of the reference's ``DreamConfig`` that the decoder reads (ref: dyllm/configs/dream.py);
+    defaults are the Dream-7B shape."""
+
+    hidden_size: int = 3584
+    num_attention_heads: int = 28
+    num_key_value_heads: int = 4
+    head_dim: int = 128
+    intermediate_size: int = 18944
+    num_hidden_layers: int = 28
+    vocab_size: int = 152064
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1000000.0
+    max_position_embeddings: int = 4096
+    mask_token_id: int = 151666
+
+
+class DreamAttention(LLaDAAttention):
+    """ref: dyllm/model_executor/models/dream.py:46-144 (same data flow as the LLaDA block; qkv bias on)."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, max_position: int, head_dim: int,
+                 rms_norm_eps: float = 1e-06, qkv_bias: bool = True, rope_theta: float = 1000000.0,
+                 rope_scaling: tuple | None = None, threshold: float = 0.99, rotary_emb: RotaryEmbedding | None = None):
+        super().__init__(hidden_size, num_heads, num_kv_heads, max_position, head_dim, rms_norm_eps, qkv_bias,
+                         rope_theta, rope_scaling, threshold, rotary_emb)
+
+
+class DreamMLP(LLaDAMLP):
+    """ref: dyllm/model_executor/models/dream.py:26-43."""
+
+
+class _DecoderLayer(nn.Module):
+    """Residual wiring shared by the decoder layers (ref: llada.py:173-187, dream.py:168-182,
+    lladamoe.py:266-280): add-RMSNorm, attention, add-RMSNorm, FFN on all rows (dense step) or on the salient
+    rows through the step's index list (sparse step)."""
+
+    def forward(self, positions, hidden_states, residual=None):
+        if residual is None:
+            hidden_states, residual = self.input_layernorm(hidden_states), hidden_states
+        else:
+            hidden_states, residual = self.input_layernorm(hidden_states, residual)
+        hidden_states = self.self_attn(positions, hidden_states)
+        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
+        if get_context().is_full:
+            hidden_states = self.mlp(hidden_states)
+        else:
+            hidden_states = self.mlp.forward_salient(hidden_states)
+        return hidden_states, residual
+
+
+class DreamDecoderLayer(_DecoderLayer):
+    def __init__(self, config: DreamShape, threshold: float, rotary_emb: RotaryEmbedding | None = None) -> None:
+        super().__init__()
+        self.self_attn = DreamAttention(
+            hidden_size=config.hidden_size, num_heads=config.num_attention_heads,
+            num_kv_heads=config.num_key_value_heads, max_position=config.max_position_embeddings,
+            rms_norm_eps=config.rms_norm_eps, qkv_bias=True, head_dim=getattr(config, "head_dim", None),
+            rope_theta=getattr(config, "rope_theta", 1000000.0), threshold=threshold, rotary_emb=rotary_emb)
+        self.mlp = DreamMLP(hidden_size=config.hidden_size, intermediate_size=config.intermediate_size)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+
+class _DecoderStack(nn.Module):
+    def _finish_init(self) -> None:
+        # every layer's output goes straight into an RMSNorm of this package, which reads a block of every
+        # sequence out of the FFN-output cache in place
+        for layer in self.layers:
+            layer.mlp.cache_update.block_view = True
+
+    def forward(self, input_ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        hidden_states = self.embed_tokens(input_ids)
+        residual = None
+        for layer in self.layers:
+            hidden_states, residual = layer(positions, hidden_states, residual)
+        hidden_states, _ = self.norm(hidden_states, residual)
+        return hidden_states
+
+
+class DreamModel(_DecoderStack):
+    def __init__(self, config: DreamShape, threshold: float):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size)
+        rope = RotaryEmbedding(config.head_dim, config.head_dim, config.max_position_embeddings, config.rope_theta)
+        self.layers = nn.ModuleList([DreamDecoderLayer(config, threshold, rope) for _ in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self._finish_init()
+
+
+class DreamForDLM(nn.Module):
+    """ref: dyllm/model_executor/models/dream.py:201-234.  ``shift_logits``: the reference's Dream sampler reads
+    the logits of the row before each candidate (sampler.py, ``DreamSampler.adjust_logits``)."""
+
+    shift_logits = True
+
+    def __init__(self, config: DreamShape, threshold: float):
+        super().__init__()
+        self.config = config
+        self.model = DreamModel(config, threshold)
+        self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+
+    def forward(self, input_ids, positions):
+        return self.model(input_ids, positions)
+
+    def compute_logits(self, hidden_states):
+        return self.lm_head(hidden_states)
+
+
+# --------------------------------------------------------------------------------------------------
+# LLaDA-MoE (ref: dyllm/model_executor/models/lladamoe.py): per-head q/k RMSNorm, mixture-of-experts FFN
+# --------------------------------------------------------------------------------------------------
+@dataclass
+class LLaDAMoEShape:
+    """The fields of the LLaDA-MoE configuration that the decoder reads; defaults are LLaDA-MoE-7B-A1B."""
+
+    hidden_size: int = 2048
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 16
+    head_dim: int = 128
+    num_experts: int = 64
+    num_experts_per_tok: int = 8
+    expert_intermediate_size: int = 1024
+    norm_topk_prob: bool = False
+    num_hidden_layers: int = 16
+    vocab_size: int = 157184
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 50000.0
+    max_position_embeddings: int = 4096
+    qk_layernorm: bool = True
+    attention_bias: bool = False
+    mask_token_id: int = 156895
+
+
+class LLaDAMoEAttention(LLaDAAttention):
+    """ref: dyllm/model_executor/models/lladamoe.py:145-242."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, max_position: int, head_dim: int,
+                 rms_norm_eps: float = 1e-05, qkv_bias: bool = False, rope_theta: float = 50000.0,
+                 rope_scaling: tuple | None = None, qk_layernorm: bool = True, threshold: float = 0.99,
+                 rotary_emb: RotaryEmbedding | None = None):
+        super().__init__(hidden_size, num_heads, num_kv_heads, max_position, head_dim, rms_norm_eps, qkv_bias,
+                         rope_theta, rope_scaling, threshold, rotary_emb, qk_layernorm=qk_layernorm)
+
+
+class LLaDAMoEDecoderLayer(_DecoderLayer):
+    def __init__(self, config: LLaDAMoEShape, threshold: float, expert_parallel_size: int = 1,
+                 rotary_emb: RotaryEmbedding | None = None) -> None:
+        super().__init__()
+        head_dim = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
+        self.self_attn = LLaDAMoEAttention(
+            hidden_size=config.hidden_size, num_heads=config.num_attention_heads,
+            num_kv_heads=config.num_key_value_heads, max_position=config.max_position_embeddings, head_dim=head_dim,
+            rms_norm_eps=config.rms_norm_eps, qkv_bias=getattr(config, "attention_bias", False),
+            rope_theta=getattr(config, "rope_theta", 50000), qk_layernorm=bool(getattr(config, "qk_layernorm", False)),
+            threshold=threshold, rotary_emb=rotary_emb)
+        self.mlp = LLaDAMoESparseBlock(config, expert_parallel_size)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+
+class LLaDAMoEModel(_DecoderStack):
+    def __init__(self, config: LLaDAMoEShape, threshold: float, expert_parallel_size: int = 1):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(config.vocab_size, config.hidden_size)
+        rope = RotaryEmbedding(config.head_dim, config.head_dim, config.max_position_embeddings, config.rope_theta)
+        self.layers = nn.ModuleList([LLaDAMoEDecoderLayer(config, threshold, expert_parallel_size, rope)
+                                     for _ in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self._finish_init()
+
+
+class LLaDAMoEForDLM(nn.Module):
+    """ref: dyllm/model_executor/models/lladamoe.py:301-315.  ``expert_parallel_size`` is 1 (every expert
+    sharded over the tensor-parallel ranks) or the tensor-parallel size (whole experts per rank)."""
+
+    def __init__(self, config: LLaDAMoEShape, threshold: float, expert_parallel_size: int = 1):
+        super().__init__()
+        self.config = config
+        self.model = LLaDAMoEModel(config, threshold, expert_parallel_size)
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
 
     def forward(self, input_ids, positions):

@@ -129,7 +129,8 @@ def prepare_full(seqs: List[Sequence], device: torch.device):
 def prepare_sparse(seqs: List[Sequence], device: torch.device, refresh_period: int = 4):
     """ref: dyllm/engine/model_runner.py:186-298.  ``refresh_period`` is the reference's hard-coded 4:
     a step with ``processed_steps > period and processed_steps % period != 0`` uses response-only
-    queries, every other sparse step the full sequence."""
+    queries, every other sparse step the full sequence.  ``processed_steps`` counts the current step too
+    (the reference's scheduler increments it before the step runs, dyllm/engine/scheduler.py:43,69)."""
     input_ids, positions, positions_k = [], [], []
     idx_q, idx_k, idx_upd = [], [], []
     cu_q, cu_k, cu_p, cu_sal = [0], [0], [0], [0]
@@ -214,27 +215,32 @@ class StepRunner:
         self._graphs: dict = {}
         self._warm: set = set()
         self._graph_pool = None
-        self._geometry = None
+        self._geometry = 0          # the model's cache epoch this runner's graphs belong to
 
     def _set_geometry(self, key) -> None:
-        """Called at the start of every generation with (batch, sequence lengths).  Sequence ids are reused
-        from one generation to the next, so when the geometry changes the activation caches forget the
-        previous batch (its ranges have other lengths) and every captured graph is dropped: a graph holds
-        the addresses and row offsets of the geometry it was captured for, and the cache arenas may move
-        when they grow."""
-        if key == self._geometry:
-            return
-        if self._geometry is not None:
+        """Called at the start of every generation with (sequence lengths, generation length).  Sequence ids
+        are reused from one generation to the next, so when the geometry changes the model's activation caches
+        forget the previous batch (its ranges have other lengths).  The record of the geometry lives on the
+        model, whose caches it describes; every runner of that model drops its captured graphs and state
+        buffers when the caches have been cleared since it captured them: a graph holds the addresses and row
+        offsets of the geometry it was captured for, and the cache arenas may move when they grow."""
+        state = getattr(self.model, "_dyllm_cache_state", None)
+        if state is None:
+            state = self.model._dyllm_cache_state = {"key": None, "epoch": 0}
+        if state["key"] is not None and state["key"] != key:
             from .cache_manager import CacheManager
 
             torch.cuda.synchronize(self.device)
-            self.release_graphs()
-            self._states.clear()
             for module in self.model.modules():
                 for value in vars(module).values():
                     if isinstance(value, CacheManager):
                         value.clear()
-        self._geometry = key
+            state["epoch"] += 1
+        state["key"] = key
+        if self._geometry != state["epoch"]:
+            self.release_graphs()
+            self._states.clear()
+            self._geometry = state["epoch"]
 
     def release_graphs(self) -> None:
         """Destroys every captured graph (needed before the process group is destroyed when the graphs
@@ -257,14 +263,25 @@ class StepRunner:
     @torch.inference_mode()
     def step(self, seqs: List[Sequence]) -> int:
         """One denoising step of every sequence; returns the number of tokens unmasked."""
-        is_full = seqs[0].processed_steps < self.num_full_steps
+        return sum(len(p) for p in self.step_picks(seqs))
+
+    @torch.inference_mode()
+    def step_picks(self, seqs: List[Sequence], forced=None):
+        """One denoising step; returns, per sequence, the ``(position, token)`` pairs this package's path chose
+        to unmask, ascending by position.  ``forced`` (same format) replaces them when the sequences are
+        updated: a test can keep the state on a recorded trajectory while it compares every step's choice.
+        The step counter follows the reference's scheduler (dyllm/engine/scheduler.py:29-75): it is
+        incremented before the step, the first ``num_full_steps`` steps are dense."""
+        for seq in seqs:
+            seq.processed_steps += 1
+        is_full = seqs[0].processed_steps <= self.num_full_steps
         if is_full:
             input_ids, positions = prepare_full(seqs, self.device)
         else:
             input_ids, positions = prepare_sparse(seqs, self.device, self.refresh_period)
         ctx = get_context()
         hidden = self.model(input_ids, positions)
-        return self._unmask(seqs, hidden, ctx)
+        return self._unmask(seqs, hidden, ctx, forced)
 
     def generate(self, prompts: List[List[int]], max_new_tokens: int, device_state: bool = True) -> List[List[int]]:
         """Runs all denoising steps of one batch and returns the generated token ids (host lists).
@@ -413,9 +430,10 @@ class StepRunner:
         set_metadata(seq_ids, seq_ids, [])
         get_metadata().running_seqs_tensor = st.seq_t
         for step in range(self.steps):
-            if step < self.num_full_steps:
+            done = step + 1     # the reference's processed_steps: incremented before the step runs
+            if done <= self.num_full_steps:
                 kind = "full"
-            elif step > self.refresh_period and step % self.refresh_period != 0:
+            elif done > self.refresh_period and done % self.refresh_period != 0:
                 kind = "pruned"
             else:
                 kind = "sparse"
@@ -425,7 +443,10 @@ class StepRunner:
         return out.tolist()
 
     def _block_logits(self, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-        """Logits of the given query rows."""
+        """Logits of the given query rows.  A model with ``shift_logits`` (Dream) predicts the token of row r
+        from row r - 1 of the packed batch (ref: sampler.py, ``DreamSampler.adjust_logits``)."""
+        if getattr(self.model, "shift_logits", False):
+            rows = (rows - 1).clamp_min(0)
         if self.full_logits:
             return self.model.compute_logits(hidden).index_select(0, rows)
         return self.model.compute_logits(hidden.index_select(0, rows))
@@ -437,7 +458,7 @@ class StepRunner:
         conf, tok = ops.row_confidence(logits.contiguous())     # bf16 logits on a GPU; raises otherwise
         return conf.view(B, blk_len), tok.view(B, blk_len)
 
-    def _unmask(self, seqs: List[Sequence], hidden: torch.Tensor, ctx) -> int:
+    def _unmask(self, seqs: List[Sequence], hidden: torch.Tensor, ctx, forced=None):
         B = len(seqs)
         gen = seqs[0].max_new_tokens
         steps_per_block = max(1, self.steps * self.block_length // gen)
@@ -445,7 +466,7 @@ class StepRunner:
         cu_q = ctx.cu_seqlens_q_cpu
         rows, cand_pos = [], []
         for b, seq in enumerate(seqs):
-            blk = min(seq.processed_steps // steps_per_block, gen // self.block_length - 1)
+            blk = min((seq.processed_steps - 1) // steps_per_block, gen // self.block_length - 1)
             start = seq.num_prompt_tokens + blk * self.block_length
             lq = cu_q[b + 1] - cu_q[b]
             off = start - (len(seq) - lq)  # position -> row inside this sequence's query rows
@@ -463,7 +484,7 @@ class StepRunner:
         top_conf, top_i = conf.topk(num_transfer, dim=-1)
         picked = torch.stack([top_i, tok.gather(1, top_i), (top_conf >= 0).long()], dim=-1).cpu()  # one D2H per step
         io_bytes["d2h"] += picked.numel() * picked.element_size()
-        n_unmasked = 0
+        picks = []
         for b, seq in enumerate(seqs):
             chosen = []
             for j in range(num_transfer):
@@ -471,10 +492,10 @@ class StepRunner:
                 if ok:
                     chosen.append((cand_pos[b][i], int(t)))
             chosen.sort()  # the kernels expect ascending row lists
-            for p, t in chosen:
+            picks.append(chosen)
+            applied = sorted(forced[b]) if forced is not None else chosen
+            for p, t in applied:
                 seq.token_ids[p] = t
-            seq.last_token_pos = [p for p, _ in chosen]
-            seq.last_tokens = [t for _, t in chosen]
-            n_unmasked += len(chosen)
-            seq.processed_steps += 1
-        return n_unmasked
+            seq.last_token_pos = [p for p, _ in applied]
+            seq.last_tokens = [t for _, t in applied]
+        return picks

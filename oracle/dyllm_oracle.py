@@ -173,6 +173,28 @@ def cache_scatter_update(cache, new_vals, row_idx, cu_seqlens, seq_starts, seq_i
     return cache
 
 
+def delta_v_update(v_new, v_cache, rows):
+    """dV of the step's salient rows and the value-cache update: ``dv = v_new - cache[rows]`` in the
+    tensors' own dtype (bf16 in the reference: one rounding of the difference), then ``cache[rows] = v_new``
+    in place.  Returns dv.  ref: dyllm/model_executor/layers/attention.py:67-74 (v_delta and the update of
+    the gathered copy), :89-96 (the same rows written back to the cache by scatter_update)."""
+    r = torch.as_tensor(_np(rows).astype(np.int64))
+    dv = v_new - v_cache[r]
+    v_cache[r] = v_new
+    return dv
+
+
+def kv_cache_update(k_new, v_new, rows_k, positions_of_rows, k_cache, v_cache, k_rows, v_rows, head_dim, base, max_position):
+    """What the reference does between the K/V projection of the salient rows and the attention kernels:
+    rotary embedding of the new keys (dyllm/model_executor/models/llada.py:110-130: the keys are placed in a
+    zero tensor, rotated with every row's position and read back, i.e. row i is rotated with its own
+    position), ``k_cache.scatter_update`` (llada.py:136-143) and the delta-V / value-cache update above.
+    ``k_rows`` / ``v_rows`` are the cache rows of the salient tokens in the two caches.  In place; returns dv."""
+    kr = rope(positions_of_rows, k_new, head_dim, base, max_position)
+    k_cache[torch.as_tensor(_np(k_rows).astype(np.int64))] = kr.flatten(1).to(k_cache.dtype)
+    return delta_v_update(v_new.flatten(1), v_cache, v_rows)
+
+
 # --------------------------------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------------------------------

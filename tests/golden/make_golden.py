@@ -1,14 +1,18 @@
-"""Generates tests/golden/llada_layer_small.pt by running the REFERENCE's own Python
+"""Generates tests/golden/llada_layer_small.pt and tests/golden/llada_layer_c1.pt by running the REFERENCE's own Python
 (`LLaDADecoderLayer`, `Attention`, `CacheManager`, `MLPcache`, `tensor_parallel_cosine_mask`, ...) on the CPU with
 bf16 modules and caches (as the reference runs them on a GPU; in fp32 its in-place RMSNorm would alias
 the residual), with the three native modules it imports replaced by the oracle's fp32 restatements.
 
 Run in the development container only (it needs the reference checkout):
 
-    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py /path/to/reference
+    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py /path/to/reference [small|c1]
 
-The fixture holds seeds, shapes and outputs; weights and inputs are regenerated from the seeds by
-`golden_inputs()` below, which the tests import.
+"small" is a toy shape; "c1" is the single-layer LLaDA-8B configuration (hidden 4096, 32 heads of 128, FFN
+intermediate 12288, one sequence of 256 prompt + 256 response positions).  The inputs are bimodal: the
+listed rows and a few more response rows change a lot between steps, all others little, and the generator
+asserts that every cosine the reference computes lies at least 1e-4 from the threshold.  A fixture holds seeds, shapes and outputs (for "c1": the
+outputs of a fixed subset of rows in bf16 plus per-row sums and norms of all rows, to stay small); weights
+and inputs are regenerated from the seeds by `golden_inputs()` below, which the tests import.
 """
 import os
 import sys
@@ -19,22 +23,41 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
 
-SHAPE = dict(hidden=256, heads=2, kv_heads=2, head_dim=128, inter=512, eps=1e-5, theta=500000.0, max_pos=512)
-BATCH, PROMPT, RESP = 2, 24, 40
+CONFIGS = {
+    "small": dict(shape=dict(hidden=256, heads=2, kv_heads=2, head_dim=128, inter=512, eps=1e-5, theta=500000.0, max_pos=512),
+                  batch=2, prompt=24, resp=40, seq_ids=[5, 3], seed=1234, wscale=0.05,
+                  salient={1: [[1, 7, 20], [3, 33]], 2: [[2, 9], [5, 30, 31]]}, extra=5, margin=0.0, subset=None),
+    "c1": dict(shape=dict(hidden=4096, heads=32, kv_heads=32, head_dim=128, inter=12288, eps=1e-5, theta=500000.0, max_pos=4096),
+               batch=1, prompt=256, resp=256, seq_ids=[0], seed=4321, wscale=0.02,
+               salient={1: [[3, 40, 41, 97, 130, 200, 255]], 2: [[0, 17, 64, 128, 129, 250]]}, extra=20, margin=1e-4,
+               subset=64),
+}
 TAU = 0.99
+_cfg = CONFIGS["small"]
+SHAPE, BATCH, PROMPT, RESP = _cfg["shape"], _cfg["batch"], _cfg["prompt"], _cfg["resp"]
 
 
-def golden_inputs(seed=1234):
+def use_config(name):
+    """Selects the configuration the module-level names (SHAPE, BATCH, PROMPT, RESP) and the functions below
+    refer to."""
+    global _cfg, SHAPE, BATCH, PROMPT, RESP
+    _cfg = CONFIGS[name]
+    SHAPE, BATCH, PROMPT, RESP = _cfg["shape"], _cfg["batch"], _cfg["prompt"], _cfg["resp"]
+    return _cfg
+
+
+def golden_inputs(seed=None):
     """Weights N(0, 0.02) (a larger scale for the value/FFN paths keeps cosines spread around the
     threshold) and three hidden-state inputs, all from one CPU generator."""
-    g = torch.Generator().manual_seed(seed)
+    g = torch.Generator().manual_seed(_cfg["seed"] if seed is None else seed)
+    ws = _cfg["wscale"]
     h, H, Hkv, D, I = SHAPE["hidden"], SHAPE["heads"], SHAPE["kv_heads"], SHAPE["head_dim"], SHAPE["inter"]
     w = {
-        "q_proj": torch.randn(H * D, h, generator=g) * 0.05,
-        "kv_proj": torch.randn(2 * Hkv * D, h, generator=g) * 0.05,
-        "o_proj": torch.randn(h, H * D, generator=g) * 0.05,
-        "gate_up_proj": torch.randn(2 * I, h, generator=g) * 0.05,
-        "down_proj": torch.randn(h, I, generator=g) * 0.05,
+        "q_proj": torch.randn(H * D, h, generator=g) * ws,
+        "kv_proj": torch.randn(2 * Hkv * D, h, generator=g) * ws,
+        "o_proj": torch.randn(h, H * D, generator=g) * ws,
+        "gate_up_proj": torch.randn(2 * I, h, generator=g) * ws,
+        "down_proj": torch.randn(h, I, generator=g) * ws,
     }
     w = {k: v.bfloat16().float() for k, v in w.items()}
     L = PROMPT + RESP
@@ -45,7 +68,7 @@ def golden_inputs(seed=1234):
     for step in (1, 2):
         bump = torch.zeros(BATCH * L, 1)
         for b in range(BATCH):
-            bump[b * L + PROMPT + torch.randperm(RESP, generator=g)[:5]] = 0.05
+            bump[b * L + PROMPT + torch.randperm(RESP, generator=g)[:_cfg["extra"]]] = 0.05 if _cfg["margin"] == 0.0 else 0.6
             for p in step_layout(step)[2][b]:
                 bump[b * L + p] = 0.6
         xs.append((xs[-1] + (0.003 + bump) * torch.randn(BATCH * L, h, generator=g)).bfloat16().float())
@@ -56,12 +79,31 @@ def step_layout(step):
     """(is_full, response_only, initial salient positions per sequence) of the three recorded steps."""
     if step == 0:
         return True, False, None
-    if step == 1:
-        return False, False, [[PROMPT + 1, PROMPT + 7, PROMPT + 20], [PROMPT + 3, PROMPT + 33]]
-    return False, True, [[PROMPT + 2, PROMPT + 9], [PROMPT + 5, PROMPT + 30, PROMPT + 31]]
+    sal = [[PROMPT + o for o in seq] for seq in _cfg["salient"][step]]
+    return False, step == 2, sal
 
 
-def main(ref_root):
+def subset_rows(rows, salient_idx):
+    """The rows whose outputs a compact fixture keeps: every salient row and an even spread of the others."""
+    n = _cfg["subset"]
+    keep = set(int(i) for i in (salient_idx.tolist() if salient_idx is not None else []))
+    keep.update(range(0, rows, max(1, rows // n)))
+    return torch.tensor(sorted(keep), dtype=torch.long)
+
+
+def pack_rows(out, residual, is_full, salient_idx):
+    """Full fp32 outputs for the toy shape; for the large one the outputs of subset_rows() in bf16 and per-row
+    sums / norms of every row."""
+    if _cfg["subset"] is None:
+        return {"out": out.float().clone(), "residual": residual.float().clone()}
+    rows = subset_rows(out.size(0), salient_idx)
+    o, r = out.float(), residual.float()
+    return {"rows": rows, "out_rows": out[rows].to(torch.bfloat16).clone(), "residual_rows": residual[rows].to(torch.bfloat16).clone(),
+            "out_sum": o.sum(1), "out_norm": o.norm(dim=1), "residual_sum": r.sum(1), "residual_norm": r.norm(dim=1)}
+
+
+def main(ref_root, config="small"):
+    use_config(config)
     os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
     import torch.distributed as dist
     from oracle import dyllm_oracle as orc
@@ -134,8 +176,8 @@ def main(ref_root):
         layer.post_attention_layernorm.weight.fill_(1.0)
 
     L = PROMPT + RESP
-    seq_ids = [5, 3]
-    record = {"shape": SHAPE, "batch": BATCH, "prompt": PROMPT, "resp": RESP, "tau": TAU, "seq_ids": seq_ids, "steps": []}
+    seq_ids = _cfg["seq_ids"]
+    record = {"config": config, "shape": SHAPE, "batch": BATCH, "prompt": PROMPT, "resp": RESP, "tau": TAU, "seq_ids": seq_ids, "steps": []}
     i32 = lambda v: torch.tensor(v, dtype=torch.int32)
     for step in range(3):
         is_full, ro, sal = step_layout(step)
@@ -167,22 +209,25 @@ def main(ref_root):
         with torch.no_grad():
             out, residual = layer(positions, x.clone().bfloat16(), None)
         ctx = get_context()
-        rec = {"out": out.float().clone(), "residual": residual.float().clone()}
+        rec = pack_rows(out, residual, is_full, None if is_full else ctx.idx_salient_row)
         if not is_full:
             rec["cosine"] = orc.cosine_values(seen_stats[-1]).float()
-            print("   min |cos - tau| =", float((rec["cosine"] - TAU).abs().min()))
+            gap = float((rec["cosine"] - TAU).abs().min())
+            print("   min |cos - tau| =", gap)
+            print("   rows within 2e-3 of tau:", int(((rec["cosine"] - TAU).abs() < 2e-3).sum()), "of", rec["cosine"].numel())
+            assert gap >= _cfg["margin"], "a cosine lies inside the margin: change the seed"
             rec["idx_salient_row"] = ctx.idx_salient_row.clone()
             rec["cu_salientlens"] = ctx.cu_salientlens.clone()
             if ro:
                 rec["idx_salient_row_k"] = ctx.idx_salient_row_k.clone()
         record["steps"].append(rec)
         print("step", step, "out", tuple(out.shape), "salient", None if is_full else ctx.idx_salient_row.tolist())
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "llada_layer_small.pt")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), f"llada_layer_{config}.pt")
     torch.save(record, path)
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":
     if len(sys.argv) < 2:
-        sys.exit("usage: make_golden.py /path/to/reference")
-    main(sys.argv[1])
+        sys.exit("usage: make_golden.py /path/to/reference [small|c1]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) > 2 else "small")

@@ -33,19 +33,24 @@ sys.path.insert(0, ROOT)
 
 TAU = 0.99
 
-# name -> (sequence lengths, response lengths, heads, kv heads, response-only queries, salient rows per sequence, seed)
+# name -> (sequence lengths, response lengths, heads, kv heads, response-only queries, salient rows per sequence,
+#          seed, query scale, delta-V scale).  The "strong" cases have peaked softmax rows and large value
+# updates, so that the P.dV term moves the context by O(1) and the cosines spread around the threshold.
 ATTENTION_CASES = {
-    "c1_heads4_full": ([512], [256], 4, 4, False, [26], 11),
-    "c1_heads4_pruned": ([512], [256], 4, 4, True, [26], 12),
-    "ragged_gqa_pruned": ([200, 136, 77], [64, 40, 33], 4, 2, True, [5, 0, 3], 13),
-    "ragged_gqa_full_dense_salient": ([192, 130], [96, 66], 4, 1, False, [40, 25], 14),
-    "batch4_mha_full": ([128, 128, 128, 128], [64, 64, 64, 64], 2, 2, False, [1, 16, 0, 7], 15),
+    "c1_heads4_full": ([512], [256], 4, 4, False, [26], 11, 1.0, 0.7),
+    "c1_heads4_pruned": ([512], [256], 4, 4, True, [26], 12, 1.0, 0.7),
+    "ragged_gqa_pruned": ([200, 136, 77], [64, 40, 33], 4, 2, True, [5, 0, 3], 13, 1.0, 0.7),
+    "ragged_gqa_full_dense_salient": ([192, 130], [96, 66], 4, 1, False, [40, 25], 14, 1.0, 0.7),
+    "batch4_mha_full": ([128, 128, 128, 128], [64, 64, 64, 64], 2, 2, False, [1, 16, 0, 7], 15, 1.0, 0.7),
+    "c1_heads4_full_strong": ([512], [256], 4, 4, False, [26], 16, 2.5, 6.0),
+    "ragged_gqa_pruned_strong": ([200, 136, 77], [64, 40, 33], 4, 2, True, [9, 4, 3], 17, 2.5, 6.0),
+    "ragged_gqa_full_strong": ([192, 130], [96, 66], 4, 1, False, [40, 25], 18, 2.0, 3.0),
 }
 
 
 def attention_case(name: str):
     """Seeded inputs of one attention case (CPU tensors; bf16 where the kernels take bf16)."""
-    lens, resp, H, Hkv, pruned, n_sal, seed = ATTENTION_CASES[name]
+    lens, resp, H, Hkv, pruned, n_sal, seed, q_scale, dv_scale = ATTENTION_CASES[name]
     g = torch.Generator().manual_seed(seed)
     D, B = 128, len(lens)
     lq = resp if pruned else lens
@@ -66,13 +71,13 @@ def attention_case(name: str):
         cu_sal.append(len(idx_q))
     S = len(idx_q)
     bf = lambda t: t.to(torch.bfloat16)
-    q = bf(torch.randn(Tq, H, D, generator=g))
+    q = bf(q_scale * torch.randn(Tq, H, D, generator=g))
     k = bf(torch.randn(Tk, Hkv, D, generator=g))
     v_cache = bf(torch.randn(Tk, Hkv, D, generator=g))
     c_old = bf(torch.randn(Tq, H, D, generator=g))
     dv = torch.zeros(Tk, Hkv, D)
     if S:
-        dv[torch.tensor(idx_k)] = 0.7 * torch.randn(S, Hkv, D, generator=g)
+        dv[torch.tensor(idx_k)] = dv_scale * torch.randn(S, Hkv, D, generator=g)
     dv = bf(dv)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32)
     return dict(q=q, k=k, v_cache=v_cache, dv=dv, c_old=c_old, cu_q=i32(cu_q), cu_k=i32(cu_k), cu_p=i32(cu_p),
@@ -124,7 +129,7 @@ def main():
     except Exception as e:  # flash-attn is third party; without it the salient rows come from fp32 softmax attention
         flash_attn_varlen_func = None
         print("flash_attn unavailable:", e)
-    record = {"attention": {}, "tau": TAU, "device": torch.cuda.get_device_name(0), "torch": torch.__version__,
+    record = {"attention": {}, "tau": TAU, "device": torch.cuda.get_device_name(0), "torch": str(torch.__version__),
               "kernel_info_d128": list(ops.attention_kernel_info(128, False))}
 
     for name in ATTENTION_CASES:

@@ -136,3 +136,60 @@ def test_kv_cache_update_equals_the_separate_steps(cuda_device, live):
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
     assert torch.equal(dv1.view(cap, Hkv, D)[:live], dv2[:live])
     assert bool((dv2[live:] == 0).all())
+
+
+@pytest.mark.parametrize("live", [41, 64])
+def test_delta_v_and_kv_cache_update_match_the_oracle(cuda_device, live):
+    """dyllm_delta_v_update and dyllm_kv_cache_update against the CPU restatement of the reference's Python
+    (layers/attention.py:67-74,89-96; models/llada.py:108-143): delta-V and both caches bit-exact, the
+    rotated keys within the rotary embedding's rounding."""
+    from oracle import dyllm_oracle as orc
+
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(11 + live)
+    B, L, Hkv, D, cap = 3, 80, 2, 128, 64
+    dev = cuda_device
+    cu = (torch.arange(B + 1) * L).to(torch.int32)
+    seq_ids = torch.tensor([1, 2, 0])
+    k_starts = torch.tensor([2 * L + 4, 0, L])           # per sequence id
+    v_starts = torch.tensor([0, L + 7, 2 * L + 7])
+    k_cache = torch.randn(3 * L + 16, Hkv * D, generator=g).bfloat16()
+    v_cache = torch.randn(3 * L + 16, Hkv * D, generator=g).bfloat16()
+    rows_k = torch.sort(torch.randperm(B * L, generator=g)[:cap]).values
+    positions = (torch.arange(B * L) % L)
+    k_new = torch.randn(cap, Hkv, D, generator=g).bfloat16()
+    v_new = torch.randn(cap, Hkv, D, generator=g).bfloat16()
+    theta, max_pos = 500000.0, 256
+    t = torch.arange(max_pos, dtype=torch.float)
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float) / D))
+    f = torch.einsum("i,j->ij", t, inv)
+    cos_sin = torch.cat((f.cos(), f.sin()), dim=-1)
+    n_dev = torch.tensor([live], dtype=torch.int32, device=dev)
+
+    # oracle on the live rows
+    b_of = torch.div(rows_k[:live], L, rounding_mode="floor")
+    k_rows = k_starts[seq_ids[b_of]] + rows_k[:live] - b_of * L
+    v_rows = v_starts[seq_ids[b_of]] + rows_k[:live] - b_of * L
+    k_want, v_want = k_cache.clone(), v_cache.clone()
+    dv_want = orc.kv_cache_update(k_new[:live], v_new[:live], rows_k[:live], positions[rows_k[:live]], k_want, v_want,
+                                  k_rows, v_rows, D, theta, max_pos)
+
+    d = lambda x: x.to(dev)
+    k_got, v_got = d(k_cache.clone()), d(v_cache.clone())
+    dv_got = torch.zeros(cap, Hkv, D, dtype=torch.bfloat16, device=dev)
+    ops.kv_cache_update(d(k_new), d(v_new), d(rows_k), d(positions), d(rows_k), d(cos_sin), d(cu), d(k_starts),
+                        d(v_starts), d(seq_ids), k_got, v_got, n_dev, dv=dv_got)
+    assert torch.equal(dv_got[:live].cpu().flatten(1), dv_want)
+    assert bool((dv_got[live:] == 0).all())
+    assert torch.equal(v_got.cpu(), v_want)
+    torch.testing.assert_close(k_got.cpu().float(), k_want.float(), rtol=8e-3, atol=1e-3)
+    untouched = torch.ones(k_cache.size(0), dtype=torch.bool)
+    untouched[k_rows] = False
+    assert torch.equal(k_got.cpu()[untouched], k_cache[untouched])
+
+    # the stand-alone delta-V entry point
+    v_got2 = d(v_cache.clone())
+    dv2 = ops.delta_v_update(d(v_new).view(cap, -1), v_got2, d(v_rows.to(torch.int32)) if live == cap else
+                             d(torch.cat([v_rows, torch.zeros(cap - live, dtype=torch.long)]).to(torch.int32)), None, n_dev)
+    assert torch.equal(dv2[:live].cpu(), dv_want) and torch.equal(v_got2.cpu(), v_want)

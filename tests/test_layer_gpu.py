@@ -1,7 +1,13 @@
 """Layer-level parity: this package's LLaDADecoderLayer (bf16, sm_100a kernels) against outputs of the
-reference's own LLaDADecoderLayer run on the CPU in fp32 (fixture tests/golden/llada_layer_small.pt,
-made by tests/golden/make_golden.py): a dense step, a full-sequence sparse step and a response-only
-sparse step on the same layer state."""
+reference's own LLaDADecoderLayer run on the CPU with bf16 modules (fixtures tests/golden/llada_layer_small.pt
+and llada_layer_c1.pt, made by tests/golden/make_golden.py): a dense step, a full-sequence sparse step and
+a response-only sparse step on the same layer state.  "c1" is the single-layer LLaDA-8B configuration
+(hidden 4096, 32 heads, FFN intermediate 12288, 256 prompt + 256 response positions).
+
+The generator keeps every reference cosine at least 1e-4 from the threshold.  Upstream of the statistics the
+two pipelines round differently (bf16 GEMMs with different accumulation orders), which moves a cosine by up
+to ~1e-3, so the decisions are required to agree on every row whose reference cosine is at least BAND from
+the threshold; the kernel-level tests, which feed identical inputs, use the 1e-4 band itself."""
 import os
 import sys
 
@@ -13,8 +19,13 @@ pytestmark = pytest.mark.gpu
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
 
 
-def _run_layer(dev):
+BAND = 2e-3
+
+
+def _run_layer(dev, config):
     import make_golden as mg
+
+    mg.use_config(config)
     from dyllm_b200.context import get_context, get_metadata, set_context, set_metadata
     from dyllm_b200.model import LLaDADecoderLayer, LLaDAShape
 
@@ -32,7 +43,7 @@ def _run_layer(dev):
         layer.mlp.down_proj.weight.copy_(w["down_proj"])
     B, P, R = mg.BATCH, mg.PROMPT, mg.RESP
     L = P + R
-    seq_ids = [5, 3]
+    seq_ids = mg.CONFIGS[config]["seq_ids"]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
     results = []
     for step in range(3):
@@ -74,21 +85,20 @@ def _run_layer(dev):
     return results
 
 
-def test_decoder_layer_matches_reference_fixture(cuda_device):
+@pytest.mark.parametrize("config", ["small", "c1"])
+def test_decoder_layer_matches_reference_fixture(cuda_device, config):
     from dyllm_b200 import _lib
 
-    fx = torch.load(os.path.join(os.path.dirname(__file__), "golden", "llada_layer_small.pt"))
-    got = _run_layer(cuda_device)
+    fx = torch.load(os.path.join(os.path.dirname(__file__), "golden", f"llada_layer_{config}.pt"))
+    got = _run_layer(cuda_device, config)
     assert _lib.load().dyllm_device_status() == 0
     tau = fx["tau"]
     for step, (g, want) in enumerate(zip(got, fx["steps"])):
-        rows = want["out"].size(0)
+        rows = g["out"].size(0)
         clear = torch.ones(rows, dtype=torch.bool)
         if step > 0:
-            # decisions are compared where the reference's cosine is clear of the threshold; the bf16
-            # pipeline and the fp32 reference may disagree inside the band
-            clear = (want["cosine"] - tau).abs() >= 2e-3
-            assert clear.float().mean() >= 0.8
+            clear = (want["cosine"] - tau).abs() >= BAND
+            assert clear.float().mean() >= (0.95 if config == "c1" else 0.8)
             ref_mask = torch.zeros(rows, dtype=torch.bool)
             ref_mask[want["idx_salient_row"]] = True
             got_mask = torch.zeros(rows, dtype=torch.bool)
@@ -100,18 +110,27 @@ def test_decoder_layer_matches_reference_fixture(cuda_device):
                 # K-space list: row r of sequence b maps to r + prompt * (b + 1)
                 b_of = torch.div(g["idx"], fx["resp"], rounding_mode="floor")
                 assert torch.equal(g["idx_k"], g["idx"] + fx["prompt"] * (b_of + 1))
-            same = got_mask == ref_mask
-            clear = clear & same
-        rd_all = g["residual"] - want["residual"]
-        od_all = g["out"] - want["out"]
-        print(f"step {step}: residual rel {(rd_all.norm() / want['residual'].norm()).item():.4g} "
-              f"worst rows {rd_all.norm(dim=1).topk(5).indices.tolist()} "
-              f"out rel(all) {(od_all.norm() / want['out'].norm()).item():.4g} "
-              f"worst rows {od_all.norm(dim=1).topk(5).indices.tolist()} clear {int(clear.sum())}/{rows}")
-        diff = (g["out"] - want["out"])[clear]
-        ref = want["out"][clear]
-        scale = max(1.0, ref.abs().max().item())
-        assert diff.abs().max().item() / scale <= 2e-2, f"step {step}: max-abs {diff.abs().max().item()}"
-        assert (diff.norm() / ref.norm()).item() <= 1e-2, f"step {step}: rel-L2 {(diff.norm() / ref.norm()).item()}"
-        rdiff = g["residual"] - want["residual"]
-        assert (rdiff.norm() / want["residual"].norm()).item() <= 1e-2
+            # rows whose decision differs inside the band went through (or skipped) the FFN: not comparable
+            clear = clear & (got_mask == ref_mask)
+        if "out" in want:
+            pairs = [("out", g["out"][clear], want["out"][clear]), ("residual", g["residual"], want["residual"])]
+        else:
+            # compact fixture: a subset of rows in full, per-row sums and norms of every row
+            sub = want["rows"]
+            keep = clear[sub]
+            pairs = [("out", g["out"][sub][keep], want["out_rows"].float()[keep]),
+                     ("residual", g["residual"][sub], want["residual_rows"].float())]
+            for name in ("out", "residual"):
+                sel = clear if name == "out" else torch.ones(rows, dtype=torch.bool)
+                norm_got, norm_want = g[name].norm(dim=1)[sel], want[name + "_norm"][sel]
+                assert torch.allclose(norm_got, norm_want, rtol=1e-2, atol=1e-3), f"step {step}: {name} row norms"
+                sum_err = (g[name].sum(1)[sel] - want[name + "_sum"][sel]).abs()
+                assert bool((sum_err <= 2e-2 * want[name + "_norm"][sel] * g[name].size(1) ** 0.5 + 1e-2).all()), \
+                    f"step {step}: {name} row sums"
+        for name, a, b in pairs:
+            diff = a - b
+            scale = max(1.0, b.abs().max().item())
+            rel = (diff.norm() / b.norm()).item()
+            print(f"{config} step {step} {name}: max-abs {diff.abs().max().item():.4g} (peak {scale:.3g}) rel-L2 {rel:.4g}")
+            assert diff.abs().max().item() / scale <= 2e-2, f"step {step} {name}: max-abs {diff.abs().max().item()}"
+            assert rel <= 1e-2, f"step {step} {name}: rel-L2 {rel}"

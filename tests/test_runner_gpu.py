@@ -92,3 +92,95 @@ def test_segmented_capture_cuts_graphs_at_collectives(cuda_device, tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     res = subprocess.run([sys.executable, str(script), str(port)], cwd=root, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "segments ok" in res.stdout, res.stdout + res.stderr
+
+
+def test_token_ids_follow_the_reference_step_loop(cuda_device):
+    """Token ids over a fixed step count against the reference's own step loop (fixture
+    tests/golden/llada_tokens_small.pt from tests/golden/make_token_golden.py: the reference's ModelRunner
+    preparation, LLaDAForDLM and sampler on the CPU).  Every step is compared and then the recorded choice is
+    applied, so one rounding-dependent choice cannot derail the steps after it.  A step's choice must be
+    identical whenever the reference's own choice was clear: the chosen row's best token at least 3 % more
+    probable than its runner-up and the chosen row's confidence at least 3 % above the best rejected row's
+    (the reference ranks bf16 probabilities, which are only resolved to ~0.4 %)."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    import make_token_golden as mtg
+    from dyllm_b200 import _lib, runner
+    from dyllm_b200.model import LLaDAForDLM, LLaDAShape
+
+    fx = torch.load(os.path.join(os.path.dirname(__file__), "golden", "llada_tokens_small.pt"))
+    c = mtg.CFG
+    assert fx["cfg"] == c
+    shape = LLaDAShape(hidden_size=c["hidden"], num_attention_heads=c["heads"], n_kv_heads=c["kv_heads"],
+                       head_dim=c["head_dim"], mlp_hidden_size=c["inter"], num_hidden_layers=c["layers"],
+                       vocab_size=c["vocab"], mask_token_id=mtg.MASK_ID, max_sequence_length=c["max_pos"],
+                       rms_norm_eps=c["eps"], rope_theta=c["theta"])
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(cuda_device):
+            model = LLaDAForDLM(shape, c["tau"])
+    finally:
+        torch.set_default_dtype(torch.float32)
+    mtg.load_weights_into(model, {k: v.to(cuda_device) for k, v in mtg.token_model_weights().items()})
+    model.eval()
+    sr = runner.StepRunner(model, mtg.MASK_ID, block_length=c["block"], steps=c["steps"], num_full_steps=c["full_steps"],
+                           refresh_period=4, use_graphs=False)
+    prompts = mtg.token_prompts()
+    seqs = sr.new_batch(prompts, c["gen"])
+    compared = agreed_anyway = 0
+    for step, rec in enumerate(fx["steps"]):
+        picks = sr.step_picks(seqs, forced=rec["picks"])
+        for b, (got, want, (sel_margin, tok_margin)) in enumerate(zip(picks, rec["picks"], rec["margins"])):
+            if sel_margin >= 0.03 and tok_margin >= 0.03:
+                compared += 1
+                assert got == want, f"step {step + 1} ({rec['kind']}) sequence {b}: {got} != {want}"
+            else:
+                agreed_anyway += got == want
+    total = len(fx["steps"]) * len(prompts)
+    print(f"clear choices compared: {compared}/{total}; unclear ones that agreed anyway: {agreed_anyway}/{total - compared}")
+    assert compared >= total // 3
+    assert [s.token_ids[s.num_prompt_tokens:] for s in seqs] == fx["final_tokens"]
+    assert _lib.load().dyllm_device_status() == 0
+    # free-running generations (host-driven and device-resident) for the record
+    for device_state in (False, True):
+        free = sr.generate(prompts, c["gen"], device_state=device_state)
+        same = sum(a == b for row, ref in zip(free, fx["final_tokens"]) for a, b in zip(row, ref))
+        print(f"free-running (device_state={device_state}): {same}/{total} final tokens equal the reference's")
+
+
+def test_two_batch_geometries_on_one_model(cuda_device):
+    """A second generation with another batch size and other lengths on the same model: the caches forget
+    the first batch (sequence ids are reused) and captured graphs of the first geometry are dropped."""
+    from dyllm_b200 import _lib, runner
+    from dyllm_b200.model import LLaDAForDLM, LLaDAShape, init_weights_
+
+    shape = LLaDAShape(hidden_size=256, num_attention_heads=2, n_kv_heads=2, head_dim=128, mlp_hidden_size=512,
+                       num_hidden_layers=2, vocab_size=1024, mask_token_id=1000, max_sequence_length=256)
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(cuda_device):
+            model = LLaDAForDLM(shape, 0.99)
+    finally:
+        torch.set_default_dtype(torch.float32)
+    init_weights_(model, seed=5, std=0.05)
+    model.eval()
+    g = torch.Generator().manual_seed(1)
+    small = torch.randint(0, 900, (2, 24), generator=g).tolist()
+    large = torch.randint(0, 900, (5, 56), generator=g).tolist()
+
+    def fresh():
+        return runner.StepRunner(model, shape.mask_token_id, block_length=8, steps=16, num_full_steps=4, refresh_period=4,
+                                 use_graphs=True)
+
+    sr = fresh()
+    want_small = sr.generate(small, 16)
+    want_large = fresh().generate(large, 16)          # another runner of the same model, another geometry
+    assert sr.generate(small, 16) == want_small       # the first runner notices that its graphs are stale
+    sr3 = fresh()
+    assert sr3.generate(small, 16) == want_small
+    assert sr3.generate(small, 16) == want_small      # replay of the captured graphs
+    assert sr3.generate(large, 16) == want_large      # longer sequences, more of them, same ids
+    assert sr3.generate(small, 16) == want_small      # and back
+    assert _lib.load().dyllm_device_status() == 0
