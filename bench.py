@@ -350,16 +350,25 @@ def run_ours(args, cfg, tau):
     _lib.load()
     B, P, GEN = cfg["batch"], cfg["prompt"], cfg["gen"]
     comm, exchange = None, "none"
+    layout = args.layout if args.layout != "auto" else ("sequence" if world > 1 and B % world == 0 else "tensor")
     if world > 1:
         exchange = "nccl"
+        if layout == "sequence" and args.tp_exchange != "peer":
+            raise SystemExit("--layout sequence needs --tp-exchange peer")
         if args.tp_exchange == "peer":
             from dyllm_b200.tp_comm import TpComm
 
             hidden = layer_shape(cfg)[0]
-            slot_rows = min(B * (P + GEN), 32768)
+            if layout == "sequence":
+                slot_rows = max((B // world) * (P + GEN), 1024)
+                exchange = ("peer-memory stores over NVLink: salient rows gathered to every rank, partial FFN outputs "
+                            "returned to the rows' owners; no other collective in a step")
+            else:
+                slot_rows = min(B * (P + GEN), 32768)
+                exchange = "peer-memory stores over NVLink (statistics, FFN rows) + NCCL (o_proj)"
             comm = TpComm.from_process_group(dev, slot_bytes=slot_rows * hidden * 2)
             layers.set_tp_comm(comm)
-            exchange = "peer-memory stores over NVLink (statistics, FFN rows) + NCCL (o_proj)"
+        layers.set_layout(layout)
 
     tp_parity = None
     if world > 1 and not args.no_tp_parity:
@@ -487,6 +496,12 @@ def run_ours(args, cfg, tau):
                "stage_seconds_per_layer_step": stages}
     cfg_d = config_dict(cfg, tau, world, args)
     cfg_d["tp_exchange"] = exchange
+    if world > 1:
+        cfg_d["layout"] = layout
+        if layout == "sequence":
+            cfg_d["parallelism"] = (f"{world} ranks: sequences of the batch sharded for attention and the all-row work "
+                                    f"(replicated attention weights), FFN weights tensor-parallel tp{world}"
+                                    + (f" / experts ep{world}" if args.ep else ""))
     line = {
         "metric": metric_name(cfg, tau), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -518,6 +533,10 @@ def main():
     ap.add_argument("--ep", action="store_true", help="config 4: whole experts per rank (expert parallelism)")
     ap.add_argument("--tp-exchange", default="peer", choices=["peer", "nccl"],
                     help="carrier of the small per-layer all-reduces under tensor parallelism")
+    ap.add_argument("--layout", default="auto", choices=["auto", "tensor", "sequence"],
+                    help="several GPUs: 'tensor' = the reference's layout (heads and FFN columns sharded, rows replicated, "
+                         "three all-reduces per layer); 'sequence' = every rank owns whole sequences, only the FFN weights "
+                         "are sharded and only salient rows travel (auto: sequence when the batch divides evenly)")
     ap.add_argument("--no-tp-parity", action="store_true", help="skip the sharded-vs-unsharded layer self-check")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers marks the line invalid")
     ap.add_argument("--denoise-steps", type=int, default=0, help="debug only")

@@ -63,6 +63,11 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_tp_push_rows": (I, [P, P, I, I, P, I, P]),
     "dyllm_tp_reduce_rows": (I, [P, I, I, P, I, P, c_int64, P, P]),
     "dyllm_tp_allreduce_rows": (I, [P, P, I, I, P, I, P, c_int64, P, P]),
+    "dyllm_tp_gather_rows": (I, [P, P, I, I, c_int64, P, I, P, P, P, P, P]),
+    "dyllm_tp_gather_push": (I, [P, P, I, I, c_int64, P, I, P, P]),
+    "dyllm_tp_gather_finish": (I, [P, I, P, P, P, P]),
+    "dyllm_tp_comm_data": (P, [P]),
+    "dyllm_tp_scatter_push": (I, [P, P, I, I, P, P]),
     "dyllm_tp_push_f32": (I, [P, P, I, P]),
     "dyllm_tp_reduce_f32": (I, [P, P, I, P]),
     "dyllm_tp_allreduce_f32": (I, [P, P, I, P]),
@@ -77,7 +82,8 @@ KERNELS_PER_CALL = {
     "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 2, "dyllm_delta_v_update": 1,
     "dyllm_add_rms_norm": 1, "dyllm_add_rms_norm_segmented": 1, "dyllm_rope_neox": 1, "dyllm_row_confidence": 1, "dyllm_kv_cache_update": 1,
     "dyllm_tp_push_rows": 1, "dyllm_tp_reduce_rows": 1, "dyllm_tp_allreduce_rows": 2, "dyllm_tp_push_f32": 1,
-    "dyllm_tp_reduce_f32": 1, "dyllm_tp_allreduce_f32": 2,
+    "dyllm_tp_reduce_f32": 1, "dyllm_tp_allreduce_f32": 2, "dyllm_tp_gather_rows": 2, "dyllm_tp_gather_push": 1,
+    "dyllm_tp_gather_finish": 1, "dyllm_tp_scatter_push": 1,
 }
 launch_count = 0
 

@@ -18,10 +18,20 @@
 //   [0]     uint32 epoch        number of completed exchanges (local use only)
 //   [4]     uint32 push ticket  [8] uint32 reduce ticket
 //   [64]    uint32 flags[2][8]  flags[parity][source rank] = epoch + 1 of the exchange whose data is complete
+//   [128]   int32 counts[2][8]  rows the source rank contributed (row gathers only)
 //   [1024]  data[2][world][slot]
 // Exchange e uses the buffers of parity e & 1.  A rank can start pushing exchange e + 2 (same parity) only
 // after it has finished reducing e + 1, for which every rank had to push e + 1, which each of them does
 // after it finished reducing e: so nobody still reads the buffer that is being overwritten.
+//
+// Sequence-sharded layout (every rank runs attention and the all-row projections for its own sequences, the
+// FFN weights are sharded over the ranks): two more exchanges built from the same pieces.
+//   gather   every rank stores its salient (normed) rows and their count into its slot of every region; a
+//            one-block kernel then waits for the flags and writes the list of all gathered rows in rank order
+//            (as row numbers of the data area, so that the gathered GEMM reads them in place), the per-rank
+//            prefix counts and the total;
+//   scatter  every rank stores each partial FFN output row into its slot of the OWNER's region only; the
+//            owner adds the slots in rank order (the reduce kernel above) and scatters into its cache.
 #include <cstring>
 
 #include "common.cuh"
@@ -32,6 +42,7 @@ namespace {
 constexpr int kTpMaxWorld = 8;
 constexpr size_t kTpHeaderBytes = 1024;
 constexpr size_t kTpFlagsOffset = 64;
+constexpr size_t kTpCountsOffset = 128;
 constexpr int kTpThreads = 256;
 constexpr int kTpStatusBase = 0x7E00;   // device status code of a flag wait that ran out: base + source rank
 
@@ -193,6 +204,124 @@ tp_reduce_rows_kernel(unsigned char* local, int world, size_t slot_bytes, int ro
     }
   }
   finish_exchange(local, epoch);
+}
+
+// Gather push: row m of the local list (x[idx[m]], idx null = identity) goes to slot `rank` of every region,
+// together with the number of rows.
+__global__ void __launch_bounds__(kTpThreads)
+tp_gather_push_kernel(unsigned char* const* __restrict__ peers, int rank, int world, size_t slot_bytes,
+                      const uint4* __restrict__ x, int64_t ldx_vecs, const int32_t* __restrict__ idx, int x_rows,
+                      int row_vecs, int max_rows, const int32_t* __restrict__ count_dev) {
+  unsigned char* local = peers[rank];
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
+  const uint32_t parity = epoch & 1u;
+  const int rows = live_rows(count_dev, 0, max_rows);
+  const int64_t total = static_cast<int64_t>(rows) * row_vecs;
+  const size_t off = data_offset(parity, world, rank, slot_bytes);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / row_vecs);
+    const int c = static_cast<int>(i - static_cast<int64_t>(m) * row_vecs);
+    int r = idx ? idx[m] : m;
+    r = r < 0 ? 0 : (r >= x_rows ? x_rows - 1 : r);
+    const uint4 v = x[static_cast<int64_t>(r) * ldx_vecs + c];
+#pragma unroll 1
+    for (int k = 0; k < world; ++k) {
+      int p = rank + 1 + k;
+      p = p >= world ? p - world : p;
+      reinterpret_cast<uint4*>(peers[p] + off)[i] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t* ticket = reinterpret_cast<uint32_t*>(local + 4);
+    const uint32_t t = atomicAdd(ticket, 1u);
+    if (t == gridDim.x - 1) {
+      *ticket = 0;
+      for (int p = 0; p < world; ++p)
+        reinterpret_cast<volatile int32_t*>(peers[p] + kTpCountsOffset)[parity * kTpMaxWorld + rank] = rows;
+      __threadfence_system();
+      for (int p = 0; p < world; ++p)
+        st_release_sys(reinterpret_cast<uint32_t*>(peers[p] + kTpFlagsOffset) + parity * kTpMaxWorld + rank, epoch + 1u);
+    }
+  }
+}
+
+// One block: waits for every rank's rows, then writes prefix[0..world] (rows of the ranks before r), the total
+// and, for every gathered row in rank order, its row number inside the data area (both parities form one
+// [2 * world * slot_rows, width] matrix that starts right after the header).
+__global__ void __launch_bounds__(kTpThreads)
+tp_gather_finish_kernel(unsigned char* local, int world, size_t slot_bytes, int slot_rows, int32_t* __restrict__ idx_all,
+                        int32_t* __restrict__ prefix, int32_t* __restrict__ total_out, unsigned long long wait_ns,
+                        int* status_word) {
+  __shared__ int pre[kTpMaxWorld + 1];
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
+  const uint32_t parity = epoch & 1u;
+  const bool ok = wait_flags(local, parity, epoch + 1u, world, wait_ns, status_word);
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int r = 0; r < world; ++r) {
+      pre[r] = acc;
+      int c = ok ? reinterpret_cast<volatile int32_t*>(local + kTpCountsOffset)[parity * kTpMaxWorld + r] : 0;
+      c = c < 0 ? 0 : (c > slot_rows ? slot_rows : c);
+      acc += c;
+    }
+    pre[world] = acc;
+    for (int r = 0; r <= world; ++r)
+      prefix[r] = pre[r];
+    *total_out = acc;
+  }
+  __syncthreads();
+  for (int r = 0; r < world; ++r) {
+    const int n = pre[r + 1] - pre[r];
+    const int base = (static_cast<int>(parity) * world + r) * slot_rows;
+    for (int j = threadIdx.x; j < n; j += blockDim.x)
+      idx_all[pre[r] + j] = base + j;
+  }
+  finish_exchange(local, epoch);
+}
+
+// Scatter push: row m of y (a row of rank r = the rank whose prefix range holds m) goes to slot `rank` of
+// rank r's region, at its position inside r's own list.
+__global__ void __launch_bounds__(kTpThreads)
+tp_scatter_push_kernel(unsigned char* const* __restrict__ peers, int rank, int world, size_t slot_bytes,
+                       const uint4* __restrict__ y, int row_vecs, int max_rows, const int32_t* __restrict__ prefix) {
+  unsigned char* local = peers[rank];
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
+  const uint32_t parity = epoch & 1u;
+  __shared__ int pre[kTpMaxWorld + 1];
+  if (threadIdx.x <= world)
+    pre[threadIdx.x] = prefix[threadIdx.x];
+  __syncthreads();
+  int rows = pre[world];
+  rows = rows > max_rows ? max_rows : rows;
+  const int64_t total = static_cast<int64_t>(rows) * row_vecs;
+  const size_t off = data_offset(parity, world, rank, slot_bytes);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / row_vecs);
+    const int c = static_cast<int>(i - static_cast<int64_t>(m) * row_vecs);
+    int owner = 0;
+    while (owner + 1 < world && pre[owner + 1] <= m)
+      ++owner;
+    const int64_t j = static_cast<int64_t>(m - pre[owner]) * row_vecs + c;
+    reinterpret_cast<uint4*>(peers[owner] + off)[j] = y[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    uint32_t* ticket = reinterpret_cast<uint32_t*>(local + 4);
+    const uint32_t t = atomicAdd(ticket, 1u);
+    if (t == gridDim.x - 1) {
+      *ticket = 0;
+      __threadfence_system();
+      for (int p = 0; p < world; ++p)
+        st_release_sys(reinterpret_cast<uint32_t*>(peers[p] + kTpFlagsOffset) + parity * kTpMaxWorld + rank, epoch + 1u);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kTpThreads)
@@ -372,6 +501,75 @@ int dyllm_tp_allreduce_rows(void* comm, const void* src, int width, int max_rows
   if (rc != DYLLM_OK)
     return rc;
   return dyllm_tp_reduce_rows(comm, width, max_rows, count_dev, row_offset, out, ldo, out_row_map, stream);
+}
+
+int dyllm_tp_gather_rows(void* comm, const void* x, int x_rows, int width, int64_t ldx, const int32_t* idx,
+                         int max_rows, const int32_t* count_dev, int32_t* idx_all, int32_t* prefix,
+                         int32_t* total_out, void* stream) {
+  DYLLM_REQUIRE(comm && x && idx_all && prefix && total_out, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_rows: null pointer");
+  TpComm* c = as_comm(comm);
+  DYLLM_REQUIRE(width > 0 && width % 8 == 0 && ldx % 8 == 0 && ldx >= width && max_rows >= 0 && x_rows > 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_rows: width %d ldx %lld max_rows %d x_rows %d", width,
+                static_cast<long long>(ldx), max_rows, x_rows);
+  const size_t row_bytes = static_cast<size_t>(width) * 2;
+  DYLLM_REQUIRE(c->slot_bytes % row_bytes == 0, DYLLM_ERR_INVALID_ARGUMENT,
+                "tp_gather_rows: the slot of %zu bytes is not a whole number of %zu-byte rows", c->slot_bytes, row_bytes);
+  DYLLM_REQUIRE(static_cast<size_t>(max_rows) * row_bytes <= c->slot_bytes, DYLLM_ERR_WORKSPACE,
+                "tp_gather_rows: %d rows of %d bf16 exceed the slot of %zu bytes", max_rows, width, c->slot_bytes);
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_rows: x must be 16-byte aligned");
+  const int row_vecs = width / 8;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  tp_gather_push_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, st>>>(
+      c->peers_dev, c->rank, c->world, c->slot_bytes, static_cast<const uint4*>(x), ldx / 8, idx, x_rows, row_vecs,
+      max_rows, count_dev);
+  int rc = check_launch("tp_gather_push");
+  if (rc != DYLLM_OK)
+    return rc;
+  tp_gather_finish_kernel<<<1, kTpThreads, 0, st>>>(c->local, c->world, c->slot_bytes,
+                                                   static_cast<int>(c->slot_bytes / row_bytes), idx_all, prefix,
+                                                   total_out, c->wait_ns, device_status_word());
+  return check_launch("tp_gather_finish");
+}
+
+int dyllm_tp_gather_push(void* comm, const void* x, int x_rows, int width, int64_t ldx, const int32_t* idx,
+                         int max_rows, const int32_t* count_dev, void* stream) {
+  DYLLM_REQUIRE(comm && x, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_push: null pointer");
+  TpComm* c = as_comm(comm);
+  DYLLM_REQUIRE(width > 0 && width % 8 == 0 && ldx % 8 == 0 && ldx >= width && max_rows >= 0 && x_rows > 0 &&
+                    static_cast<size_t>(max_rows) * width * 2 <= c->slot_bytes,
+                DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_push: bad shape");
+  const int row_vecs = width / 8;
+  tp_gather_push_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0,
+                          static_cast<cudaStream_t>(stream)>>>(c->peers_dev, c->rank, c->world, c->slot_bytes,
+                                                                static_cast<const uint4*>(x), ldx / 8, idx, x_rows,
+                                                                row_vecs, max_rows, count_dev);
+  return check_launch("tp_gather_push");
+}
+
+int dyllm_tp_gather_finish(void* comm, int width, int32_t* idx_all, int32_t* prefix, int32_t* total_out, void* stream) {
+  DYLLM_REQUIRE(comm && idx_all && prefix && total_out && width > 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_finish: bad argument");
+  TpComm* c = as_comm(comm);
+  const size_t row_bytes = static_cast<size_t>(width) * 2;
+  DYLLM_REQUIRE(c->slot_bytes % row_bytes == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_finish: slot is not a whole number of rows");
+  tp_gather_finish_kernel<<<1, kTpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      c->local, c->world, c->slot_bytes, static_cast<int>(c->slot_bytes / row_bytes), idx_all, prefix, total_out,
+      c->wait_ns, device_status_word());
+  return check_launch("tp_gather_finish");
+}
+
+void* dyllm_tp_comm_data(void* comm) { return comm ? as_comm(comm)->local + kTpHeaderBytes : nullptr; }
+
+int dyllm_tp_scatter_push(void* comm, const void* y, int width, int max_rows, const int32_t* prefix, void* stream) {
+  DYLLM_REQUIRE(comm && y && prefix, DYLLM_ERR_INVALID_ARGUMENT, "tp_scatter_push: null pointer");
+  TpComm* c = as_comm(comm);
+  DYLLM_REQUIRE(width > 0 && width % 8 == 0 && max_rows >= 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_scatter_push: width %d max_rows %d",
+                width, max_rows);
+  DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(y) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_scatter_push: y must be 16-byte aligned");
+  const int row_vecs = width / 8;
+  tp_scatter_push_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0,
+                           static_cast<cudaStream_t>(stream)>>>(c->peers_dev, c->rank, c->world, c->slot_bytes,
+                                                                 static_cast<const uint4*>(y), row_vecs, max_rows, prefix);
+  return check_launch("tp_scatter_push");
 }
 
 int dyllm_tp_push_f32(void* comm, const float* src, int n, void* stream) {

@@ -9,6 +9,8 @@ Projections that run on every row (q_proj, o_proj, lm_head) stay ``F.linear``.
 
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -23,12 +25,61 @@ from .context import get_context, get_metadata
 # --------------------------------------------------------------------------------------------------
 # distributed helpers (ref: dyllm/distributed/parallel_state.py)
 # --------------------------------------------------------------------------------------------------
+_replicated_depth = 0     # > 0 while modules are being built (or run) as if there were a single rank
+
+
 def _world_size() -> int:
+    if _replicated_depth:
+        return 1
     return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
 
 
 def _rank() -> int:
+    if _replicated_depth:
+        return 0
     return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+@contextlib.contextmanager
+def replicated():
+    """Modules built inside this scope are unsharded: every rank holds their complete weights."""
+    global _replicated_depth
+    _replicated_depth += 1
+    try:
+        yield
+    finally:
+        _replicated_depth -= 1
+
+
+# How the work of a step is spread over the ranks.
+#   "tensor"    the reference's layout (dyllm/model_executor/layers/linear.py): every rank sees every row;
+#               attention heads and FFN columns are sharded; three all-reduces per sparse layer.
+#   "sequence"  every rank owns whole sequences of the batch and runs the all-row work (projections, norms,
+#               attention, statistics, selection, caches) for them alone with replicated attention weights;
+#               only the FFN / expert weights are sharded, and only the salient rows travel: they are
+#               gathered from all ranks, pushed through the sharded FFN, and the partial outputs go back to
+#               the rows' owners.  No [T_q, hidden] all-reduce and no statistics all-reduce exist.
+_layout = "tensor"
+
+
+def set_layout(name: str) -> None:
+    global _layout
+    if name not in ("tensor", "sequence"):
+        raise ValueError(f"unknown layout {name!r}")
+    _layout = name
+
+
+def get_layout() -> str:
+    return _layout
+
+
+def attention_scope():
+    """Scope in which a model builds its attention block: unsharded under the sequence layout."""
+    return replicated() if _layout == "sequence" else contextlib.nullcontext()
+
+
+def sequence_sharded() -> bool:
+    return _layout == "sequence" and _world_size() > 1
 
 
 # A step driver that captures the launches of a step into CUDA graphs installs a hook here: every SUM
@@ -98,6 +149,24 @@ def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.
     if _world_size() > 1:
         all_reduce_stats(stats)
     return ops.cosine_mask(stats, threshold)      # raises unless the statistics are fp32 [rows, 3] on a GPU
+
+
+def _gathered_ffn(ffn_shard, x: torch.Tensor, idx32, cap_local: int, count_dev, hint: int, out=None, out_row_map=None):
+    """FFN of the sequence-sharded layout: the rows ``x[idx32[:count]]`` of every rank are gathered on all ranks
+    (peer-memory stores), ``ffn_shard(matrix, idx_all, capacity, total_dev, hint)`` runs this rank's weight shard
+    over all of them, and each partial output row returns to the rank that owns the row, which adds the ranks'
+    partials in rank order and writes the sums to ``out[map[m]]`` (default: a packed ``[cap_local, hidden]``
+    tensor, which is returned)."""
+    comm = get_tp_comm()
+    if comm is None:
+        raise RuntimeError("the sequence-sharded layout needs the peer-memory exchange (layers.set_tp_comm)")
+    mat, idx_all, prefix, total = comm.gather_rows(x, idx32, count_dev, cap_local)
+    cap_total = idx_all.numel()
+    y = ffn_shard(mat, idx_all, cap_total, total, hint * comm.world if hint else 0)
+    if out is None:
+        out = torch.empty((cap_local, x.size(1)), dtype=x.dtype, device=x.device)
+    comm.scatter_reduce_rows(y, prefix, cap_total, count_dev, cap_local, out, out_row_map)
+    return out
 
 
 def divide(numerator: int, denominator: int) -> int:
@@ -318,10 +387,16 @@ class LLaDAMLP(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Reference calling convention: ``x`` holds the rows to process (all rows of a dense step, the
         gathered salient rows of a sparse step)."""
+        if sequence_sharded():
+            return self.cache_update(_gathered_ffn(self._ffn_shard, x, None, x.size(0), None, 0))
         y = ops.swiglu_ffn(x, self.gate_up_proj.weight, self.down_proj.weight)
         if self.down_proj.tp_size > 1:
             all_reduce_sum(y)
         return self.cache_update(y)
+
+    def _ffn_shard(self, mat, idx_all, cap_total, total_dev, hint):
+        return ops.swiglu_ffn(mat, self.gate_up_proj.weight, self.down_proj.weight, idx_all, num_rows=cap_total,
+                              num_rows_dev=total_dev, rows_hint=hint)
 
     def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
         """Sparse step on the full ``[T_q, hidden]`` activation: the salient rows are read through the step's
@@ -338,7 +413,13 @@ class LLaDAMLP(nn.Module):
             width, inter = hidden.size(1), self.down_proj.weight.size(1)
             # algorithmic bytes: the three weight matrices (this rank's shards) once, the rows in and out
             nbytes = 3.0 * width * inter * 2 + 2.0 * rows * width * 2
-            if self.down_proj.tp_size > 1:
+            if sequence_sharded():
+                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
+                world = _world_size()
+                with profiling.region("swiglu_ffn", 6.0 * rows * world * width * inter, nbytes):
+                    _gathered_ffn(self._ffn_shard, hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache,
+                                  out_row_map=dest)
+            elif self.down_proj.tp_size > 1:
                 with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
                     y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
                                        num_rows=cap, num_rows_dev=n_dev, rows_hint=hint)
@@ -420,6 +501,8 @@ class LLaDAMoESparseBlock(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Reference calling convention: ``x`` holds the rows to process."""
+        if sequence_sharded():
+            return self.cache_update(_gathered_ffn(self._experts, x, None, x.size(0), None, 0))
         y = self._experts(x, None, x.size(0), None, 0)
         if _world_size() > 1:
             all_reduce_sum(y)
@@ -434,7 +517,10 @@ class LLaDAMoESparseBlock(nn.Module):
         cm = self.cache_update.cache_manager
         if cap:
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
-            if _world_size() > 1:
+            if sequence_sharded():
+                dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
+                _gathered_ffn(self._experts, hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
+            elif _world_size() > 1:
                 y = self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint)
                 all_reduce_salient_rows(y, n_dev, cm, md.running_seqs_tensor, rows_k)
             else:
@@ -479,6 +565,7 @@ class Attention(nn.Module):
         self.scale = scale
         self.num_kv_heads = num_kv_heads
         self.threshold = threshold
+        self.tp_size = _world_size()        # 1 under the sequence-sharded layout: this rank's rows are complete
         self.context_cache = CacheManager(self.num_heads * self.head_dim)
         self.v_cache = CacheManager(self.num_kv_heads * self.head_dim)
         self._hint_host = None      # pinned int32[1]: this layer's salient count, copied back without waiting
@@ -560,7 +647,7 @@ class Attention(nn.Module):
 
         # 12 B/token all-reduce, then mask + ordered compaction (+ K-space offsets) in one launch; the new
         # lists stay on the device together with their length
-        if _world_size() > 1:
+        if self.tp_size > 1:
             all_reduce_stats(stats)
         with profiling.region("salient_select", 0.0, 12.0 * ctx.total_seqlen):
             sel = ops.salient_select(stats, self.threshold, ctx.cu_seqlens_q,

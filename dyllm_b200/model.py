@@ -19,7 +19,7 @@ from . import ops
 from .cache_manager import CacheManager
 from .context import get_context, get_metadata
 from .layers import (Attention, ColumnParallelLinear, KVParallelLinear, LLaDAMLP, LLaDAMoESparseBlock, RMSNorm,
-                     RotaryEmbedding, RowParallelLinear, _world_size)
+                     RotaryEmbedding, RowParallelLinear, _world_size, attention_scope)
 
 
 @dataclass
@@ -45,6 +45,12 @@ class LLaDAAttention(nn.Module):
                  rope_scaling: tuple | None = None, threshold: float = 0.99, rotary_emb: RotaryEmbedding | None = None,
                  qk_layernorm: bool = False):
         super().__init__()
+        with attention_scope():      # unsharded when every rank owns whole sequences
+            self._build(hidden_size, num_heads, num_kv_heads, max_position, head_dim, rms_norm_eps, qkv_bias,
+                        rope_theta, rope_scaling, threshold, rotary_emb, qk_layernorm)
+
+    def _build(self, hidden_size, num_heads, num_kv_heads, max_position, head_dim, rms_norm_eps, qkv_bias, rope_theta,
+               rope_scaling, threshold, rotary_emb, qk_layernorm):
         tp = _world_size()
         self.total_num_heads = num_heads
         self.num_heads = num_heads // tp

@@ -216,6 +216,9 @@ class StepRunner:
         self._warm: set = set()
         self._graph_pool = None
         self._geometry = 0          # the model's cache epoch this runner's graphs belong to
+        # host-driven steps keep the last step's candidate positions, confidences and tokens here when set
+        self.record_candidates = False
+        self.last_candidates = None
 
     def _set_geometry(self, key) -> None:
         """Called at the start of every generation with (sequence lengths, generation length).  Sequence ids
@@ -289,6 +292,16 @@ class StepRunner:
         With ``device_state`` (equal-length prompts, and steps * tokens-per-step == max_new_tokens) the token
         matrix, the step layouts and the list of positions unmasked in the previous step stay on the device:
         the prompts go up once, the generated ids come back once, and no step waits for the host."""
+        from . import layers
+
+        sharded = layers.sequence_sharded()
+        if sharded:
+            # every rank generates for its own slice of the batch; the results are gathered at the end
+            world, rank = dist.get_world_size(), dist.get_rank()
+            if len(prompts) % world:
+                raise RuntimeError(f"the sequence-sharded layout needs a batch ({len(prompts)}) divisible by the ranks ({world})")
+            per = len(prompts) // world
+            prompts = prompts[rank * per:(rank + 1) * per]
         lens = {len(p) for p in prompts}
         gen = max_new_tokens
         steps_per_block = max(1, self.steps * self.block_length // gen)
@@ -299,11 +312,16 @@ class StepRunner:
         exact = (gen % self.block_length == 0 and steps_per_block * num_transfer == self.block_length
                  and steps_per_block * (gen // self.block_length) == self.steps)
         if device_state and len(lens) == 1 and exact:
-            return self._generate_device(prompts, gen, steps_per_block, num_transfer)
+            return self._generate_device(prompts, gen, steps_per_block, num_transfer, sharded)
         seqs = self.new_batch(prompts, max_new_tokens)
         for _ in range(self.steps):
             self.step(seqs)
-        return [s.token_ids[s.num_prompt_tokens:] for s in seqs]
+        out = [s.token_ids[s.num_prompt_tokens:] for s in seqs]
+        if sharded:
+            parts = [None] * dist.get_world_size()
+            dist.all_gather_object(parts, out)
+            out = [row for part in parts for row in part]
+        return out
 
     def _device_state(self, B: int, P: int, gen: int, steps_per_block: int, num_transfer: int):
         """Buffers of the device-resident loop for one batch geometry.  They are allocated once and reused
@@ -418,7 +436,7 @@ class StepRunner:
         _lib.launch_count += entry[1]
 
     @torch.inference_mode()
-    def _generate_device(self, prompts, gen, steps_per_block, num_transfer):
+    def _generate_device(self, prompts, gen, steps_per_block, num_transfer, gather_ranks=False):
         B, P = len(prompts), len(prompts[0])
         st = self._device_state(B, P, gen, steps_per_block, num_transfer)
         prompt_t = torch.tensor(prompts, dtype=torch.int64)
@@ -438,7 +456,13 @@ class StepRunner:
             else:
                 kind = "sparse"
             self._run_step(st, kind)
-        out = st.tokens[:, P:].cpu()
+        out = st.tokens[:, P:].contiguous()
+        if gather_ranks:
+            world = dist.get_world_size()
+            full = torch.empty((world * B, gen), dtype=out.dtype, device=out.device)
+            dist.all_gather_into_tensor(full, out)
+            out = full
+        out = out.cpu()
         io_bytes["d2h"] += out.numel() * 8
         return out.tolist()
 
@@ -481,6 +505,8 @@ class StepRunner:
         io_bytes["h2d"] += still_masked.numel()
         still_masked = still_masked.to(self.device)
         conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
+        if self.record_candidates:
+            self.last_candidates = (cand_pos, conf.cpu(), tok.cpu())
         top_conf, top_i = conf.topk(num_transfer, dim=-1)
         picked = torch.stack([top_i, tok.gather(1, top_i), (top_conf >= 0).long()], dim=-1).cpu()  # one D2H per step
         io_bytes["d2h"] += picked.numel() * picked.element_size()

@@ -100,3 +100,51 @@ class TpComm:
         require_cuda(t, "t", torch.float32)
         call("dyllm_tp_allreduce_f32", self._comm, ptr(t), t.numel(), stream_ptr(t.device))
         return t
+
+    # ------------------------------------------------------------------ sequence-sharded layout
+    def data_matrix(self, width: int, device: torch.device) -> torch.Tensor:
+        """The data area of the local region as a bf16 ``[2 * world * slot_rows, width]`` matrix (both buffer
+        parities; the row numbers a gather returns point into it).  The tensor aliases library memory."""
+        slot_rows = self.slot_bytes // (2 * width)
+        if slot_rows * 2 * width != self.slot_bytes:
+            raise RuntimeError(f"slot of {self.slot_bytes} bytes is not a whole number of rows of {width} bf16")
+        key = (width, device)
+        cached = getattr(self, "_matrices", None)
+        if cached is None:
+            cached = self._matrices = {}
+        if key not in cached:
+            rows = 2 * self.world * slot_rows
+            base = load().dyllm_tp_comm_data(self._comm)
+            cached[key] = _device_view(base, rows, width, device)
+        return cached[key]
+
+    def gather_rows(self, x: torch.Tensor, idx: torch.Tensor | None, count_dev: torch.Tensor | None, max_rows: int):
+        """All ranks' rows ``x[idx[:count]]`` -> (matrix, idx_all int32 [world * slot_rows], prefix int32
+        [world + 1], total int32 [1]); see ``dyllm_tp_gather_rows``."""
+        require_cuda(x, "x", torch.bfloat16, 2)
+        width, dev = x.size(1), x.device
+        mat = self.data_matrix(width, dev)
+        cap = self.world * (self.slot_bytes // (2 * width))
+        idx_all = torch.empty((cap,), dtype=torch.int32, device=dev)
+        prefix = torch.empty((self.world + 1,), dtype=torch.int32, device=dev)
+        total = torch.empty((1,), dtype=torch.int32, device=dev)
+        call("dyllm_tp_gather_rows", self._comm, ptr(x), x.size(0), width, x.stride(0), ptr(idx), int(max_rows),
+             ptr(count_dev), ptr(idx_all), ptr(prefix), ptr(total), stream_ptr(dev))
+        return mat, idx_all, prefix, total
+
+    def scatter_reduce_rows(self, y: torch.Tensor, prefix: torch.Tensor, max_total: int, count_dev, max_rows: int,
+                            out: torch.Tensor, out_row_map: torch.Tensor | None) -> None:
+        """Partial output rows ``y`` (one per gathered row) go back to their owners, which add the ranks'
+        partials in rank order and write the sums to ``out[map[m]]``."""
+        require_cuda(y, "y", torch.bfloat16, 2)
+        call("dyllm_tp_scatter_push", self._comm, ptr(y), y.size(1), int(max_total), ptr(prefix), stream_ptr(y.device))
+        self.reduce_rows(y.size(1), count_dev, 0, int(max_rows), out, out_row_map)
+
+
+def _device_view(address: int, rows: int, width: int, device: torch.device) -> torch.Tensor:
+    """A bf16 ``[rows, width]`` tensor over device memory owned by the library (no copy, no ownership)."""
+
+    class _Holder:
+        __cuda_array_interface__ = {"shape": (rows * width,), "typestr": "<i2", "data": (address, False), "version": 3}
+
+    return torch.as_tensor(_Holder(), device=device).view(torch.bfloat16).view(rows, width)

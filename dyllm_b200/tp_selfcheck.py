@@ -25,14 +25,13 @@ BAND = 2e-3      # decisions are compared where the unsharded cosine is at least
 @contextlib.contextmanager
 def _single_rank():
     """Makes the layer classes see a world of one rank (construction and forward of the unsharded layer)."""
-    saved = (layers._world_size, layers._rank, model_mod._world_size, layers._tp_comm)
-    layers._world_size = model_mod._world_size = lambda: 1
-    layers._rank = lambda: 0
+    saved = layers._tp_comm
     layers._tp_comm = None
     try:
-        yield
+        with layers.replicated():
+            yield
     finally:
-        layers._world_size, layers._rank, model_mod._world_size, layers._tp_comm = saved
+        layers._tp_comm = saved
 
 
 def _build_layer(dev, shape, tau, seed):

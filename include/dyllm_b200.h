@@ -386,6 +386,33 @@ int dyllm_tp_reduce_rows(void* comm, int width, int max_rows, const int32_t* cou
 int dyllm_tp_allreduce_rows(void* comm, const void* src, int width, int max_rows, const int32_t* count_dev,
                             int row_offset, void* out, int64_t ldo, const int32_t* out_row_map, void* stream);
 
+/* Row gather of the sequence-sharded layout (every rank runs attention and the all-row projections for its
+ * own sequences; the FFN / expert weights are sharded over the ranks).  Every rank contributes the rows
+ * x[idx[m]] (idx null = identity), m < min(max_rows, *count_dev), of its bf16 [x_rows, width] activation
+ * (row pitch ldx); afterwards every rank holds all contributions, ordered by rank, in the data area of its
+ * region (dyllm_tp_comm_data: a bf16 matrix of 2 * world * (slot_bytes / (2 * width)) rows of `width`), and
+ *   idx_all[0..total)   row numbers of the gathered rows inside that matrix (feed them, with the matrix as
+ *                       x, to dyllm_swiglu_ffn / dyllm_moe_route / dyllm_moe_ffn as their index list)
+ *   prefix[0..world]    number of rows contributed by the ranks before r
+ *   total_out[0]        prefix[world]
+ * The counts may differ from rank to rank.  slot_bytes must be a whole number of rows >= max_rows.
+ * dyllm_tp_gather_rows = dyllm_tp_gather_push + dyllm_tp_gather_finish (the split form lets a test run
+ * several emulated ranks one after the other).  No counterpart in the reference, whose tensor-parallel
+ * ranks all hold every row (dyllm/model_executor/models/llada.py:184-186 gathers locally). */
+int dyllm_tp_gather_rows(void* comm, const void* x, int x_rows, int width, int64_t ldx, const int32_t* idx,
+                         int max_rows, const int32_t* count_dev, int32_t* idx_all, int32_t* prefix,
+                         int32_t* total_out, void* stream);
+int dyllm_tp_gather_push(void* comm, const void* x, int x_rows, int width, int64_t ldx, const int32_t* idx,
+                         int max_rows, const int32_t* count_dev, void* stream);
+int dyllm_tp_gather_finish(void* comm, int width, int32_t* idx_all, int32_t* prefix, int32_t* total_out,
+                           void* stream);
+void* dyllm_tp_comm_data(void* comm);
+/* The way back: y holds one partial output row per gathered row (same order); row m goes to the rank that
+ * contributed it (prefix from the gather), into the pushing rank's slot there.  The owner then calls
+ * dyllm_tp_reduce_rows with its own count to add the world slots in rank order and scatter the sums.
+ * ref: dyllm/model_executor/layers/linear.py:216-220 (SUM over the ranks' partial down projections). */
+int dyllm_tp_scatter_push(void* comm, const void* y, int width, int max_rows, const int32_t* prefix, void* stream);
+
 /* In-place SUM all-reduce of n fp32 values (the [rows, 3] cosine statistics, 12 bytes per token).
  * ref: dyllm/distributed/parallel_state.py:60-61. */
 int dyllm_tp_push_f32(void* comm, const float* src, int n, void* stream);

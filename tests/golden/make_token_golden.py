@@ -11,10 +11,12 @@ the sampler's three Triton helpers (``triton_repeat_interleave``, ``launch_ragge
 ``launch_filter_and_count``, sampler.py:16-175) are restated in torch below; ``.cuda()`` / pinned memory are
 no-ops.
 
-Besides the chosen (position, token) pairs the fixture records, per step, how clear the choice was (the
-best-to-second-best probability ratio of the chosen row and the margin between the last chosen and the first
-rejected confidence), so that a test can require equality wherever the reference's choice does not hinge on
-rounding.
+Besides the chosen (position, token) pairs the fixture records, per step: every candidate row's confidence
+(fp32 softmax maximum of the reference's logits), its best token and that token's lead over the runner-up; how
+clear the choice among the rows was (margin between the last chosen and the first rejected confidence); and
+the cosines every layer's selection saw.  A test can then compare the confidences numerically, require equal
+tokens and rows wherever the reference's choice does not hinge on rounding, and notice when a salient decision
+inside the rounding band forks the two runs.
 
     TORCHDYNAMO_DISABLE=1 python tests/golden/make_token_golden.py /path/to/reference
 """
@@ -167,6 +169,19 @@ def main(ref_root):
     from dyllm.utils.metadata import get_metadata, set_metadata
 
     _sampler_standins(sampler_mod)
+    # record the cosines every layer's selection sees (dyllm/distributed/parallel_state.py:52-66)
+    import dyllm.distributed as ddist
+    import dyllm.model_executor.layers.attention as ref_attn
+    from oracle import dyllm_oracle as orc
+
+    seen_cos = []
+    real_mask = ddist.tensor_parallel_cosine_mask
+
+    def recording_mask(stats, threshold):
+        seen_cos.append(orc.cosine_values(stats).float())
+        return real_mask(stats, threshold)
+
+    ref_attn.tensor_parallel_cosine_mask = recording_mask
     c = CFG
     cfg = types.SimpleNamespace(hidden_size=c["hidden"], num_attention_heads=c["heads"], n_kv_heads=c["kv_heads"],
                                 max_sequence_length=c["max_pos"], rms_norm_eps=c["eps"], head_dim=c["head_dim"],
@@ -188,6 +203,7 @@ def main(ref_root):
             s.processed_steps += 1                 # scheduler.py:43,69
         is_full = seqs[0].processed_steps <= c["full_steps"]
         get_metadata().finished_seqs = []
+        seen_cos.clear()
         with torch.no_grad():
             input_ids, positions = ModelRunner.prepare_full(runner, seqs) if is_full else ModelRunner.prepare_sparse(runner, seqs)
             ctx = get_context()
@@ -204,7 +220,7 @@ def main(ref_root):
             probs = torch.softmax(logits.index_select(0, rows).float(), dim=-1)
             top2 = probs.topk(2, dim=-1).values
         reset_context()
-        picks, clear = [], []
+        picks, clear, cand_rec = [], [], []
         for b, s in enumerate(seqs):
             n = int(counts[b])
             p_list, t_list = pos[b, :n].tolist(), toks[b, :n].tolist()
@@ -216,12 +232,19 @@ def main(ref_root):
             tok_margin = float((cand[chosen_rows, 0] / cand[chosen_rows, 1] - 1.0).min()) if n else float("inf")
             picks.append(sorted(zip(p_list, t_list)))
             clear.append((sel_margin, tok_margin))
+            lo, hi = int(cu_f[b]), int(cu_f[b + 1])
+            cand_pos = (rel[lo:hi] + offs[b]).tolist()
+            cand_rec.append([(p, float(cf), int(tk), float(mg)) for p, cf, tk, mg in
+                             zip(cand_pos, conf.tolist(), probs[lo:hi].argmax(-1).tolist(),
+                                 (cand[:, 0] / cand[:, 1] - 1.0).tolist())])
             s.update_token(p_list, t_list)
             s.update_block_idx()
+        gap = min((float((cs - c["tau"]).abs().min()) for cs in seen_cos), default=float("inf"))
         record["steps"].append({"kind": "full" if is_full else ("pruned" if pruned else "sparse"), "picks": picks,
-                                "margins": clear})
-        print(step + 1, record["steps"][-1]["kind"], picks, [tuple(round(x, 3) for x in m) for m in clear])
+                                "margins": clear, "candidates": cand_rec, "layer_cosines": [cs.clone() for cs in seen_cos], "cosine_gap": gap})
+        print(step + 1, record["steps"][-1]["kind"], picks, [tuple(round(x, 3) for x in m) for m in clear], "cos gap %.5f" % gap)
     record["final_tokens"] = [s.token_ids[s.num_prompt_tokens:] for s in seqs]
+    print("smallest |cos - tau| of the run:", min(st["cosine_gap"] for st in record["steps"]))
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "llada_tokens_small.pt")
     torch.save(record, path)
     print("wrote", path, os.path.getsize(path), "bytes")

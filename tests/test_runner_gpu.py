@@ -98,16 +98,25 @@ def test_token_ids_follow_the_reference_step_loop(cuda_device):
     """Token ids over a fixed step count against the reference's own step loop (fixture
     tests/golden/llada_tokens_small.pt from tests/golden/make_token_golden.py: the reference's ModelRunner
     preparation, LLaDAForDLM and sampler on the CPU).  Every step is compared and then the recorded choice is
-    applied, so one rounding-dependent choice cannot derail the steps after it.  A step's choice must be
-    identical whenever the reference's own choice was clear: the chosen row's best token at least 3 % more
-    probable than its runner-up and the chosen row's confidence at least 3 % above the best rejected row's
-    (the reference ranks bf16 probabilities, which are only resolved to ~0.4 %)."""
+    applied, so one rounding-dependent choice cannot derail the steps after it.  Per step:
+
+    * every candidate row's confidence is within 25 % of the reference's (mean error of a step within 8 %): with
+      random-init weights the vocabulary projection turns the ~0.5 % bf16 noise of the hidden states into a few
+      per cent of confidence, and the candidates of a block lie only a few per cent apart;
+    * a candidate's best token is the reference's wherever that token leads its runner-up by 25 %;
+    * the rows chosen for unmasking are the reference's wherever the last chosen confidence leads the first
+      rejected one by 25 %;
+    * every layer's salient set equals the reference's on all rows whose reference cosine is at least 2e-3 from
+      the threshold.  The first decision inside that band that goes the other way forks the two runs (the row's
+      FFN output is fresh in one and cached in the other), after which only the salient-set check goes on."""
     import os
     import sys
 
     sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
     import make_token_golden as mtg
-    from dyllm_b200 import _lib, runner
+    from oracle import dyllm_oracle as orc
+
+    from dyllm_b200 import _lib, ops, runner
     from dyllm_b200.model import LLaDAForDLM, LLaDAShape
 
     fx = torch.load(os.path.join(os.path.dirname(__file__), "golden", "llada_tokens_small.pt"))
@@ -127,23 +136,73 @@ def test_token_ids_follow_the_reference_step_loop(cuda_device):
     model.eval()
     sr = runner.StepRunner(model, mtg.MASK_ID, block_length=c["block"], steps=c["steps"], num_full_steps=c["full_steps"],
                            refresh_period=4, use_graphs=False)
+    sr.record_candidates = True
     prompts = mtg.token_prompts()
     seqs = sr.new_batch(prompts, c["gen"])
-    compared = agreed_anyway = 0
-    for step, rec in enumerate(fx["steps"]):
-        picks = sr.step_picks(seqs, forced=rec["picks"])
-        for b, (got, want, (sel_margin, tok_margin)) in enumerate(zip(picks, rec["picks"], rec["margins"])):
-            if sel_margin >= 0.03 and tok_margin >= 0.03:
-                compared += 1
-                assert got == want, f"step {step + 1} ({rec['kind']}) sequence {b}: {got} != {want}"
-            else:
-                agreed_anyway += got == want
-    total = len(fx["steps"]) * len(prompts)
-    print(f"clear choices compared: {compared}/{total}; unclear ones that agreed anyway: {agreed_anyway}/{total - compared}")
-    assert compared >= total // 3
+    seen = []
+    real_select = ops.salient_select
+
+    def recording_select(stats, threshold, *a, **k):
+        sel = real_select(stats, threshold, *a, **k)
+        seen.append((orc.cosine_values(stats.cpu()).float(), sel.idx[: int(sel.count.item())].cpu()))
+        return sel
+
+    ops.salient_select = recording_select
+    forked_at = None
+    failures = []
+    steps_before_fork = rows_compared = tokens_compared = picks_compared = 0
+    try:
+        for step, rec in enumerate(fx["steps"]):
+            seen.clear()
+            picks = sr.step_picks(seqs, forced=rec["picks"])
+            for layer, ((cos_got, idx_got), cos_ref) in enumerate(zip(seen, rec["layer_cosines"])):
+                m_ref = cos_ref < c["tau"]
+                m_got = torch.zeros_like(m_ref)
+                m_got[idx_got] = True
+                clear = (cos_ref - c["tau"]).abs() >= 2e-3
+                if forked_at is None:
+                    assert torch.equal(m_got[clear], m_ref[clear]), f"step {step + 1} layer {layer}: salient sets differ"
+                    if not torch.equal(m_got, m_ref):
+                        forked_at = step + 1
+                        print(f"step {step + 1} layer {layer}: a decision inside the band went the other way "
+                              f"(cosine error max {float((cos_got - cos_ref).abs().max()):.2e})")
+            if forked_at is not None and forked_at <= step + 1:
+                continue
+            steps_before_fork += 1
+            cand_pos, conf, tok = sr.last_candidates
+            for b, (got, want, (sel_margin, _)) in enumerate(zip(picks, rec["picks"], rec["margins"])):
+                mine = {p: (float(conf[b, i]), int(tok[b, i])) for i, p in enumerate(cand_pos[b]) if conf[b, i] >= 0}
+                ref = {p: (cf, tk, mg) for p, cf, tk, mg in rec["candidates"][b]}
+                assert set(mine) == set(ref), f"step {step + 1} sequence {b}: candidate rows differ"
+                errs = []
+                for p, (cf, tk, mg) in ref.items():
+                    errs.append(abs(mine[p][0] - cf) / cf)
+                    rows_compared += 1
+                    if mg >= 0.25:
+                        tokens_compared += 1
+                        if mine[p][1] != tk:
+                            failures.append(f"step {step + 1} sequence {b} position {p}: token {mine[p][1]} != {tk} "
+                                            f"(reference lead {mg:.2f}, confidence {mine[p][0]:.3f} vs {cf:.3f})")
+                print(f"step {step + 1} ({rec['kind']}) sequence {b}: confidence errors max {max(errs):.3f} "
+                      f"mean {sum(errs) / len(errs):.3f}")
+                if not (max(errs) <= 0.25 and sum(errs) / len(errs) <= 0.08):
+                    failures.append(f"step {step + 1} ({rec['kind']}) sequence {b}: confidence errors max {max(errs):.3f} "
+                                    f"mean {sum(errs) / len(errs):.3f}")
+                if sel_margin >= 0.25:
+                    picks_compared += 1
+                    if got != want:
+                        failures.append(f"step {step + 1} sequence {b}: {got} != {want}")
+    finally:
+        ops.salient_select = real_select
+    print(f"steps compared before the runs forked: {steps_before_fork} (fork at step {forked_at}); candidate confidences "
+          f"compared {rows_compared}, tokens {tokens_compared}, row choices {picks_compared}")
+    assert not failures, "\n".join(failures)
+    assert steps_before_fork >= 6 and rows_compared >= 100 and tokens_compared >= 40
     assert [s.token_ids[s.num_prompt_tokens:] for s in seqs] == fx["final_tokens"]
     assert _lib.load().dyllm_device_status() == 0
     # free-running generations (host-driven and device-resident) for the record
+    sr.record_candidates = False
+    total = c["batch"] * c["gen"]
     for device_state in (False, True):
         free = sr.generate(prompts, c["gen"], device_state=device_state)
         same = sum(a == b for row, ref in zip(free, fx["final_tokens"]) for a, b in zip(row, ref))

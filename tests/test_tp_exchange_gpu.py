@@ -116,3 +116,56 @@ def test_slot_overflow_is_rejected(cuda_device):
         assert _lib.load().dyllm_device_status() == 0
     finally:
         comms[0].close()
+
+
+@pytest.mark.parametrize("world,width,counts", [(2, 256, [5, 0]), (4, 512, [17, 64, 1, 33]), (8, 4096, [3, 0, 9, 2, 0, 1, 7, 4])])
+def test_gather_and_owner_scatter_of_the_sequence_sharded_layout(cuda_device, world, width, counts):
+    """Every rank contributes a different number of indexed rows; all ranks then see all rows in rank order;
+    per-row partial results travel back to the owner, which adds them in rank order and scatters them."""
+    from dyllm_b200 import _lib
+    from dyllm_b200._lib import call, ptr, stream_ptr
+    from dyllm_b200.tp_comm import TpComm
+
+    dev, slot_rows, x_rows = cuda_device, 64, 200
+    comms = TpComm.emulated_world(world, slot_rows * width * 2)
+    try:
+        g = torch.Generator(device=dev).manual_seed(world + width)
+        for round_ in range(3):
+            xs = [torch.randn(x_rows, width, generator=g, device=dev).bfloat16() for _ in range(world)]
+            idxs = [torch.randperm(x_rows, generator=g, device=dev)[:slot_rows].to(torch.int32) for _ in range(world)]
+            cnts = [torch.tensor([counts[(r + round_) % world]], dtype=torch.int32, device=dev) for r in range(world)]
+            n = [int(c) for c in cnts]
+            for c, x, i, k in zip(comms, xs, idxs, cnts):
+                call("dyllm_tp_gather_push", c._comm, ptr(x), x_rows, width, x.stride(0), ptr(i), slot_rows, ptr(k), stream_ptr(dev))
+            outs = []
+            for c in comms:
+                idx_all = torch.full((world * slot_rows,), -1, dtype=torch.int32, device=dev)
+                prefix = torch.empty(world + 1, dtype=torch.int32, device=dev)
+                total = torch.empty(1, dtype=torch.int32, device=dev)
+                call("dyllm_tp_gather_finish", c._comm, width, ptr(idx_all), ptr(prefix), ptr(total), stream_ptr(dev))
+                outs.append((c.data_matrix(width, dev), idx_all, prefix, total))
+            want_rows = torch.cat([x[i[:k].long()] for x, i, k in zip(xs, idxs, n)])
+            want_prefix = [0]
+            for k in n:
+                want_prefix.append(want_prefix[-1] + k)
+            for mat, idx_all, prefix, total in outs:
+                assert int(total) == sum(n) and prefix.tolist() == want_prefix
+                assert torch.equal(mat[idx_all[: sum(n)].long()], want_rows)
+            # partial outputs: rank r computes (r + 1) * row; the owner's sum is row * world * (world + 1) / 2
+            ys = [(want_rows.float() * (r + 1)).bfloat16() for r in range(world)]
+            for c, y, (_, _, prefix, _) in zip(comms, ys, outs):
+                call("dyllm_tp_scatter_push", c._comm, ptr(y), width, world * slot_rows, ptr(prefix), stream_ptr(dev))
+            for r, (c, k) in enumerate(zip(comms, cnts)):
+                dest = torch.full((slot_rows + 8, width), 9.0, dtype=torch.bfloat16, device=dev)
+                rows = torch.arange(slot_rows, dtype=torch.int32, device=dev) + 3       # scatter with an offset
+                c.reduce_rows(width, k, 0, slot_rows, dest, rows)
+                acc = torch.zeros(n[r], width, device=dev)
+                for y in ys:
+                    acc += y[want_prefix[r]: want_prefix[r + 1]].float()
+                want = torch.full((slot_rows + 8, width), 9.0, dtype=torch.bfloat16, device=dev)
+                want[3: 3 + n[r]] = acc.bfloat16()
+                assert torch.equal(dest, want), f"round {round_} rank {r}"
+        assert _lib.load().dyllm_device_status() == 0
+    finally:
+        for c in comms:
+            c.close()

@@ -56,14 +56,8 @@ def _worker(rank, world, port, out_queue):
     cache_manager.CacheManager.__init__.__defaults__ = (64, torch.float32, torch.device("cpu"))
     cfg = model.LLaDAShape(hidden_size=256, num_attention_heads=4, n_kv_heads=2, mlp_hidden_size=512,
                            num_hidden_layers=1, vocab_size=512, max_sequence_length=64)
-    real = (layers._world_size, layers._rank)
-    layers._world_size, layers._rank = (lambda: 1), (lambda: 0)
-    model._world_size = layers._world_size
-    try:
+    with layers.replicated():
         single = model.LLaDAForDLM(cfg, 0.99)
-    finally:
-        layers._world_size, layers._rank = real
-        model._world_size = real[0]
     model.init_weights_(single, seed=3)
     sharded = model.LLaDAForDLM(cfg, 0.99)
     model.init_weights_(sharded, seed=3)

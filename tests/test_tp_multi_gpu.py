@@ -31,10 +31,10 @@ def _worker(rank, world, port, results):
     from dyllm_b200.tp_comm import TpComm
 
     out = {}
-    comm = TpComm.from_process_group(dev, slot_bytes=256 * 512 * 2)
+    comm = TpComm.from_process_group(dev, slot_bytes=1024 * 4096 * 2)
     # --- exchange: rows (two rounds, count on the device, scatter map) and fp32 ------------------
     g = torch.Generator(device=dev).manual_seed(100 + rank)
-    cap, width, live = 600, 512, 417
+    cap, width, live = 2500, 4096, 1717        # more rows than a slot holds: three rounds
     count = torch.tensor([live], dtype=torch.int32, device=dev)
     ok_rows = True
     for _ in range(3):
@@ -82,6 +82,30 @@ def _worker(rank, world, port, results):
     out["graphs_captured"] = len(graphs._graphs)
     out["status"] = _lib.load().dyllm_device_status()
     graphs.release_graphs()
+
+    # --- sequence-sharded layout: every rank owns whole sequences, the FFN weights stay sharded --------
+    layers.set_layout("sequence")
+    try:
+        out["selfcheck_sequence"] = tp_selfcheck.run(dev, 0.99)
+        torch.set_default_dtype(torch.bfloat16)
+        with torch.device(dev):
+            model_s = LLaDAForDLM(shape, 0.99)
+        torch.set_default_dtype(torch.float32)
+        init_weights_(model_s, seed=3, std=0.05)
+        model_s.eval()
+        prompts4 = torch.randint(0, 900, (4, 40), generator=torch.Generator().manual_seed(1)).tolist()
+        eager_s = runner.StepRunner(model_s, shape.mask_token_id, block_length=8, steps=32, num_full_steps=4, use_graphs=False)
+        graphs_s = runner.StepRunner(model_s, shape.mask_token_id, block_length=8, steps=32, num_full_steps=4, use_graphs=True)
+        want_s = eager_s.generate(prompts4, 32)
+        got_s = [graphs_s.generate(prompts4, 32) for _ in range(2)]
+        out["sequence_graphs_equal_eager"] = all(g == want_s for g in got_s) and len(want_s) == 4
+        # attention weights are complete on every rank, FFN weights are shards
+        a, m = model_s.model.layers[0].self_attn, model_s.model.layers[0].mlp
+        out["sequence_shapes"] = (tuple(a.q_proj.weight.shape), tuple(m.down_proj.weight.shape))
+        out["status_sequence"] = _lib.load().dyllm_device_status()
+        graphs_s.release_graphs()
+    finally:
+        layers.set_layout("tensor")
     layers.set_tp_comm(None)
     comm.close()
     dist.barrier()
@@ -113,6 +137,9 @@ def test_tensor_parallel_path_on_gpus(cuda_device, world):
         assert res["exchange"], res
         assert res["graphs_equal_eager"] and res["graphs_captured"] == 3, res
         assert res["status"] == 0 and res["shutdown"], res
-    report = results[0]["selfcheck"]
-    print("sharded vs unsharded layer:", report)
-    assert report["ok"], report
+        assert res["sequence_graphs_equal_eager"] and res["status_sequence"] == 0, res
+        assert res["sequence_shapes"] == ((512, 512), (512, 1024 // world)), res
+    for key in ("selfcheck", "selfcheck_sequence"):
+        report = results[0][key]
+        print(f"{key}: sharded vs unsharded layer:", report)
+        assert report["ok"], report
