@@ -45,7 +45,9 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     MN-major operand, bit 1 = ``V`` is compact ``[num_salient, Hkv, D]`` (row i = key
     ``idx_salient_row_k[i]``) instead of the zero-padded ``[T_k, Hkv, D]`` tensor.  ``num_salient_dev``
     (extension): device int32 scalar with the live length of the index lists, whose tensors are then
-    only capacity-sized.  ``c_cache`` (extension): ``(seq_starts, seq_ids, update_in_place)``; ``C`` is then the
+    only capacity-sized.  bit 2 of ``v_layout`` (extension): ``cosine_stats`` is overwritten, not added to.
+    With ``c_cache`` and ``is_q_pruned``, ``idx_salient_row_k`` may be None: a listed query row's key row is
+    the row at the same distance from the end of its sequence.  ``c_cache`` (extension): ``(seq_starts, seq_ids, update_in_place)``; ``C`` is then the
     context cache arena ``[cache_rows, H, D]`` read (and optionally updated) in place instead of a packed copy.
     """
     if not (isinstance(Q, torch.Tensor) and Q.is_cuda):
@@ -94,7 +96,9 @@ def attention_sparse_varlen(Q, K, V, C, o_sal, cu_seqlens_q, cu_seqlens_k, max_s
     if force_mask_v_rows not in (-1, 0, 1):
         raise RuntimeError("force_mask_v_rows must be -1, 0, or 1")
     idx_k = idx_salient_row
-    if is_q_pruned:
+    if is_q_pruned and idx_salient_row_k is None and c_cache is not None:
+        idx_k = None        # extension: key rows derived from the query rows (queries = last rows of a sequence)
+    elif is_q_pruned:
         _check_tensor(idx_salient_row_k, "idx_salient_row_k", dev, i32, 1)
         if idx_salient_row_k.numel() != idx_salient_row.numel():
             raise RuntimeError("parallel Q/K pruning requires matching salient Q and K index counts")

@@ -144,6 +144,7 @@ __device__ __forceinline__ bool small_rows_item(int n_sal, int num_kt) {
 // One unit of work: (sequence, query head, tile of 128 query rows).
 struct AttnItem {
   int h, hk, sal_begin, n_sal, q_end, q0, k_begin, len_k, num_kt, num_st;
+  int k_shift;       // K row of a query row listed in idx_q when no K-space list is given: idx_q[i] + k_shift
   int64_t c_delta;   // C_old row of query row r: r + c_delta (cache-resident context)
   bool tile_tma;     // the tile lies completely inside the sequence: context through shared memory
   bool fast;         // at most kFastSal salient keys: gathered early into their own buffers
@@ -180,6 +181,8 @@ __device__ __forceinline__ bool decode_item(const AttnParams& p, int item, AttnI
     return false;   // salient_rows_small_kernel takes this sequence
   it.hk = it.h / (p.H / p.Hkv);
   it.num_st = EXACT ? it.num_kt : (it.n_sal + kBKeys - 1) / kBKeys;   // tiles of pass B
+  // the queries of a sequence are its last len_q rows
+  it.k_shift = EXACT ? 0 : it.k_begin + it.len_k - (it.q_end - q_begin) - q_begin;
   it.c_delta = 0;
   if (!EXACT && p.c_seq_starts)
     it.c_delta = p.c_seq_starts[p.c_seq_ids[b]] + (it.len_k - (it.q_end - q_begin)) - q_begin;
@@ -460,7 +463,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!decode_item<EXACT>(p, item, it))
         continue;
       const int h = it.h, hk = it.hk, q0 = it.q0, q_end = it.q_end, sal_begin = it.sal_begin, n_sal = it.n_sal;
-      const int num_kt = it.num_kt, num_st = it.num_st, len_k = it.len_k;
+      const int num_kt = it.num_kt, num_st = it.num_st, len_k = it.len_k, k_shift = it.k_shift;
       const int64_t c_delta = it.c_delta;
       const bool tile_tma = it.tile_tma, fast = it.fast;
       float m = kNegBig, l = 0.f;
@@ -490,7 +493,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           if (q0 + row < q_end)
             src = p.idx_q[sal_begin + q0 + row];
         } else if (row < n_sal) {
-          src = p.idx_k[sal_begin + row];
+          src = p.idx_k ? p.idx_k[sal_begin + row] : p.idx_q[sal_begin + row] + k_shift;
         }
         s_src[row] = src;
         s_sal_pos[row] = 0;
@@ -631,7 +634,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 308);
           if (half == 0) {
             const int j = st * kBKeys + row;
-            s_src[row] = j < n_sal ? p.idx_k[sal_begin + j] : -1;
+            s_src[row] = j < n_sal ? (p.idx_k ? p.idx_k[sal_begin + j] : p.idx_q[sal_begin + j] + k_shift) : -1;
           }
           asm volatile("bar.sync 1, 256;" ::: "memory");
         }
@@ -1138,11 +1141,16 @@ __device__ __forceinline__ bool mask_rule(float dot, float a, float b, float thr
 
 __global__ void __launch_bounds__(256)
 attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, float* __restrict__ stats,
-                          uint8_t* __restrict__ mask, float threshold) {
+                          uint8_t* __restrict__ mask, float threshold, int accumulate) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= Tq)
     return;
-  float s0 = stats[r * 3 + 0], s1 = stats[r * 3 + 1], s2 = stats[r * 3 + 2];
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+  if (accumulate) {
+    s0 = stats[r * 3 + 0];
+    s1 = stats[r * 3 + 1];
+    s2 = stats[r * 3 + 2];
+  }
   for (int h = 0; h < H; ++h) {
     const float* ps = partial + (static_cast<int64_t>(h) * Tq + r) * 3;
     s0 += ps[0];
@@ -1221,7 +1229,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   DYLLM_REQUIRE(q && k && c && out && cu_seqlens_q && cu_seqlens_k && cu_salientlens && cosine_stats &&
                     cosine_out && workspace,
                 DYLLM_ERR_INVALID_ARGUMENT, "attention_sparse_varlen: null pointer");
-  DYLLM_REQUIRE(num_salient == 0 || (v && o_sal && idx_salient_row_q && idx_salient_row_k), DYLLM_ERR_INVALID_ARGUMENT,
+  DYLLM_REQUIRE(num_salient == 0 || (v && o_sal && idx_salient_row_q), DYLLM_ERR_INVALID_ARGUMENT,
                 "attention_sparse_varlen: salient rows without delta-V / o_sal / index lists");
   DYLLM_REQUIRE(workspace_bytes >= dyllm_attention_sparse_workspace_bytes(total_q, num_heads), DYLLM_ERR_WORKSPACE,
                 "attention_sparse_varlen: workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
@@ -1287,7 +1295,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   if (rc != DYLLM_OK)
     return rc;
   attention_finalize_kernel<<<cdiv_i(total_q, 256), 256, 0, s>>>(p.partial, num_heads, total_q, cosine_stats,
-                                                                 cosine_out, threshold);
+                                                                 cosine_out, threshold, (v_layout & 4) ? 0 : 1);
   return check_launch("attention_finalize");
 }
 

@@ -10,17 +10,11 @@ constexpr int kNormThreads = 256;
 
 // y = bf16( bf16((x + r) * rsqrt(mean((x + r)^2) + eps)) * w ), r_out = bf16(x + r); fp32 statistics.
 // One block per row; VPT 16-byte vectors per thread are kept in registers between the two passes.
+// yr null = only the residual sum is wanted; ror null = only the normalised row.
 template <int VPT>
-__global__ void __launch_bounds__(kNormThreads)
-add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
-                    uint4* __restrict__ y, uint4* __restrict__ res_out, int vecs, float inv_width, float eps,
-                    int x_seg_rows, int64_t x_seg_pitch_rows) {
-  const int64_t row = blockIdx.x;
-  // x may consist of equal segments of rows that lie x_seg_pitch_rows apart (a block of every sequence
-  // read straight out of a cache); everything else is packed
-  const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
-  const uint4* xr = x + x_row * vecs;
-  const uint4* rr = res_in ? res_in + row * vecs : nullptr;
+__device__ __forceinline__ void norm_one_row(const uint4* __restrict__ xr, const uint4* __restrict__ rr,
+                                             const uint4* __restrict__ w, uint4* __restrict__ yr,
+                                             uint4* __restrict__ ror, int vecs, float inv_width, float eps) {
   float vals[VPT][8];
   float ss = 0.f;
 #pragma unroll
@@ -46,15 +40,18 @@ add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_i
         ss = fmaf(s1, s1, ss);
         ro2[i] = __floats2bfloat162_rn(s0, s1);
       }
-      if (res_out)
-        res_out[row * vecs + v] = ro;
+      if (ror)
+        ror[v] = ro;
     }
   }
+  if (!yr)
+    return;      // uniform over the block
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1)
     ss += __shfl_xor_sync(0xffffffffu, ss, off);
   __shared__ float red[kNormThreads / 32];
   __shared__ float s_scale;
+  __syncthreads();   // a block that normalises several rows reuses the two shared words
   if ((threadIdx.x & 31) == 0)
     red[threadIdx.x >> 5] = ss;
   __syncthreads();
@@ -80,8 +77,47 @@ add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_i
         const __nv_bfloat162 n = __floats2bfloat162_rn(vals[j][2 * i] * scale, vals[j][2 * i + 1] * scale);
         o2[i] = __hmul2(n, w2[i]);
       }
-      y[row * vecs + v] = o;
+      yr[v] = o;
     }
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kNormThreads)
+add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
+                    uint4* __restrict__ y, uint4* __restrict__ res_out, int vecs, float inv_width, float eps,
+                    int x_seg_rows, int64_t x_seg_pitch_rows) {
+  const int64_t row = blockIdx.x;
+  // x may consist of equal segments of rows that lie x_seg_pitch_rows apart (a block of every sequence
+  // read straight out of a cache); everything else is packed
+  const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
+  norm_one_row<VPT>(x + x_row * vecs, res_in ? res_in + row * vecs : nullptr, w, y + row * vecs,
+                    res_out ? res_out + row * vecs : nullptr, vecs, inv_width, eps);
+}
+
+// The same arithmetic when only the listed rows' normalised values are needed (the FFN of a sparse step
+// reads the salient rows alone): blocks [0, rows) write the residual sum of their row, the remaining blocks
+// walk the list and write the normalised row m to y_sel[m], ready to be the FFN's packed input.
+template <int VPT>
+__global__ void __launch_bounds__(kNormThreads)
+add_rms_norm_rows_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
+                         uint4* __restrict__ y_sel, uint4* __restrict__ res_out, int rows, int vecs, float inv_width,
+                         float eps, int x_seg_rows, int64_t x_seg_pitch_rows, const int32_t* __restrict__ sel_idx,
+                         int sel_max, const int32_t* __restrict__ sel_count_dev) {
+  if (static_cast<int>(blockIdx.x) < rows) {
+    const int64_t row = blockIdx.x;
+    const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
+    norm_one_row<VPT>(x + x_row * vecs, res_in ? res_in + row * vecs : nullptr, w, nullptr, res_out + row * vecs, vecs,
+                      inv_width, eps);
+    return;
+  }
+  const int count = sel_count_dev ? min(sel_max, *sel_count_dev) : sel_max;
+  for (int m = static_cast<int>(blockIdx.x) - rows; m < count; m += static_cast<int>(gridDim.x) - rows) {
+    int64_t row = sel_idx[m];
+    row = row < 0 ? 0 : (row >= rows ? rows - 1 : row);
+    const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
+    norm_one_row<VPT>(x + x_row * vecs, res_in ? res_in + row * vecs : nullptr, w, y_sel + static_cast<int64_t>(m) * vecs,
+                      nullptr, vecs, inv_width, eps);
   }
 }
 
@@ -250,6 +286,50 @@ int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pi
     default: add_rms_norm_kernel<4><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
   }
   return check_launch("add_rms_norm");
+}
+
+int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
+                            const void* weight, float eps, void* residual_out, int rows, int width,
+                            const int32_t* sel_idx, int sel_max, const int32_t* sel_count_dev, void* y_sel,
+                            void* stream) {
+  DYLLM_REQUIRE(rows >= 0 && width > 0 && sel_max >= 0, DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm_rows: rows %d width %d",
+                rows, width);
+  DYLLM_REQUIRE(x_seg_rows > 0 && x_seg_pitch_rows >= x_seg_rows, DYLLM_ERR_INVALID_ARGUMENT,
+                "add_rms_norm_rows: segments of %d rows, %lld rows apart", x_seg_rows,
+                static_cast<long long>(x_seg_pitch_rows));
+  DYLLM_REQUIRE(width % 8 == 0 && width <= 8 * kNormThreads * 4, DYLLM_ERR_UNSUPPORTED,
+                "add_rms_norm_rows: width %d must be a multiple of 8 and at most %d", width, 8 * kNormThreads * 4);
+  if (rows == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(x && weight && residual_out && (sel_max == 0 || (sel_idx && y_sel)), DYLLM_ERR_INVALID_ARGUMENT,
+                "add_rms_norm_rows: null pointer");
+  DYLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual_in) |
+                  reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y_sel) |
+                  reinterpret_cast<uintptr_t>(residual_out)) & 15) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm_rows: buffers must be 16-byte aligned");
+  const int vecs = width / 8;
+  const int vpt = cdiv_i(vecs, kNormThreads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const uint4* xp = static_cast<const uint4*>(x);
+  const uint4* rp = static_cast<const uint4*>(residual_in);
+  const uint4* wp = static_cast<const uint4*>(weight);
+  uint4* yp = static_cast<uint4*>(y_sel);
+  uint4* rop = static_cast<uint4*>(residual_out);
+  const float inv = 1.0f / static_cast<float>(width);
+  // the list is walked by at most 1024 blocks (each takes the entries blockIdx, blockIdx + n, ...)
+  const int sel_blocks = sel_max < 1024 ? sel_max : 1024;
+  const unsigned grid = static_cast<unsigned>(rows + sel_blocks);
+#define DYLLM_NORM_ROWS(V)                                                                                         \
+  add_rms_norm_rows_kernel<V><<<grid, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, rows, vecs, inv, eps, x_seg_rows, \
+                                                            x_seg_pitch_rows, sel_idx, sel_max, sel_count_dev)
+  switch (vpt) {
+    case 1: DYLLM_NORM_ROWS(1); break;
+    case 2: DYLLM_NORM_ROWS(2); break;
+    case 3: DYLLM_NORM_ROWS(3); break;
+    default: DYLLM_NORM_ROWS(4); break;
+  }
+#undef DYLLM_NORM_ROWS
+  return check_launch("add_rms_norm_rows");
 }
 
 int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, const float* cos_sin, int rows,

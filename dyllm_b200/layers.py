@@ -312,6 +312,14 @@ class RMSNorm(nn.Module):
             x = x.contiguous()
         return ops.add_rms_norm(x, self.weight, self.eps, residual)
 
+    def forward_rows(self, x: torch.Tensor, residual: torch.Tensor, sel_idx32: torch.Tensor, sel_count_dev=None):
+        """Residual add of every row, normalised values of the listed rows only, packed in list order:
+        ``(y_sel, new_residual)``.  What a sparse step needs of the post-attention norm: its output feeds the
+        FFN of the salient rows and nothing else (ref: dyllm/model_executor/models/llada.py:183-185)."""
+        if x.dim() == 2:
+            x = x.contiguous()
+        return ops.add_rms_norm_rows(x, self.weight, self.eps, residual, sel_idx32, sel_count_dev)
+
 
 class RotaryEmbedding(nn.Module):
     def __init__(self, head_size: int, rotary_dim: int, max_position_embeddings: int, base: float) -> None:
@@ -398,15 +406,17 @@ class LLaDAMLP(nn.Module):
         return ops.swiglu_ffn(mat, self.gate_up_proj.weight, self.down_proj.weight, idx_all, num_rows=cap_total,
                               num_rows_dev=total_dev, rows_hint=hint)
 
-    def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
+    def forward_salient(self, hidden: torch.Tensor, staged: bool = False) -> torch.Tensor:
         """Sparse step on the full ``[T_q, hidden]`` activation: the salient rows are read through the step's
         index list (live count on the device) and the down projection scatters straight into the
         FFN-output cache (replaces gather_rows_2D + MLP + scatter_update,
-        dyllm/model_executor/models/llada.py:184-186)."""
+        dyllm/model_executor/models/llada.py:184-186).  With ``staged`` the input already holds the salient
+        rows alone, packed in list order (``RMSNorm.forward_rows``)."""
         ctx, md = get_context(), get_metadata()
         cap = ctx.idx_salient_row.numel()
         n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
         cm = self.cache_update.cache_manager
+        idx32 = None if staged else ctx.idx_salient_row32
         if cap:
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
             rows = hint or cap
@@ -417,18 +427,17 @@ class LLaDAMLP(nn.Module):
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
                 world = _world_size()
                 with profiling.region("swiglu_ffn", 6.0 * rows * world * width * inter, nbytes):
-                    _gathered_ffn(self._ffn_shard, hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache,
-                                  out_row_map=dest)
+                    _gathered_ffn(self._ffn_shard, hidden, idx32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
             elif self.down_proj.tp_size > 1:
                 with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
-                    y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
+                    y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, idx32,
                                        num_rows=cap, num_rows_dev=n_dev, rows_hint=hint)
                 with profiling.region("ffn_all_reduce", 0.0, 2.0 * rows * width * 2):
                     all_reduce_salient_rows(y, n_dev, cm, md.running_seqs_tensor, rows_k)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
                 with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
-                    ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, ctx.idx_salient_row32,
+                    ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, idx32,
                                    num_rows=cap, num_rows_dev=n_dev, rows_hint=hint, out=cm.cache, out_row_map=dest)
         cm.finish(md.finished_seqs)
         return self.cache_update.result()
@@ -508,24 +517,26 @@ class LLaDAMoESparseBlock(nn.Module):
             all_reduce_sum(y)
         return self.cache_update(y)
 
-    def forward_salient(self, hidden: torch.Tensor) -> torch.Tensor:
+    def forward_salient(self, hidden: torch.Tensor, staged: bool = False) -> torch.Tensor:
         """Sparse step on the full activation: rows through the salient list, results scattered into the
-        FFN-output cache (at TP/EP > 1 after the all-reduce)."""
+        FFN-output cache (at TP/EP > 1 after the all-reduce).  With ``staged`` the input already holds the
+        salient rows alone, packed in list order."""
         ctx, md = get_context(), get_metadata()
         cap = ctx.idx_salient_row.numel()
         n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
         cm = self.cache_update.cache_manager
+        idx32 = None if staged else ctx.idx_salient_row32
         if cap:
             rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
             if sequence_sharded():
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
-                _gathered_ffn(self._experts, hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
+                _gathered_ffn(self._experts, hidden, idx32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
             elif _world_size() > 1:
-                y = self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint)
+                y = self._experts(hidden, idx32, cap, n_dev, hint)
                 all_reduce_salient_rows(y, n_dev, cm, md.running_seqs_tensor, rows_k)
             else:
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
-                self._experts(hidden, ctx.idx_salient_row32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
+                self._experts(hidden, idx32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
         cm.finish(md.finished_seqs)
         return self.cache_update.result()
 
@@ -629,11 +640,11 @@ class Attention(nn.Module):
             o_sal = attention_salient_rows(q, k, v_full, ctx.cu_seqlens_k, ctx.cu_salientlens, idx_q32,
                                            max_rows_per_seq=max_rows, num_salient=cap)
 
-        stats = torch.zeros((ctx.total_seqlen, 3), dtype=torch.float32, device=q.device)
+        stats = torch.empty((ctx.total_seqlen, 3), dtype=torch.float32, device=q.device)   # overwritten (v_layout bit 2)
         mask = torch.empty((ctx.total_seqlen,), dtype=torch.bool, device=q.device)
         # the previous context is read from, and the new one written back to, the cache arena itself
         c_arena = self.context_cache.cache.view(-1, H, D)
-        rows_k32 = rows_k.to(torch.int32) if is_q_pruned else None
+        rows_k32 = None      # response-only steps: the kernel derives the key rows from the query rows
         # algorithmic flops: Q K^T over all keys (sum over sequences of len_q * len_k, equal lengths here)
         flops = 2.0 * ctx.total_seqlen * ctx.max_seqlen_k * H * D
         # algorithmic bytes: Q and the previous context read, the new context written, K read once
@@ -641,7 +652,7 @@ class Attention(nn.Module):
         with profiling.region("delta_attention", flops, nbytes):
             new_c = attention_sparse_varlen(q, k, dv, c_arena, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens,
-                                            idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=3,
+                                            idx_q32, stats, mask, self.threshold, is_q_pruned, rows_k32, v_layout=7,
                                             num_salient_dev=n_dev,
                                             c_cache=(self.context_cache.seq_start_gpu, seq_t, True))
 

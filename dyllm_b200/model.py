@@ -113,6 +113,22 @@ class LLaDAAttention(nn.Module):
         return out
 
 
+def _post_attention(layer, hidden_states, residual):
+    """Second half of a decoder layer (ref: llada.py:183-186): residual add + RMSNorm, then the FFN on all rows
+    (dense step) or on the salient rows (sparse step).  In a sparse step only the salient rows are normalised:
+    they come out packed in list order and go straight into the FFN's GEMMs."""
+    ctx = get_context()
+    if ctx.is_full:
+        hidden_states, residual = layer.post_attention_layernorm(hidden_states, residual)
+        return layer.mlp(hidden_states), residual
+    if ctx.idx_salient_row32 is not None and ctx.idx_salient_row32.numel():
+        staged, residual = layer.post_attention_layernorm.forward_rows(hidden_states, residual, ctx.idx_salient_row32,
+                                                                       ctx.num_salient_dev)
+        return layer.mlp.forward_salient(staged, staged=True), residual
+    hidden_states, residual = layer.post_attention_layernorm(hidden_states, residual)
+    return layer.mlp.forward_salient(hidden_states), residual
+
+
 class LLaDADecoderLayer(nn.Module):
     def __init__(self, config: LLaDAShape, threshold: float, rotary_emb: RotaryEmbedding | None = None) -> None:
         super().__init__()
@@ -131,13 +147,7 @@ class LLaDADecoderLayer(nn.Module):
         else:
             hidden_states, residual = self.input_layernorm(hidden_states, residual)
         hidden_states = self.self_attn(positions, hidden_states)
-        ctx = get_context()
-        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
-        if ctx.is_full:
-            hidden_states = self.mlp(hidden_states)
-        else:
-            hidden_states = self.mlp.forward_salient(hidden_states)
-        return hidden_states, residual
+        return _post_attention(self, hidden_states, residual)
 
 
 class LLaDAModel(nn.Module):
@@ -221,12 +231,7 @@ class _DecoderLayer(nn.Module):
         else:
             hidden_states, residual = self.input_layernorm(hidden_states, residual)
         hidden_states = self.self_attn(positions, hidden_states)
-        hidden_states, residual = self.post_attention_layernorm(hidden_states, residual)
-        if get_context().is_full:
-            hidden_states = self.mlp(hidden_states)
-        else:
-            hidden_states = self.mlp.forward_salient(hidden_states)
-        return hidden_states, residual
+        return _post_attention(self, hidden_states, residual)
 
 
 class DreamDecoderLayer(_DecoderLayer):

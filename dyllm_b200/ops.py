@@ -257,6 +257,37 @@ def add_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: to
     return y if residual is None else (y, res_out)
 
 
+def add_rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor, sel_idx: torch.Tensor,
+                      sel_count_dev: torch.Tensor | None = None):
+    """Residual add of every row, RMSNorm of the listed rows only: returns ``(y_sel [len(sel_idx), width],
+    new_residual [rows, width])`` where ``y_sel[m]`` is the normalised row ``sel_idx[m]`` (the packed FFN input of
+    a sparse step).  ``x`` as for :func:`add_rms_norm`.
+
+    ref: dyllm/model_executor/models/llada.py:183-185.
+    """
+    if not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.bfloat16:
+        raise RuntimeError("x must be a CUDA bfloat16 tensor")
+    require_cuda(weight, "weight", torch.bfloat16, 1)
+    require_cuda(sel_idx, "sel_idx", torch.int32, 1)
+    width = x.size(-1)
+    if x.dim() == 2:
+        require_cuda(x, "x", torch.bfloat16, 2)
+        rows, seg_rows, seg_pitch = x.size(0), max(x.size(0), 1), max(x.size(0), 1)
+    elif x.dim() == 3 and x.stride(2) == 1 and x.stride(1) == width and x.stride(0) % width == 0 \
+            and x.stride(0) >= x.size(1) * width:
+        rows, seg_rows, seg_pitch = x.size(0) * x.size(1), x.size(1), x.stride(0) // width
+    else:
+        raise RuntimeError("x must be [rows, width] contiguous or [segments, rows, width] with contiguous rows")
+    require_cuda(residual, "residual", torch.bfloat16, 2)
+    if residual.shape != (rows, width):
+        raise RuntimeError("residual must be [rows, width]")
+    res_out = torch.empty_like(residual)
+    y_sel = torch.empty((sel_idx.numel(), width), dtype=x.dtype, device=x.device)
+    call("dyllm_add_rms_norm_rows", ptr(x), seg_rows, seg_pitch, ptr(residual), ptr(weight), float(eps), ptr(res_out),
+         rows, width, ptr(sel_idx), sel_idx.numel(), ptr(sel_count_dev), ptr(y_sel), stream_ptr(x.device))
+    return y_sel, res_out
+
+
 def rope_neox_(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, pos_idx: torch.Tensor | None = None,
                num_rows_dev: torch.Tensor | None = None) -> torch.Tensor:
     """In-place NeoX rotary embedding of ``x [rows, heads, 128]``.

@@ -207,13 +207,16 @@ size_t dyllm_attention_sparse_workspace_bytes(int total_q, int num_heads);
  * q, c, out: [total_q, num_heads, 128]; k, v: [total_k, num_kv_heads, 128]; o_sal: [num_salient,
  * num_heads, 128]; all bf16.  idx_salient_row_q (query space) and idx_salient_row_k (key space) hold
  * num_salient ascending rows each, grouped by sequence through cu_salientlens; pass the same list
- * twice when queries are not pruned.  num_salient_dev (nullable) is a device int32 holding the live list
+ * twice when queries are not pruned.  idx_salient_row_k may be null: the key row of a listed query row is
+ * then taken to be the row at the same distance from the end of its sequence (the queries of a sequence
+ * are its last len_q rows, as the reference's response-only steps build them).  num_salient_dev (nullable) is a device int32 holding the live list
  * length; num_salient is then only the capacity of the lists (the per-sequence counts always come from
  * cu_salientlens on the device).  The softmax scale is 1/sqrt(128).  Statistics are reduced over
  * heads in a fixed order.  v_layout is a bit set: bit 0 selects how the delta-V tile is fed to the
  * tensor cores (1 = as gathered, MN-major descriptor; 0 = transposed while gathering; results are
  * identical); bit 1 set means v is compact, [num_salient, num_kv_heads, 128] with row i belonging to
- * key idx_salient_row_k[i], instead of the zero-padded [total_k, ...] tensor (no memset, no scatter).
+ * key idx_salient_row_k[i], instead of the zero-padded [total_k, ...] tensor (no memset, no scatter);
+ * bit 2 set means cosine_stats is overwritten instead of added to (the caller need not zero-fill it).
  * Cache-resident context (c_seq_starts and c_seq_ids not null): c is then the context cache arena
  * [cache_rows, num_heads, 128] itself and the old context of query row r of batch entry b is cache row
  * c_seq_starts[c_seq_ids[b]] + len_k(b) - len_q(b) + (r - cu_seqlens_q[b]) (the last len_q rows of the
@@ -322,6 +325,18 @@ int dyllm_add_rms_norm(const void* x, const void* residual_in, const void* weigh
 int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
                                  const void* weight, float eps, void* y, void* residual_out, int rows, int width,
                                  void* stream);
+
+/* The residual add of every row and the RMSNorm of the listed rows only (the FFN of a sparse step reads
+ * nothing but the salient rows of the normalised activation):
+ *   residual_out[r] = bf16(x[r] + residual_in[r])                                 every row r < rows
+ *   y_sel[m]        = the RMSNorm of row sel_idx[m], exactly as dyllm_add_rms_norm    m < min(sel_max, *sel_count_dev)
+ * y_sel is a packed [sel_max, width] tensor in list order, i.e. the gathered FFN input.  x may be segmented
+ * as for dyllm_add_rms_norm_segmented.
+ * ref: dyllm/model_executor/models/llada.py:183-185 (post_attention_layernorm on all rows, then gather_rows_2D). */
+int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
+                            const void* weight, float eps, void* residual_out, int rows, int width,
+                            const int32_t* sel_idx, int sel_max, const int32_t* sel_count_dev, void* y_sel,
+                            void* stream);
 
 /* Confidence of the most likely token per row of bf16 logits [rows, vocab] (row pitch in elements,
  * multiple of 8): conf[r] = max_j softmax(logits[r])_j in fp32, token[r] = the first j attaining the maximum.

@@ -5,9 +5,11 @@ the residual), with the three native modules it imports replaced by the oracle's
 
 Run in the development container only (it needs the reference checkout):
 
-    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py /path/to/reference [small|c1]
+    TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py /path/to/reference [small|c1|dream|moe]
 
-"small" is a toy shape; "c1" is the single-layer LLaDA-8B configuration (hidden 4096, 32 heads of 128, FFN
+"small" is a toy LLaDA shape; "dream" a toy Dream layer (grouped-query attention, biased q/k/v; the
+reference's DreamDecoderLayer); "moe" a toy LLaDA-MoE layer (per-head q/k RMSNorm, 8 experts top-2; the
+reference's LLaDAMoEDecoderLayer with its own naive_experts loop standing for its Triton grouped GEMM); "c1" is the single-layer LLaDA-8B configuration (hidden 4096, 32 heads of 128, FFN
 intermediate 12288, one sequence of 256 prompt + 256 response positions).  The inputs are bimodal: the
 listed rows and a few more response rows change a lot between steps, all others little, and the generator
 asserts that every cosine the reference computes lies at least 1e-4 from the threshold.  A fixture holds seeds, shapes and outputs (for "c1": the
@@ -32,6 +34,13 @@ CONFIGS = {
                salient={1: [[3, 40, 41, 97, 130, 200, 255]], 2: [[0, 17, 64, 128, 129, 250]]}, extra=20, margin=1e-4,
                subset=64),
 }
+CONFIGS["dream"] = dict(shape=dict(hidden=512, heads=4, kv_heads=2, head_dim=128, inter=1024, eps=1e-6, theta=1000000.0, max_pos=512),
+                        family="dream", batch=2, prompt=24, resp=40, seq_ids=[1, 4], seed=2234, wscale=0.05,
+                        salient={1: [[1, 7, 20], [3, 33]], 2: [[2, 9], [5, 30, 31]]}, extra=5, margin=0.0, subset=None)
+CONFIGS["moe"] = dict(shape=dict(hidden=256, heads=2, kv_heads=2, head_dim=128, inter=128, eps=1e-5, theta=50000.0, max_pos=512,
+                                 experts=8, top_k=2),
+                      family="lladamoe", batch=2, prompt=24, resp=40, seq_ids=[2, 0], seed=3234, wscale=0.05,
+                      salient={1: [[1, 7, 20], [3, 33]], 2: [[2, 9], [5, 30, 31]]}, extra=5, margin=0.0, subset=None)
 TAU = 0.99
 _cfg = CONFIGS["small"]
 SHAPE, BATCH, PROMPT, RESP = _cfg["shape"], _cfg["batch"], _cfg["prompt"], _cfg["resp"]
@@ -59,6 +68,18 @@ def golden_inputs(seed=None):
         "gate_up_proj": torch.randn(2 * I, h, generator=g) * ws,
         "down_proj": torch.randn(h, I, generator=g) * ws,
     }
+    fam = _cfg.get("family", "llada")
+    if fam == "dream":          # biased q / k / v projections
+        w["q_bias"] = torch.randn(H * D, generator=g) * 0.1
+        w["kv_bias"] = torch.randn(2 * Hkv * D, generator=g) * 0.1
+    if fam == "lladamoe":       # per-head q / k norm weights, router, experts (gate rows first)
+        E = SHAPE["experts"]
+        w["q_norm"] = 1.0 + 0.1 * torch.randn(D, generator=g)
+        w["k_norm"] = 1.0 + 0.1 * torch.randn(D, generator=g)
+        w["router"] = torch.randn(E, h, generator=g) * 0.3
+        w["experts_gate_up"] = torch.randn(E, 2 * I, h, generator=g) * ws
+        w["experts_down"] = torch.randn(E, h, I, generator=g) * ws
+        del w["gate_up_proj"], w["down_proj"]
     w = {k: v.bfloat16().float() for k, v in w.items()}
     L = PROMPT + RESP
     x0 = torch.randn(BATCH * L, h, generator=g).bfloat16().float()
@@ -81,6 +102,30 @@ def step_layout(step):
         return True, False, None
     sal = [[PROMPT + o for o in seq] for seq in _cfg["salient"][step]]
     return False, step == 2, sal
+
+
+def load_layer_weights(layer, w):
+    """Copies golden_inputs() weights into a decoder layer with the reference's module tree (either
+    implementation; which tensors exist depends on the model family)."""
+    with torch.no_grad():
+        layer.self_attn.q_proj.weight.copy_(w["q_proj"])
+        layer.self_attn.kv_proj.weight.copy_(w["kv_proj"])
+        layer.self_attn.o_proj.weight.copy_(w["o_proj"])
+        if "q_bias" in w:
+            layer.self_attn.q_proj.bias.copy_(w["q_bias"])
+            layer.self_attn.kv_proj.bias.copy_(w["kv_bias"])
+        if "q_norm" in w:
+            layer.self_attn.q_norm.weight.copy_(w["q_norm"])
+            layer.self_attn.k_norm.weight.copy_(w["k_norm"])
+        if "router" in w:
+            layer.mlp.gate.weight.copy_(w["router"])
+            layer.mlp.gate_up_proj.copy_(w["experts_gate_up"])
+            layer.mlp.down_proj.copy_(w["experts_down"])
+        else:
+            layer.mlp.gate_up_proj.weight.copy_(w["gate_up_proj"])
+            layer.mlp.down_proj.weight.copy_(w["down_proj"])
+        layer.input_layernorm.weight.fill_(1.0)
+        layer.post_attention_layernorm.weight.fill_(1.0)
 
 
 def subset_rows(rows, salient_idx):
@@ -157,23 +202,38 @@ def main(ref_root, config="small"):
         return real_mask(stats, threshold)
 
     ref_attn.tensor_parallel_cosine_mask = recording_mask
-    from dyllm.model_executor.models.llada import LLaDADecoderLayer
     from dyllm.utils.context import get_context, set_context
     from dyllm.utils.metadata import get_metadata, set_metadata
 
-    cfg = types.SimpleNamespace(hidden_size=SHAPE["hidden"], num_attention_heads=SHAPE["heads"], n_kv_heads=SHAPE["kv_heads"],
-                                max_sequence_length=SHAPE["max_pos"], rms_norm_eps=SHAPE["eps"], head_dim=SHAPE["head_dim"],
-                                rope_theta=SHAPE["theta"], mlp_hidden_size=SHAPE["inter"])
-    layer = LLaDADecoderLayer(cfg, TAU).bfloat16()
+    fam = _cfg.get("family", "llada")
+    common = dict(hidden_size=SHAPE["hidden"], num_attention_heads=SHAPE["heads"], rms_norm_eps=SHAPE["eps"],
+                  head_dim=SHAPE["head_dim"], rope_theta=SHAPE["theta"])
+    if fam == "dream":
+        from dyllm.model_executor.models.dream import DreamDecoderLayer
+
+        cfg = types.SimpleNamespace(num_key_value_heads=SHAPE["kv_heads"], max_position_embeddings=SHAPE["max_pos"],
+                                    intermediate_size=SHAPE["inter"], **common)
+        layer = DreamDecoderLayer(cfg, TAU).bfloat16()
+    elif fam == "lladamoe":
+        ddist.initialize_parallel_state(1)
+        import dyllm.model_executor.layers.fused_moe as fm
+        import dyllm.model_executor.models.lladamoe as lm
+
+        # the reference's own per-expert loop (fused_moe.py:341-369) stands for its Triton grouped GEMM
+        lm.fused_experts = lambda x, w1, w2, tw, ti, activation="silu": fm.naive_experts(x, w1, w2, tw, ti, activation)
+        cfg = types.SimpleNamespace(num_key_value_heads=SHAPE["kv_heads"], max_position_embeddings=SHAPE["max_pos"],
+                                    num_experts=SHAPE["experts"], num_experts_per_tok=SHAPE["top_k"],
+                                    expert_intermediate_size=SHAPE["inter"], norm_topk_prob=False, qk_layernorm=True,
+                                    attention_bias=False, **common)
+        layer = lm.LLaDAMoEDecoderLayer(cfg, TAU).bfloat16()
+    else:
+        from dyllm.model_executor.models.llada import LLaDADecoderLayer
+
+        cfg = types.SimpleNamespace(n_kv_heads=SHAPE["kv_heads"], max_sequence_length=SHAPE["max_pos"],
+                                    mlp_hidden_size=SHAPE["inter"], **common)
+        layer = LLaDADecoderLayer(cfg, TAU).bfloat16()
     w, xs = golden_inputs()
-    with torch.no_grad():
-        layer.self_attn.q_proj.weight.copy_(w["q_proj"])
-        layer.self_attn.kv_proj.weight.copy_(w["kv_proj"])
-        layer.self_attn.o_proj.weight.copy_(w["o_proj"])
-        layer.mlp.gate_up_proj.weight.copy_(w["gate_up_proj"])
-        layer.mlp.down_proj.weight.copy_(w["down_proj"])
-        layer.input_layernorm.weight.fill_(1.0)
-        layer.post_attention_layernorm.weight.fill_(1.0)
+    load_layer_weights(layer, w)
 
     L = PROMPT + RESP
     seq_ids = _cfg["seq_ids"]
@@ -229,5 +289,5 @@ def main(ref_root, config="small"):
 
 if __name__ == "__main__":
     if len(sys.argv) < 2:
-        sys.exit("usage: make_golden.py /path/to/reference [small|c1]")
+        sys.exit("usage: make_golden.py /path/to/reference [small|c1|dream|moe]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) > 2 else "small")

@@ -258,3 +258,12 @@ def test_attention_cache_resident_context_equals_packed_path(cuda_device, case_i
         assert torch.equal(after[s0:s0 + lens_q[b]], ref_out[int(cu_q[b]):int(cu_q[b + 1])])
         touched[s0:s0 + lens_q[b]] = True
     assert torch.equal(after[~touched], before[~touched])
+    # key rows derived from the query rows (no K-space list) and statistics overwritten instead of added to:
+    # same bits, with a statistics buffer that holds garbage on entry
+    d_arena2 = d(arena)
+    stats2 = torch.full((Tq, 3), 123.0, device=cuda_device)
+    mask2 = torch.empty(Tq, dtype=torch.bool, device=cuda_device)
+    out2 = attention_sparse_varlen(d(case["q"]), d(case["k"]), d(case["dv"]), d_arena2, d(case["o_sal"]), d(cu_q), d(cu_k),
+                                   case["max_q"], case["max_k"], Tq, d(case["cu_sal"]), d(case["idx_q"]), stats2, mask2, TAU,
+                                   ro, None, v_layout=1 | 4, c_cache=(d(seq_starts), d(seq_ids), True))
+    assert torch.equal(out2.cpu(), ref_out) and torch.equal(stats2.cpu(), ref_stats) and torch.equal(mask2.cpu(), ref_mask)

@@ -83,3 +83,33 @@ def test_add_rms_norm_reads_equal_blocks_in_place(cuda_device):
     y2, r2 = ops.add_rms_norm(view, w, 1e-5, res)
     assert torch.equal(y1, y2) and torch.equal(r1, r2)
     assert torch.equal(ops.add_rms_norm(packed, w, 1e-5), ops.add_rms_norm(view, w, 1e-5))
+
+
+@pytest.mark.parametrize("rows,width,n_sel,live", [(300, 4096, 300, 37), (64, 3584, 10, 10), (2000, 2048, 1500, 1500), (16, 256, 16, 0)])
+def test_add_rms_norm_rows_equals_full_norm_on_listed_rows(cuda_device, rows, width, n_sel, live):
+    """Residual sums of every row and normalised values of the listed rows only: the same bits as the full
+    norm, packed in list order; rows past the live count are left alone."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + width)
+    dev = cuda_device
+    x = torch.randn(rows, width, generator=g).bfloat16().to(dev)
+    res = torch.randn(rows, width, generator=g).bfloat16().to(dev)
+    w = (1.0 + 0.1 * torch.randn(width, generator=g)).bfloat16().to(dev)
+    idx = torch.sort(torch.randperm(rows, generator=g)[:n_sel]).values.to(torch.int32).to(dev)
+    count = torch.tensor([live], dtype=torch.int32, device=dev)
+    y_full, res_full = ops.add_rms_norm(x, w, 1e-5, res)
+    y_sel, res_out = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, count)
+    assert torch.equal(res_out, res_full)
+    assert torch.equal(y_sel[:live], y_full[idx[:live].long()])
+    # without a device-side count the whole list is live
+    y_all, _ = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, None)
+    assert torch.equal(y_all, y_full[idx.long()])
+    # segmented input: a block of every sequence read out of a cache
+    if rows % 4 == 0:
+        seg = rows // 4
+        cache = torch.randn(4, seg + 7, width, generator=g).bfloat16().to(dev)
+        view = cache[:, 7:, :]
+        y_full, res_full = ops.add_rms_norm(view, w, 1e-5, res)
+        y_sel, res_out = ops.add_rms_norm_rows(view, w, 1e-5, res, idx, count)
+        assert torch.equal(res_out, res_full) and torch.equal(y_sel[:live], y_full[idx[:live].long()])

@@ -30,17 +30,28 @@ def _run_layer(dev, config):
     from dyllm_b200.model import LLaDADecoderLayer, LLaDAShape
 
     S = mg.SHAPE
-    cfg = LLaDAShape(hidden_size=S["hidden"], num_attention_heads=S["heads"], n_kv_heads=S["kv_heads"],
-                     head_dim=S["head_dim"], mlp_hidden_size=S["inter"], rms_norm_eps=S["eps"], rope_theta=S["theta"],
-                     max_sequence_length=S["max_pos"], num_hidden_layers=1)
-    layer = LLaDADecoderLayer(cfg, mg.TAU).to(dev).bfloat16()
+    from dyllm_b200 import model as M
+
+    family = mg.CONFIGS[config].get("family", "llada")
+    if family == "dream":
+        cfg = M.DreamShape(hidden_size=S["hidden"], num_attention_heads=S["heads"], num_key_value_heads=S["kv_heads"],
+                           head_dim=S["head_dim"], intermediate_size=S["inter"], rms_norm_eps=S["eps"],
+                           rope_theta=S["theta"], max_position_embeddings=S["max_pos"], num_hidden_layers=1)
+        layer = M.DreamDecoderLayer(cfg, mg.TAU)
+    elif family == "lladamoe":
+        cfg = M.LLaDAMoEShape(hidden_size=S["hidden"], num_attention_heads=S["heads"], num_key_value_heads=S["kv_heads"],
+                              head_dim=S["head_dim"], num_experts=S["experts"], num_experts_per_tok=S["top_k"],
+                              expert_intermediate_size=S["inter"], rms_norm_eps=S["eps"], rope_theta=S["theta"],
+                              max_position_embeddings=S["max_pos"], num_hidden_layers=1)
+        layer = M.LLaDAMoEDecoderLayer(cfg, mg.TAU)
+    else:
+        cfg = LLaDAShape(hidden_size=S["hidden"], num_attention_heads=S["heads"], n_kv_heads=S["kv_heads"],
+                         head_dim=S["head_dim"], mlp_hidden_size=S["inter"], rms_norm_eps=S["eps"], rope_theta=S["theta"],
+                         max_sequence_length=S["max_pos"], num_hidden_layers=1)
+        layer = LLaDADecoderLayer(cfg, mg.TAU)
+    layer = layer.to(dev).bfloat16()
     w, xs = mg.golden_inputs()
-    with torch.no_grad():
-        layer.self_attn.q_proj.weight.copy_(w["q_proj"])
-        layer.self_attn.kv_proj.weight.copy_(w["kv_proj"])
-        layer.self_attn.o_proj.weight.copy_(w["o_proj"])
-        layer.mlp.gate_up_proj.weight.copy_(w["gate_up_proj"])
-        layer.mlp.down_proj.weight.copy_(w["down_proj"])
+    mg.load_layer_weights(layer, {k: v.to(dev) for k, v in w.items()})
     B, P, R = mg.BATCH, mg.PROMPT, mg.RESP
     L = P + R
     seq_ids = mg.CONFIGS[config]["seq_ids"]
@@ -85,7 +96,7 @@ def _run_layer(dev, config):
     return results
 
 
-@pytest.mark.parametrize("config", ["small", "c1"])
+@pytest.mark.parametrize("config", ["small", "c1", "dream", "moe"])
 def test_decoder_layer_matches_reference_fixture(cuda_device, config):
     from dyllm_b200 import _lib
 
