@@ -34,6 +34,9 @@ int sm_count();
 // on a wait stores a non-zero code here; the host entry point that launched it reports
 // DYLLM_ERR_DEVICE_TIMEOUT on its next status query.
 int* device_status_word();            // device pointer (per device), zero-initialised
+// Per-device arrival counters for split-K output tiles (kSplitTicketCount ints, zero between launches).
+constexpr int kSplitTicketCount = 4096;
+int* split_tickets();
 int read_and_clear_device_status();   // synchronises the given stream's device; used by tests
 
 #ifdef __CUDACC__

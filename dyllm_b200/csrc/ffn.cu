@@ -67,44 +67,6 @@ stage_rows_kernel(const uint4* __restrict__ x, int64_t x_pitch_vecs, const int32
   }
 }
 
-// out[map[m]][n] = bf16(scale[m] * sum_z partial[z][m][n]) in split order (deterministic).
-__global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float* __restrict__ partial, int max_splits, int n_tiles, int slots, int num_kt,
-                     int split_rows, int n_total, int M,
-                     const int32_t* __restrict__ m_count_dev, __nv_bfloat16* __restrict__ out, int64_t ldc,
-                     const int32_t* __restrict__ out_row_map, const float* __restrict__ row_scale,
-                     __nv_bfloat16* __restrict__ out2, int64_t ldc2, int split_col) {
-  const int m_count = m_count_dev ? min(*m_count_dev, M) : M;
-  if (m_count > split_rows)
-    return;  // the GEMM wrote its results directly
-  const int splits = effective_splits((m_count + kGemmBM - 1) / kGemmBM, n_tiles, slots, max_splits, num_kt);
-  if (splits == 1)
-    return;
-  const int m = blockIdx.y;
-  if (m >= m_count)
-    return;
-  const int n = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (n >= n_total)
-    return;
-  const int out_row = out_row_map ? out_row_map[m] : m;
-  if (out_row < 0)
-    return;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int z = 0; z < splits; ++z) {
-    const float4* src =
-        reinterpret_cast<const float4*>(partial + (static_cast<int64_t>(z) * split_rows + m) * n_total + n);
-    const float4 a = __ldg(src), b = __ldg(src + 1);
-    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
-  }
-  const float scale = row_scale ? row_scale[m] : 1.0f;
-  uint4 o = make_uint4(pack_bf16x2(acc[0] * scale, acc[1] * scale), pack_bf16x2(acc[2] * scale, acc[3] * scale),
-                       pack_bf16x2(acc[4] * scale, acc[5] * scale), pack_bf16x2(acc[6] * scale, acc[7] * scale));
-  __nv_bfloat16* dst = (out2 && n >= split_col) ? out2 + static_cast<int64_t>(out_row) * ldc2 + (n - split_col)
-                                                : out + static_cast<int64_t>(out_row) * ldc + n;
-  *reinterpret_cast<uint4*>(dst) = o;
-}
-
 struct Plan {
   int tile_n;
   int splits;
@@ -203,6 +165,9 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   p.status_word = device_status_word();
   p.n_total = n;
   p.partial = plan.splits > 1 ? partial : nullptr;
+  p.split_tickets = split_tickets();
+  if (!p.split_tickets || static_cast<int64_t>(plan.grid.x) * (kSplitRows / kGemmBM) > kSplitTicketCount)
+    p.partial = nullptr;   // no counters for this many tiles: every CTA runs its whole k range
   p.split_rows = kSplitRows;
   p.split_slots = plan.slots;
 
@@ -237,14 +202,7 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   } else {
     rc = launch_mode<64, false, 8>(a_mode, ta, tb, p, plan.grid, stream);
   }
-  if (rc != DYLLM_OK || plan.splits == 1)
-    return rc;
-  const int rows = p.M < kSplitRows ? p.M : kSplitRows;
-  dim3 rgrid(cdiv_i(n, 256 * 8), rows);
-  splitk_reduce_kernel<<<rgrid, 256, 0, stream>>>(partial, plan.splits, n / plan.tile_n, plan.slots, p.K / kGemmBK,
-                                                  kSplitRows, n, p.M, p.m_count_dev, p.out, p.ldc,
-                                                  p.out_row_map, p.row_scale, p.out2, p.ldc2, p.split_col);
-  return check_launch("splitk_reduce");
+  return rc;
 }
 
 int stage_rows(const void* x, int64_t ldx, const int32_t* idx, int x_rows, void* compact, int width, int num_rows,

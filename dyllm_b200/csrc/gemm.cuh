@@ -39,6 +39,7 @@ struct GemmParams {
   int64_t ldc2;
   int split_col;
   float* partial;              // split-K: fp32 [gridDim.z][split_rows][n_total]; null = no split-K
+  int* split_tickets;          // split-K: arrival counter per (row tile, column tile), zero between launches
   int split_rows;              // split-K is used only while the live row count is <= split_rows
   int split_slots;             // CTAs the device runs at once; the live split count is derived from it
   int n_total;                 // output columns (row pitch of `partial`)
@@ -104,10 +105,11 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int num_kt_all = p.K / BK;
   int kt_begin = 0, kt_end = num_kt_all;
   bool write_partial = false;
+  int splits = 1;
   if (p.partial != nullptr) {
-    const int splits = m_count <= p.split_rows
-                           ? effective_splits((m_count + BM - 1) / BM, gridDim.x, p.split_slots, gridDim.z, num_kt_all)
-                           : 1;
+    splits = m_count <= p.split_rows
+                 ? effective_splits((m_count + BM - 1) / BM, gridDim.x, p.split_slots, gridDim.z, num_kt_all)
+                 : 1;
     if (static_cast<int>(blockIdx.z) >= splits)
       return;
     if (splits > 1) {
@@ -127,6 +129,7 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   __shared__ uint64_t tmem_empty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int last_split;   // split-K: this CTA was the last to finish the current output tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -303,6 +306,38 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                                    __uint_as_float(g[8 * i + 2 * j + 1]) * scale);
               d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
             }
+          }
+        }
+      }
+      if (!SWIGLU && MT == 1 && write_partial) {
+        // Split-K: the CTA that finishes an output tile last adds the splits' partial sums in split order
+        // (the same order whichever CTA is last: deterministic) and writes the tile.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          int* ticket = p.split_tickets + mt * gridDim.x + n_tile;
+          const int t = atomicAdd(ticket, 1);
+          last_split = (t == splits - 1) ? 1 : 0;
+          if (t == splits - 1)
+            *ticket = 0;   // every split has arrived: ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (last_split && store) {
+          __threadfence();
+          const float* src0 = p.partial + static_cast<int64_t>(m) * p.n_total + n0;
+          const int64_t zstride = static_cast<int64_t>(p.split_rows) * p.n_total;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BNH; c0 += 8) {
+            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int z = 0; z < splits; ++z) {
+              const float4* src = reinterpret_cast<const float4*>(src0 + z * zstride + c0);
+              const float4 a = __ldcg(src), b = __ldcg(src + 1);
+              acc8[0] += a.x; acc8[1] += a.y; acc8[2] += a.z; acc8[3] += a.w;
+              acc8[4] += b.x; acc8[5] += b.y; acc8[6] += b.z; acc8[7] += b.w;
+            }
+            *reinterpret_cast<uint4*>(dst + c0) =
+                make_uint4(pack_bf16x2(acc8[0] * scale, acc8[1] * scale), pack_bf16x2(acc8[2] * scale, acc8[3] * scale),
+                           pack_bf16x2(acc8[4] * scale, acc8[5] * scale), pack_bf16x2(acc8[6] * scale, acc8[7] * scale));
           }
         }
       }

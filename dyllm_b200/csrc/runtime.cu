@@ -14,9 +14,13 @@ thread_local char g_error[512] = {0};
 constexpr int kMaxDevices = 64;
 int g_sm_count[kMaxDevices] = {0};
 int* g_status_word[kMaxDevices] = {nullptr};
+int* g_split_tickets_ptr[kMaxDevices] = {nullptr};
 std::mutex g_mutex;
 // One status word per device that loads this library (zero-initialised by the loader).
 __device__ int g_device_status = 0;
+// Arrival counters of the split-K GEMMs (one per output tile): zero between launches; the last CTA to
+// arrive at a tile adds the splits' partial sums and resets the counter.
+__device__ int g_split_tickets[kSplitTicketCount] = {0};
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -79,6 +83,18 @@ int* device_status_word() {
     g_status_word[dev] = static_cast<int*>(p);
   }
   return g_status_word[dev];
+}
+
+int* split_tickets() {
+  const int dev = current_device();
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_split_tickets_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_split_tickets) != cudaSuccess)
+      return nullptr;
+    g_split_tickets_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_split_tickets_ptr[dev];
 }
 
 int read_and_clear_device_status() {

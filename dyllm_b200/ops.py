@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import torch
 
+from . import _lib as _lib_mod
 from ._lib import call, load, ptr, require_cuda, stream_ptr
 
 
@@ -175,6 +176,8 @@ def swiglu_ffn(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, i
     call("dyllm_swiglu_ffn", ptr(x), x.size(0), hidden, x.stride(0), ptr(idx), num_rows, ptr(num_rows_dev),
          int(rows_hint), ptr(w_gate_up), ptr(w_down), inter, ptr(out), out.stride(0), ptr(out_row_map), ptr(ws),
          ws.numel(), a_mode, tile_n, stream_ptr(x.device))
+    if idx is None:
+        _lib_mod.launch_count -= 1      # no row staging launch when the rows arrive packed
     return out
 
 

@@ -159,7 +159,10 @@ size_t dyllm_gathered_linear_workspace_bytes(int max_rows, int in_features, int 
  * out_row_map null = m (negative entries drop the row), row_scale null = 1.  When out2 is not null,
  * output columns >= split_col (a multiple of 128) go to out2[.., column - split_col] instead (used to
  * write K and V of the fused K/V projection into two tensors).  in_features % 64 == 0,
- * out_features % 64 == 0.  Few rows and few column tiles switch on a deterministic split-K.
+ * out_features % 64 == 0.  Few rows and few column tiles switch on a deterministic split-K: the k range is
+ * cut into at most 4 parts whose fp32 partial sums go to the workspace, and the CTA that finishes an output
+ * tile last adds them in split order inside the same launch (arrival counters live in a small array inside
+ * the library, so two split-K calls on one device must not overlap on the GPU: issue them on one stream).
  * ref: dyllm/model_executor/models/llada.py:108 (kv_proj(hidden_states[idx_salient_row])),
  *      dyllm/model_executor/layers/linear.py:50-51. */
 int dyllm_gathered_linear(const void* x, int x_rows, int in_features, int64_t ldx, const int32_t* idx,
