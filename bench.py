@@ -379,7 +379,8 @@ def run_ours(args, cfg, tau):
     model, shape = build_model(cfg, tau, dev, args.layers, args.ep)
     dsteps = args.denoise_steps or cfg["steps"]
     full_steps = dsteps if tau is None else (args.full_steps if args.full_steps is not None else cfg["full"])
-    sr = runner.StepRunner(model, shape.mask_token_id, cfg["block"], dsteps, full_steps, REFRESH)
+    sr = runner.StepRunner(model, shape.mask_token_id, cfg["block"], dsteps, full_steps, REFRESH,
+                           graph_rows_hint=args.rows_hint or runner.GRAPH_ROWS_HINT)
     g = torch.Generator().manual_seed(1)
     prompts = torch.randint(0, shape.vocab_size - 1024, (B, P), generator=g).tolist()
 
@@ -537,6 +538,8 @@ def main():
                     help="several GPUs: 'tensor' = the reference's layout (heads and FFN columns sharded, rows replicated, "
                          "three all-reduces per layer); 'sequence' = every rank owns whole sequences, only the FFN weights "
                          "are sharded and only salient rows travel (auto: sequence when the batch divides evenly)")
+    ap.add_argument("--rows-hint", type=int, default=0,
+                    help="salient rows per layer the captured steps are shaped for (default 128; any value is correct)")
     ap.add_argument("--no-tp-parity", action="store_true", help="skip the sharded-vs-unsharded layer self-check")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers marks the line invalid")
     ap.add_argument("--denoise-steps", type=int, default=0, help="debug only")

@@ -49,7 +49,7 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_delta_v_update": (I, [P, P, P, I, P, I, P, P]),
     "dyllm_add_rms_norm": (I, [P, P, P, F, P, P, I, I, P]),
     "dyllm_add_rms_norm_segmented": (I, [P, I, c_int64, P, P, F, P, P, I, I, P]),
-    "dyllm_add_rms_norm_rows": (I, [P, I, c_int64, P, P, F, P, I, I, P, I, P, P, P]),
+    "dyllm_add_rms_norm_rows": (I, [P, I, c_int64, P, P, F, P, P, I, I, P, I, P, P, P]),
     "dyllm_rope_neox": (I, [P, P, P, P, I, P, I, I, I, P]),
     "dyllm_row_confidence": (I, [P, I, I, c_int64, P, P, P]),
     "dyllm_kv_cache_update": (I, [P, P, P, P, P, P, I, P, P, P, P, I, I, P, I, I, P, P, P, P]),

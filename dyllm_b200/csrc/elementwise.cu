@@ -95,20 +95,22 @@ add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_i
                     res_out ? res_out + row * vecs : nullptr, vecs, inv_width, eps);
 }
 
-// The same arithmetic when only the listed rows' normalised values are needed (the FFN of a sparse step
-// reads the salient rows alone): blocks [0, rows) write the residual sum of their row, the remaining blocks
-// walk the list and write the normalised row m to y_sel[m], ready to be the FFN's packed input.
+// The same arithmetic with the listed rows' normalised values also (or only) written packed in list order:
+// blocks [0, rows) handle their row (residual sum; normalised row when y_all is given), the remaining blocks
+// walk the list and write the normalised row sel_idx[m] to y_sel[m], ready to be the packed input of a
+// gathered GEMM (the FFN of a sparse step reads the salient rows alone; its K/V projection likewise).
 template <int VPT>
 __global__ void __launch_bounds__(kNormThreads)
 add_rms_norm_rows_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
-                         uint4* __restrict__ y_sel, uint4* __restrict__ res_out, int rows, int vecs, float inv_width,
+                         uint4* __restrict__ y_all, uint4* __restrict__ y_sel, uint4* __restrict__ res_out, int rows,
+                         int vecs, float inv_width,
                          float eps, int x_seg_rows, int64_t x_seg_pitch_rows, const int32_t* __restrict__ sel_idx,
                          int sel_max, const int32_t* __restrict__ sel_count_dev) {
   if (static_cast<int>(blockIdx.x) < rows) {
     const int64_t row = blockIdx.x;
     const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
-    norm_one_row<VPT>(x + x_row * vecs, res_in ? res_in + row * vecs : nullptr, w, nullptr, res_out + row * vecs, vecs,
-                      inv_width, eps);
+    norm_one_row<VPT>(x + x_row * vecs, res_in ? res_in + row * vecs : nullptr, w, y_all ? y_all + row * vecs : nullptr,
+                      res_out ? res_out + row * vecs : nullptr, vecs, inv_width, eps);
     return;
   }
   const int count = sel_count_dev ? min(sel_max, *sel_count_dev) : sel_max;
@@ -289,7 +291,7 @@ int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pi
 }
 
 int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
-                            const void* weight, float eps, void* residual_out, int rows, int width,
+                            const void* weight, float eps, void* y_all, void* residual_out, int rows, int width,
                             const int32_t* sel_idx, int sel_max, const int32_t* sel_count_dev, void* y_sel,
                             void* stream) {
   DYLLM_REQUIRE(rows >= 0 && width > 0 && sel_max >= 0, DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm_rows: rows %d width %d",
@@ -301,11 +303,11 @@ int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_r
                 "add_rms_norm_rows: width %d must be a multiple of 8 and at most %d", width, 8 * kNormThreads * 4);
   if (rows == 0)
     return DYLLM_OK;
-  DYLLM_REQUIRE(x && weight && residual_out && (sel_max == 0 || (sel_idx && y_sel)), DYLLM_ERR_INVALID_ARGUMENT,
-                "add_rms_norm_rows: null pointer");
+  DYLLM_REQUIRE(x && weight && (y_all || residual_out) && (sel_max == 0 || (sel_idx && y_sel)),
+                DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm_rows: null pointer");
   DYLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual_in) |
                   reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y_sel) |
-                  reinterpret_cast<uintptr_t>(residual_out)) & 15) == 0,
+                  reinterpret_cast<uintptr_t>(y_all) | reinterpret_cast<uintptr_t>(residual_out)) & 15) == 0,
                 DYLLM_ERR_INVALID_ARGUMENT, "add_rms_norm_rows: buffers must be 16-byte aligned");
   const int vecs = width / 8;
   const int vpt = cdiv_i(vecs, kNormThreads);
@@ -314,14 +316,16 @@ int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_r
   const uint4* rp = static_cast<const uint4*>(residual_in);
   const uint4* wp = static_cast<const uint4*>(weight);
   uint4* yp = static_cast<uint4*>(y_sel);
+  uint4* yap = static_cast<uint4*>(y_all);
   uint4* rop = static_cast<uint4*>(residual_out);
   const float inv = 1.0f / static_cast<float>(width);
   // the list is walked by at most 1024 blocks (each takes the entries blockIdx, blockIdx + n, ...)
   const int sel_blocks = sel_max < 1024 ? sel_max : 1024;
   const unsigned grid = static_cast<unsigned>(rows + sel_blocks);
 #define DYLLM_NORM_ROWS(V)                                                                                         \
-  add_rms_norm_rows_kernel<V><<<grid, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, rows, vecs, inv, eps, x_seg_rows, \
-                                                            x_seg_pitch_rows, sel_idx, sel_max, sel_count_dev)
+  add_rms_norm_rows_kernel<V><<<grid, kNormThreads, 0, s>>>(xp, rp, wp, yap, yp, rop, rows, vecs, inv, eps,       \
+                                                            x_seg_rows, x_seg_pitch_rows, sel_idx, sel_max,       \
+                                                            sel_count_dev)
   switch (vpt) {
     case 1: DYLLM_NORM_ROWS(1); break;
     case 2: DYLLM_NORM_ROWS(2); break;

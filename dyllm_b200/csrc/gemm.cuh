@@ -322,22 +322,48 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             *ticket = 0;   // every split has arrived: ready for the next launch
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (last_split && store) {
+        if (last_split) {
+          // all 128 epilogue threads share the live rows: 8 threads per row (32 bytes of fp32 each), 16 rows per
+          // pass, the splits' loads of a pass all in flight at once
           __threadfence();
-          const float* src0 = p.partial + static_cast<int64_t>(m) * p.n_total + n0;
+          const int t = threadIdx.x - 64;
+          const int cg = (t & 7) * 8, r0 = t >> 3;
+          const int rows_live = min(kGemmBM, m_count - mt * BM);
           const int64_t zstride = static_cast<int64_t>(p.split_rows) * p.n_total;
-#pragma unroll 1
-          for (int c0 = 0; c0 < BNH; c0 += 8) {
-            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int z = 0; z < splits; ++z) {
-              const float4* src = reinterpret_cast<const float4*>(src0 + z * zstride + c0);
-              const float4 a = __ldcg(src), b = __ldcg(src + 1);
-              acc8[0] += a.x; acc8[1] += a.y; acc8[2] += a.z; acc8[3] += a.w;
-              acc8[4] += b.x; acc8[5] += b.y; acc8[6] += b.z; acc8[7] += b.w;
+          for (int r = r0; r < rows_live; r += 16) {
+            const int mr = mt * BM + r;
+            const int orow = p.out_row_map ? p.out_row_map[mr] : mr;
+            if (orow < 0)
+              continue;
+            const float sc = p.row_scale ? p.row_scale[mr] : 1.0f;
+            __nv_bfloat16* drow = (p.out2 && n0 >= p.split_col)
+                                      ? p.out2 + static_cast<int64_t>(orow) * p.ldc2 + (n0 - p.split_col)
+                                      : p.out + static_cast<int64_t>(orow) * p.ldc + n0;
+            const float* srow = p.partial + static_cast<int64_t>(mr) * p.n_total + n0;
+#pragma unroll
+            for (int c0 = 0; c0 < BNH; c0 += 64) {
+              float4 va[4], vb[4];
+#pragma unroll
+              for (int z = 0; z < 4; ++z) {
+                if (z < splits) {
+                  const float4* src = reinterpret_cast<const float4*>(srow + z * zstride + c0 + cg);
+                  va[z] = __ldcg(src);
+                  vb[z] = __ldcg(src + 1);
+                } else {
+                  va[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                  vb[z] = va[z];
+                }
+              }
+              float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+              for (int z = 0; z < 4; ++z) {   // split order: the same sum whichever CTA arrives last
+                acc8[0] += va[z].x; acc8[1] += va[z].y; acc8[2] += va[z].z; acc8[3] += va[z].w;
+                acc8[4] += vb[z].x; acc8[5] += vb[z].y; acc8[6] += vb[z].z; acc8[7] += vb[z].w;
+              }
+              *reinterpret_cast<uint4*>(drow + c0 + cg) =
+                  make_uint4(pack_bf16x2(acc8[0] * sc, acc8[1] * sc), pack_bf16x2(acc8[2] * sc, acc8[3] * sc),
+                             pack_bf16x2(acc8[4] * sc, acc8[5] * sc), pack_bf16x2(acc8[6] * sc, acc8[7] * sc));
             }
-            *reinterpret_cast<uint4*>(dst + c0) =
-                make_uint4(pack_bf16x2(acc8[0] * scale, acc8[1] * scale), pack_bf16x2(acc8[2] * scale, acc8[3] * scale),
-                           pack_bf16x2(acc8[4] * scale, acc8[5] * scale), pack_bf16x2(acc8[6] * scale, acc8[7] * scale));
           }
         }
       }

@@ -222,10 +222,11 @@ class ColumnParallelLinear(LinearBase):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return F.linear(x, self.weight, self.bias)
 
-    def forward_gathered(self, x: torch.Tensor, idx32: torch.Tensor, num_rows: int, num_rows_dev=None,
+    def forward_gathered(self, x: torch.Tensor, idx32: torch.Tensor | None, num_rows: int, num_rows_dev=None,
                          rows_hint: int = 0, split_col: int = 0):
         """``self(x[idx])`` on the tcgen05 GEMM; ``num_rows`` may be a capacity with the live count on the
-        device.  With ``split_col`` the output columns are returned as two tensors (K and V halves)."""
+        device.  ``idx32`` None: ``x`` already holds the rows packed in list order.  With ``split_col`` the
+        output columns are returned as two tensors (K and V halves)."""
         n_out = self.weight.size(0)
         if split_col:
             out = torch.empty((num_rows, split_col), dtype=x.dtype, device=x.device)
@@ -318,7 +319,18 @@ class RMSNorm(nn.Module):
         FFN of the salient rows and nothing else (ref: dyllm/model_executor/models/llada.py:183-185)."""
         if x.dim() == 2:
             x = x.contiguous()
-        return ops.add_rms_norm_rows(x, self.weight, self.eps, residual, sel_idx32, sel_count_dev)
+        y_sel, res_out, _ = ops.add_rms_norm_rows(x, self.weight, self.eps, residual, sel_idx32, sel_count_dev)
+        return y_sel, res_out
+
+    def forward_with_rows(self, x: torch.Tensor, residual: torch.Tensor | None, sel_idx32: torch.Tensor, sel_count_dev=None):
+        """The full norm plus the listed rows packed in list order: ``(y, new_residual or None, y_sel)``.  What a
+        sparse step needs of the input norm: every row feeds q_proj, the salient rows also feed kv_proj
+        (ref: dyllm/model_executor/models/llada.py:103,108)."""
+        if x.dim() == 2:
+            x = x.contiguous()
+        y_sel, res_out, y_all = ops.add_rms_norm_rows(x, self.weight, self.eps, residual, sel_idx32, sel_count_dev,
+                                                      all_rows=True)
+        return y_all, res_out, y_sel
 
 
 class RotaryEmbedding(nn.Module):

@@ -71,7 +71,9 @@ class LLaDAAttention(nn.Module):
         self.rotary_emb = rotary_emb or RotaryEmbedding(self.head_dim, self.head_dim, max_position, rope_theta)
         self.attn = Attention(self.num_heads, self.head_dim, self.scaling, self.num_kv_heads, threshold)
 
-    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor) -> torch.Tensor:
+    def forward(self, positions: torch.Tensor, hidden_states: torch.Tensor, salient_rows=None) -> torch.Tensor:
+        """``salient_rows`` (sparse steps, optional): the normalised hidden rows of the step's salient tokens,
+        packed in list order (``RMSNorm.forward_with_rows``); the K/V projection then reads them directly."""
         ctx, md = get_context(), get_metadata()
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         q = self.q_proj(hidden_states)
@@ -93,8 +95,11 @@ class LLaDAAttention(nn.Module):
             q = self.rotary_emb.rotate(positions, q)
             dv = None
             if cap:
-                k_new, v_new = self.kv_proj.forward_gathered(hidden_states, ctx.idx_salient_row32, cap, n_dev, hint,
-                                                             split_col=self.kv_size)
+                if salient_rows is not None:
+                    k_new, v_new = self.kv_proj.forward_gathered(salient_rows, None, cap, n_dev, hint, split_col=self.kv_size)
+                else:
+                    k_new, v_new = self.kv_proj.forward_gathered(hidden_states, ctx.idx_salient_row32, cap, n_dev, hint,
+                                                                 split_col=self.kv_size)
                 rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
                 if self.k_norm is not None:
                     k_new = self.k_norm(k_new.view(-1, D))       # rows past the live count hold nothing of value
@@ -111,6 +116,23 @@ class LLaDAAttention(nn.Module):
         out = self.o_proj(o.flatten(-2, -1))
         self.k_cache.finish(md.finished_seqs)
         return out
+
+
+def _input_norm(layer, hidden_states, residual):
+    """First norm of a decoder layer (ref: llada.py:176-179).  In a sparse step the salient rows (the list the
+    previous layer published) also come out packed for the K/V projection.  Returns (normalised, residual,
+    packed salient rows or None)."""
+    ctx = get_context()
+    idx32 = None if ctx.is_full else ctx.idx_salient_row32
+    if idx32 is not None and idx32.numel():
+        y, res_out, packed = layer.input_layernorm.forward_with_rows(hidden_states, residual, idx32, ctx.num_salient_dev)
+        if residual is None:      # first layer: the residual stream starts as the embedding
+            res_out = hidden_states if hidden_states.dim() == 2 else hidden_states.reshape(-1, hidden_states.size(-1))
+        return y, res_out, packed
+    if residual is None:
+        return layer.input_layernorm(hidden_states), hidden_states, None
+    y, res_out = layer.input_layernorm(hidden_states, residual)
+    return y, res_out, None
 
 
 def _post_attention(layer, hidden_states, residual):
@@ -142,11 +164,8 @@ class LLaDADecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
     def forward(self, positions, hidden_states, residual=None):
-        if residual is None:
-            hidden_states, residual = self.input_layernorm(hidden_states), hidden_states
-        else:
-            hidden_states, residual = self.input_layernorm(hidden_states, residual)
-        hidden_states = self.self_attn(positions, hidden_states)
+        hidden_states, residual, packed = _input_norm(self, hidden_states, residual)
+        hidden_states = self.self_attn(positions, hidden_states, packed)
         return _post_attention(self, hidden_states, residual)
 
 
@@ -226,11 +245,8 @@ class _DecoderLayer(nn.Module):
     rows through the step's index list (sparse step)."""
 
     def forward(self, positions, hidden_states, residual=None):
-        if residual is None:
-            hidden_states, residual = self.input_layernorm(hidden_states), hidden_states
-        else:
-            hidden_states, residual = self.input_layernorm(hidden_states, residual)
-        hidden_states = self.self_attn(positions, hidden_states)
+        hidden_states, residual, packed = _input_norm(self, hidden_states, residual)
+        hidden_states = self.self_attn(positions, hidden_states, packed)
         return _post_attention(self, hidden_states, residual)
 
 

@@ -260,13 +260,14 @@ def add_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: to
     return y if residual is None else (y, res_out)
 
 
-def add_rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor, sel_idx: torch.Tensor,
-                      sel_count_dev: torch.Tensor | None = None):
-    """Residual add of every row, RMSNorm of the listed rows only: returns ``(y_sel [len(sel_idx), width],
-    new_residual [rows, width])`` where ``y_sel[m]`` is the normalised row ``sel_idx[m]`` (the packed FFN input of
-    a sparse step).  ``x`` as for :func:`add_rms_norm`.
+def add_rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: torch.Tensor | None,
+                      sel_idx: torch.Tensor, sel_count_dev: torch.Tensor | None = None, all_rows: bool = False):
+    """RMSNorm (with the residual add) whose listed rows also come out packed in list order.  Returns
+    ``(y_sel [len(sel_idx), width], new_residual [rows, width] or None, y_all [rows, width] or None)``: ``y_sel[m]`` is
+    the normalised row ``sel_idx[m]`` (the packed input of a gathered GEMM), ``new_residual`` exists when a residual
+    came in, ``y_all`` only with ``all_rows``.  ``x`` as for :func:`add_rms_norm`.
 
-    ref: dyllm/model_executor/models/llada.py:183-185.
+    ref: dyllm/model_executor/models/llada.py:176-185.
     """
     if not isinstance(x, torch.Tensor) or not x.is_cuda or x.dtype != torch.bfloat16:
         raise RuntimeError("x must be a CUDA bfloat16 tensor")
@@ -281,14 +282,19 @@ def add_rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, residua
         rows, seg_rows, seg_pitch = x.size(0) * x.size(1), x.size(1), x.stride(0) // width
     else:
         raise RuntimeError("x must be [rows, width] contiguous or [segments, rows, width] with contiguous rows")
-    require_cuda(residual, "residual", torch.bfloat16, 2)
-    if residual.shape != (rows, width):
-        raise RuntimeError("residual must be [rows, width]")
-    res_out = torch.empty_like(residual)
+    res_out = None
+    if residual is not None:
+        require_cuda(residual, "residual", torch.bfloat16, 2)
+        if residual.shape != (rows, width):
+            raise RuntimeError("residual must be [rows, width]")
+        res_out = torch.empty_like(residual)
+    elif not all_rows:
+        raise RuntimeError("without a residual the normalised rows are the only output: pass all_rows=True")
+    y_all = torch.empty((rows, width), dtype=x.dtype, device=x.device) if all_rows else None
     y_sel = torch.empty((sel_idx.numel(), width), dtype=x.dtype, device=x.device)
-    call("dyllm_add_rms_norm_rows", ptr(x), seg_rows, seg_pitch, ptr(residual), ptr(weight), float(eps), ptr(res_out),
-         rows, width, ptr(sel_idx), sel_idx.numel(), ptr(sel_count_dev), ptr(y_sel), stream_ptr(x.device))
-    return y_sel, res_out
+    call("dyllm_add_rms_norm_rows", ptr(x), seg_rows, seg_pitch, ptr(residual), ptr(weight), float(eps), ptr(y_all),
+         ptr(res_out), rows, width, ptr(sel_idx), sel_idx.numel(), ptr(sel_count_dev), ptr(y_sel), stream_ptr(x.device))
+    return y_sel, res_out, y_all
 
 
 def rope_neox_(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, pos_idx: torch.Tensor | None = None,

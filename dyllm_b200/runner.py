@@ -186,7 +186,7 @@ class StepRunner:
 
     def __init__(self, model, mask_id: int, block_length: int = 32, steps: int = 256, num_full_steps: int = 8,
                  refresh_period: int = 4, use_graphs: bool = True, full_logits: bool = False,
-                 graphs_with_tp: bool | None = None):
+                 graphs_with_tp: bool | None = None, graph_rows_hint: int = GRAPH_ROWS_HINT):
         self.model = model
         self.mask_id = mask_id
         self.block_length = block_length
@@ -196,6 +196,9 @@ class StepRunner:
         self.device = next(model.parameters()).device
         self.salient_counts: list[int] = []
         self.use_graphs = use_graphs
+        # salient-row estimate baked into the launches of a captured step (any value is correct; the GEMMs are
+        # shaped for it: narrow tiles and split-K up to a few hundred rows, wide and tall tiles above)
+        self.graph_rows_hint = max(1, int(graph_rows_hint))
         # With several ranks a step is captured whole, NCCL all-reduces and peer-memory exchanges included
         # (DYLLM_TP_GRAPHS=whole, the default).  NCCL keeps a communicator alive for as long as a graph that
         # captured one of its collectives exists, and destroying the process group waits for that: call
@@ -408,7 +411,7 @@ class StepRunner:
             if key not in self._warm:
                 # same launch shapes as the capture that follows, so that every kernel it needs is loaded
                 self._warm.add(key)
-                st.fixed_hint = GRAPH_ROWS_HINT
+                st.fixed_hint = self.graph_rows_hint
                 try:
                     self._device_step(st, kind)
                 finally:
@@ -417,7 +420,7 @@ class StepRunner:
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             before = _lib.launch_count
-            st.fixed_hint = GRAPH_ROWS_HINT
+            st.fixed_hint = self.graph_rows_hint
             try:
                 if _multi_rank() and self.tp_graph_mode == "segmented":
                     graph = _SegmentedCapture(self._graph_pool)

@@ -329,15 +329,17 @@ int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pi
                                  const void* weight, float eps, void* y, void* residual_out, int rows, int width,
                                  void* stream);
 
-/* The residual add of every row and the RMSNorm of the listed rows only (the FFN of a sparse step reads
- * nothing but the salient rows of the normalised activation):
- *   residual_out[r] = bf16(x[r] + residual_in[r])                                 every row r < rows
- *   y_sel[m]        = the RMSNorm of row sel_idx[m], exactly as dyllm_add_rms_norm    m < min(sel_max, *sel_count_dev)
- * y_sel is a packed [sel_max, width] tensor in list order, i.e. the gathered FFN input.  x may be segmented
- * as for dyllm_add_rms_norm_segmented.
- * ref: dyllm/model_executor/models/llada.py:183-185 (post_attention_layernorm on all rows, then gather_rows_2D). */
+/* The add-RMSNorm with the listed rows' normalised values also written packed in list order (the input of a
+ * gathered GEMM of a sparse step, which then needs no row-staging launch):
+ *   residual_out[r] = bf16(x[r] + residual_in[r])                 every row r < rows (nullable)
+ *   y_all[r]        = the RMSNorm of row r, as dyllm_add_rms_norm     every row (nullable: the post-attention norm of
+ *                     a sparse step feeds the FFN of the salient rows and nothing else)
+ *   y_sel[m]        = the RMSNorm of row sel_idx[m]                   m < min(sel_max, *sel_count_dev)
+ * y_sel is a packed [sel_max, width] tensor.  x may be segmented as for dyllm_add_rms_norm_segmented.
+ * ref: dyllm/model_executor/models/llada.py:176-185 (both norms of a layer, hidden_states[idx_salient_row] and
+ *      gather_rows_2D after them). */
 int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_rows, const void* residual_in,
-                            const void* weight, float eps, void* residual_out, int rows, int width,
+                            const void* weight, float eps, void* y_all, void* residual_out, int rows, int width,
                             const int32_t* sel_idx, int sel_max, const int32_t* sel_count_dev, void* y_sel,
                             void* stream);
 

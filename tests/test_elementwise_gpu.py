@@ -99,17 +99,24 @@ def test_add_rms_norm_rows_equals_full_norm_on_listed_rows(cuda_device, rows, wi
     idx = torch.sort(torch.randperm(rows, generator=g)[:n_sel]).values.to(torch.int32).to(dev)
     count = torch.tensor([live], dtype=torch.int32, device=dev)
     y_full, res_full = ops.add_rms_norm(x, w, 1e-5, res)
-    y_sel, res_out = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, count)
-    assert torch.equal(res_out, res_full)
+    y_sel, res_out, none = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, count)
+    assert none is None and torch.equal(res_out, res_full)
     assert torch.equal(y_sel[:live], y_full[idx[:live].long()])
     # without a device-side count the whole list is live
-    y_all, _ = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, None)
-    assert torch.equal(y_all, y_full[idx.long()])
+    y_list, _, _ = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, None)
+    assert torch.equal(y_list, y_full[idx.long()])
+    # every row normalised as well (the input norm of a sparse step), with and without a residual
+    y_sel, res_out, y_all = ops.add_rms_norm_rows(x, w, 1e-5, res, idx, count, all_rows=True)
+    assert torch.equal(y_all, y_full) and torch.equal(res_out, res_full) and torch.equal(y_sel[:live], y_full[idx[:live].long()])
+    y_plain = ops.add_rms_norm(x, w, 1e-5)
+    y_sel, res_out, y_all = ops.add_rms_norm_rows(x, w, 1e-5, None, idx, count, all_rows=True)
+    assert res_out is None and torch.equal(y_all, y_plain) and torch.equal(y_sel[:live], y_plain[idx[:live].long()])
     # segmented input: a block of every sequence read out of a cache
     if rows % 4 == 0:
         seg = rows // 4
         cache = torch.randn(4, seg + 7, width, generator=g).bfloat16().to(dev)
         view = cache[:, 7:, :]
         y_full, res_full = ops.add_rms_norm(view, w, 1e-5, res)
-        y_sel, res_out = ops.add_rms_norm_rows(view, w, 1e-5, res, idx, count)
+        y_sel, res_out, y_all = ops.add_rms_norm_rows(view, w, 1e-5, res, idx, count, all_rows=True)
         assert torch.equal(res_out, res_full) and torch.equal(y_sel[:live], y_full[idx[:live].long()])
+        assert torch.equal(y_all, y_full)
