@@ -205,6 +205,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_out,
                  const __grid_constant__ CUtensorMap tmap_c, const AttnParams p) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;                      // Q tile
@@ -884,6 +886,8 @@ constexpr uint32_t kSmallSmem = kSmallStages * kTileBytes + 3 * kSalBytes + 1024
 __global__ void __launch_bounds__(kAttnThreads, 2)
 salient_rows_small_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                           const AttnParams p) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int b = blockIdx.x / p.H, h = blockIdx.x % p.H;
   const int sal_begin = p.cu_sal[b];
   const int n_sal = p.cu_sal[b + 1] - sal_begin;
@@ -1142,6 +1146,8 @@ __device__ __forceinline__ bool mask_rule(float dot, float a, float b, float thr
 __global__ void __launch_bounds__(256)
 attention_finalize_kernel(const float* __restrict__ partial, int H, int Tq, float* __restrict__ stats,
                           uint8_t* __restrict__ mask, float threshold, int accumulate) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= Tq)
     return;
@@ -1186,7 +1192,7 @@ int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
   // persistent grid: as many CTAs as the device runs at once (two per SM)
   const int64_t resident = 2ll * sm_count();
   const unsigned blocks = static_cast<unsigned>(items < resident ? items : resident);
-  attention_kernel<EXACT><<<blocks, kAttnThreads, kAttnSmem, s>>>(tq, tk, tv, tout, tc, p);
+  DYLLM_LAUNCH(attention_kernel<EXACT>, blocks, kAttnThreads, kAttnSmem, s, tq, tk, tv, tout, tc, p);
   return check_launch(EXACT ? "salient_attention" : "delta_attention");
 }
 
@@ -1294,7 +1300,7 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
   rc = launch_attention<false>(tq, tk, tk, tout, tc, p, blocks, s);
   if (rc != DYLLM_OK)
     return rc;
-  attention_finalize_kernel<<<cdiv_i(total_q, 256), 256, 0, s>>>(p.partial, num_heads, total_q, cosine_stats,
+  DYLLM_LAUNCH(attention_finalize_kernel, cdiv_i(total_q, 256), 256, 0, s, p.partial, num_heads, total_q, cosine_stats,
                                                                  cosine_out, threshold, (v_layout & 4) ? 0 : 1);
   return check_launch("attention_finalize");
 }
@@ -1358,8 +1364,7 @@ int dyllm_attention_salient_rows(const void* q, const void* k, const void* v, vo
                          cudaGetErrorString(cudaGetLastError()));
       smem_set[dev] = true;
     }
-    salient_rows_small_kernel<<<static_cast<unsigned>(batch) * num_heads, kAttnThreads, kSmallSmem,
-                                static_cast<cudaStream_t>(stream)>>>(tk, tv, p);
+    DYLLM_LAUNCH(salient_rows_small_kernel, static_cast<unsigned>(batch) * num_heads, kAttnThreads, kSmallSmem, static_cast<cudaStream_t>(stream), tk, tv, p);
     rc = check_launch("salient_rows_small");
     if (rc != DYLLM_OK)
       return rc;

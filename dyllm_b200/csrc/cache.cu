@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(kCopyWarps * 32)
 cache_rows_kernel(uint4* __restrict__ cache, uint4* __restrict__ packed, const int64_t* __restrict__ seq_starts,
                   const int32_t* __restrict__ cu_pack, const int32_t* __restrict__ cu_k,
                   const int64_t* __restrict__ seq_ids, int batch, int packed_rows, int vecs) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int live_rows = min(packed_rows, cu_pack[batch]);
@@ -72,6 +74,8 @@ scatter_rows_kernel(uint4* __restrict__ cache, const uint4* __restrict__ new_row
                     const int64_t* __restrict__ row_idx, const CuT* __restrict__ cu,
                     const int64_t* __restrict__ seq_starts, const int64_t* __restrict__ seq_ids, int batch,
                     int num_rows, const int32_t* __restrict__ num_rows_dev, int vecs) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
@@ -96,6 +100,8 @@ kv_cache_update_kernel(const uint4* __restrict__ k_new, const uint4* __restrict_
                        const int64_t* __restrict__ v_starts, const int64_t* __restrict__ seq_ids, int batch,
                        int num_rows, const int32_t* __restrict__ num_rows_dev, int heads,
                        uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, uint4* __restrict__ dv) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
   const int64_t total = static_cast<int64_t>(n) * heads * 8;
   for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
@@ -158,6 +164,8 @@ kv_cache_update_kernel(const uint4* __restrict__ k_new, const uint4* __restrict_
 __global__ void __launch_bounds__(kCopyWarps * 32)
 delta_v_update_kernel(const uint4* __restrict__ v_new, uint4* __restrict__ cache, const int32_t* __restrict__ rows,
                       int num_rows, const int32_t* __restrict__ num_rows_dev, int vecs, uint4* __restrict__ dv) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
@@ -211,7 +219,7 @@ int launch_rows(const char* name, void* cache, void* packed, const int64_t* seq_
     return rc;
   const int vecs = static_cast<int>(static_cast<int64_t>(width) * elem_bytes / 16);
   const int blocks = min(cdiv_i(rows, kCopyWarps), sm_count() * 8);
-  cache_rows_kernel<TO_CACHE><<<blocks, kCopyWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(cache_rows_kernel<TO_CACHE>, blocks, kCopyWarps * 32, 0, static_cast<cudaStream_t>(stream), 
       static_cast<uint4*>(cache), static_cast<uint4*>(packed), seq_starts, cu_pack, cu_k, seq_ids, batch, rows,
       vecs);
   return check_launch(name);
@@ -268,7 +276,7 @@ int dyllm_delta_v_update(const void* v_new, void* cache, const int32_t* rows, in
                   reinterpret_cast<uintptr_t>(dv)) & 15) == 0,
                 DYLLM_ERR_INVALID_ARGUMENT, "delta_v_update: buffers must be 16-byte aligned");
   const int blocks = min(cdiv_i(num_rows, kCopyWarps), sm_count() * 8);
-  delta_v_update_kernel<<<blocks, kCopyWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(delta_v_update_kernel, blocks, kCopyWarps * 32, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint4*>(v_new), static_cast<uint4*>(cache), rows, num_rows, num_rows_dev, width / 8,
       static_cast<uint4*>(dv));
   return check_launch("delta_v_update");
@@ -295,7 +303,7 @@ int dyllm_kv_cache_update(const void* k_new, const void* v_new, const int64_t* r
   const int64_t want = (total + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int blocks = static_cast<int>(want < cap ? want : cap);
-  kv_cache_update_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(kv_cache_update_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new), rows_k, positions, pos_idx, cos_sin, max_pos,
       cu_seqlens_k, k_seq_starts, v_seq_starts, seq_ids, batch, num_rows, num_rows_dev, kv_heads,
       static_cast<uint4*>(k_cache), static_cast<uint4*>(v_cache), static_cast<uint4*>(dv));
@@ -314,11 +322,11 @@ int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t*
   const int blocks = min(cdiv_i(num_rows, kCopyWarps), sm_count() * 8);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cu_is_int64)
-    scatter_rows_kernel<int64_t><<<blocks, kCopyWarps * 32, 0, s>>>(
+    DYLLM_LAUNCH(scatter_rows_kernel<int64_t>, blocks, kCopyWarps * 32, 0, s, 
         static_cast<uint4*>(cache), static_cast<const uint4*>(new_rows), row_idx,
         static_cast<const int64_t*>(cu_seqlens), seq_starts, seq_ids, batch, num_rows, num_rows_dev, vecs);
   else
-    scatter_rows_kernel<int32_t><<<blocks, kCopyWarps * 32, 0, s>>>(
+    DYLLM_LAUNCH(scatter_rows_kernel<int32_t>, blocks, kCopyWarps * 32, 0, s, 
         static_cast<uint4*>(cache), static_cast<const uint4*>(new_rows), row_idx,
         static_cast<const int32_t*>(cu_seqlens), seq_starts, seq_ids, batch, num_rows, num_rows_dev, vecs);
   return check_launch("cache_scatter_update");

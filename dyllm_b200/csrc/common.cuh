@@ -39,7 +39,39 @@ constexpr int kSplitTicketCount = 4096;
 int* split_tickets();
 int read_and_clear_device_status();   // synchronises the given stream's device; used by tests
 
+// Programmatic dependent launch (off with DYLLM_PDL=0 in the environment).
+bool pdl_enabled();
+
 #ifdef __CUDACC__
+
+// Every kernel of this library is launched with the programmatic-stream-serialization attribute and begins
+// with pdl_wait() + pdl_trigger(): the next kernel of the stream may be scheduled, run its prologue (barrier
+// initialisation, tensor-memory allocation, descriptor prefetch) and then block in its own pdl_wait() while
+// this one is still running, which hides the launch latency between the ~500 small kernels of a denoising
+// step.  griddepcontrol.wait returns only when every earlier grid of the stream has completed and its memory
+// operations are visible, so placing it before the first global access keeps plain stream semantics; it is a
+// no-op in a kernel launched without the attribute (after a library kernel the trigger falls at completion).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define DYLLM_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  (void)::dyllm::launch_pdl(kernel, dim3(grid), dim3(block), static_cast<size_t>(smem), stream, __VA_ARGS__)
 
 // ----------------------------------------------------------------------------------------------
 // Small device utilities

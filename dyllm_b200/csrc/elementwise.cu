@@ -87,6 +87,8 @@ __global__ void __launch_bounds__(kNormThreads)
 add_rms_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res_in, const uint4* __restrict__ w,
                     uint4* __restrict__ y, uint4* __restrict__ res_out, int vecs, float inv_width, float eps,
                     int x_seg_rows, int64_t x_seg_pitch_rows) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int64_t row = blockIdx.x;
   // x may consist of equal segments of rows that lie x_seg_pitch_rows apart (a block of every sequence
   // read straight out of a cache); everything else is packed
@@ -106,6 +108,8 @@ add_rms_norm_rows_kernel(const uint4* __restrict__ x, const uint4* __restrict__ 
                          int vecs, float inv_width,
                          float eps, int x_seg_rows, int64_t x_seg_pitch_rows, const int32_t* __restrict__ sel_idx,
                          int sel_max, const int32_t* __restrict__ sel_count_dev) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   if (static_cast<int>(blockIdx.x) < rows) {
     const int64_t row = blockIdx.x;
     const int64_t x_row = (row / x_seg_rows) * x_seg_pitch_rows + row % x_seg_rows;
@@ -129,6 +133,8 @@ __global__ void __launch_bounds__(256)
 rope_neox_kernel(uint4* __restrict__ x, const int64_t* __restrict__ positions, const int64_t* __restrict__ pos_idx,
                  const float* __restrict__ cos_sin, int rows, int heads, int max_pos,
                  const int32_t* __restrict__ num_rows_dev) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = num_rows_dev ? min(rows, *num_rows_dev) : rows;
   const int64_t total = static_cast<int64_t>(n) * heads * 8;
   for (int64_t t = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; t < total;
@@ -169,6 +175,8 @@ constexpr int kConfThreads = 256;
 __global__ void __launch_bounds__(kConfThreads)
 row_confidence_kernel(const __nv_bfloat16* __restrict__ logits, int vocab, int64_t pitch,
                       float* __restrict__ conf, int64_t* __restrict__ token) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const __nv_bfloat16* row = logits + static_cast<int64_t>(blockIdx.x) * pitch;
   float m = -INFINITY, l = 0.f;
   int arg = 0;
@@ -282,10 +290,10 @@ int dyllm_add_rms_norm_segmented(const void* x, int x_seg_rows, int64_t x_seg_pi
   uint4* rop = static_cast<uint4*>(residual_out);
   const float inv = 1.0f / static_cast<float>(width);
   switch (vpt) {
-    case 1: add_rms_norm_kernel<1><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
-    case 2: add_rms_norm_kernel<2><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
-    case 3: add_rms_norm_kernel<3><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
-    default: add_rms_norm_kernel<4><<<rows, kNormThreads, 0, s>>>(xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    case 1: DYLLM_LAUNCH(add_rms_norm_kernel<1>, rows, kNormThreads, 0, s, xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    case 2: DYLLM_LAUNCH(add_rms_norm_kernel<2>, rows, kNormThreads, 0, s, xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    case 3: DYLLM_LAUNCH(add_rms_norm_kernel<3>, rows, kNormThreads, 0, s, xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
+    default: DYLLM_LAUNCH(add_rms_norm_kernel<4>, rows, kNormThreads, 0, s, xp, rp, wp, yp, rop, vecs, inv, eps, x_seg_rows, x_seg_pitch_rows); break;
   }
   return check_launch("add_rms_norm");
 }
@@ -323,7 +331,7 @@ int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_r
   const int sel_blocks = sel_max < 1024 ? sel_max : 1024;
   const unsigned grid = static_cast<unsigned>(rows + sel_blocks);
 #define DYLLM_NORM_ROWS(V)                                                                                         \
-  add_rms_norm_rows_kernel<V><<<grid, kNormThreads, 0, s>>>(xp, rp, wp, yap, yp, rop, rows, vecs, inv, eps,       \
+  DYLLM_LAUNCH(add_rms_norm_rows_kernel<V>, grid, kNormThreads, 0, s, xp, rp, wp, yap, yp, rop, rows, vecs, inv, eps,       \
                                                             x_seg_rows, x_seg_pitch_rows, sel_idx, sel_max,       \
                                                             sel_count_dev)
   switch (vpt) {
@@ -350,7 +358,7 @@ int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, c
   int64_t want = cdiv_l(total, 256);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   const int blocks = static_cast<int>(want < cap ? want : cap);
-  rope_neox_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint4*>(x), positions, pos_idx,
+  DYLLM_LAUNCH(rope_neox_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), static_cast<uint4*>(x), positions, pos_idx,
                                                                         cos_sin, rows, heads, max_pos, num_rows_dev);
   return check_launch("rope_neox");
 }
@@ -364,7 +372,7 @@ int dyllm_row_confidence(const void* logits, int rows, int vocab, int64_t pitch,
   DYLLM_REQUIRE(logits && conf && token, DYLLM_ERR_INVALID_ARGUMENT, "row_confidence: null pointer");
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(logits) & 15) == 0 && pitch % 8 == 0, DYLLM_ERR_INVALID_ARGUMENT,
                 "row_confidence: rows must start on 16-byte boundaries");
-  row_confidence_kernel<<<rows, kConfThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(row_confidence_kernel, rows, kConfThreads, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(logits), vocab, pitch, conf, token);
   return check_launch("row_confidence");
 }

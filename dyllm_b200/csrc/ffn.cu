@@ -32,7 +32,7 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
                        cudaGetErrorString(cudaGetLastError()));
     smem_set[dev].store(true, std::memory_order_release);
   }
-  kernel<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  DYLLM_LAUNCH(kernel, grid, kGemmThreads, Cfg::SMEM_BYTES, stream, ta, tb, p);
   return check_launch("gathered_gemm");
 }
 
@@ -48,6 +48,8 @@ int launch_mode(int a_mode, const CUtensorMap& ta, const CUtensorMap& tb, const 
 __global__ void __launch_bounds__(256)
 stage_rows_kernel(const uint4* __restrict__ x, int64_t x_pitch_vecs, const int32_t* __restrict__ idx, int x_rows,
                   uint4* __restrict__ compact, int vecs, int num_rows, const int32_t* __restrict__ num_rows_dev) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int m = blockIdx.x * 8 + warp; m < n; m += gridDim.x * 8) {
@@ -117,6 +119,8 @@ __global__ void cache_dest_rows_kernel(const int64_t* __restrict__ row_idx, cons
                                        const int64_t* __restrict__ seq_starts, const int64_t* __restrict__ seq_ids,
                                        int batch, int num_rows, const int32_t* __restrict__ num_rows_dev,
                                        int32_t* __restrict__ dest) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
   for (int m = blockIdx.x * blockDim.x + threadIdx.x; m < num_rows; m += gridDim.x * blockDim.x) {
     if (m >= n) {
@@ -211,7 +215,7 @@ int stage_rows(const void* x, int64_t ldx, const int32_t* idx, int x_rows, void*
   int blocks = cdiv_i(h, 8);
   const int cap = sm_count() * 8;
   blocks = blocks > cap ? cap : (blocks < 1 ? 1 : blocks);
-  stage_rows_kernel<<<blocks, 256, 0, stream>>>(static_cast<const uint4*>(x), ldx / 8, idx, x_rows,
+  DYLLM_LAUNCH(stage_rows_kernel, blocks, 256, 0, stream, static_cast<const uint4*>(x), ldx / 8, idx, x_rows,
                                                static_cast<uint4*>(compact), width / 8, num_rows, num_rows_dev);
   return check_launch("stage_rows");
 }
@@ -248,7 +252,7 @@ int dyllm_cache_dest_rows(const int64_t* row_idx, const int32_t* cu_seqlens, con
   DYLLM_REQUIRE(row_idx && cu_seqlens && seq_starts && seq_ids && dest_rows && batch > 0, DYLLM_ERR_INVALID_ARGUMENT,
                 "cache_dest_rows: null pointer or empty batch");
   const int blocks = min(cdiv_i(num_rows, 256), sm_count() * 4);
-  cache_dest_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(cache_dest_rows_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), 
       row_idx, cu_seqlens, seq_starts, seq_ids, batch, num_rows, num_rows_dev, dest_rows);
   return check_launch("cache_dest_rows");
 }

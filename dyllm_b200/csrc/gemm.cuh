@@ -93,6 +93,8 @@ template <int BNH, bool SWIGLU, int A_MODE, int STAGES, int MINB, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, MINB)
 gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const GemmParams p) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   using Cfg = GemmCfg<BNH, SWIGLU, STAGES, MT>;
   constexpr int BM = kGemmBM * MT, BK = kGemmBK, BN = Cfg::BN;
   static_assert(MT == 1 || A_MODE == 0, "256-row tiles take their rows as one TMA box");

@@ -27,6 +27,8 @@ moe_route_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int32_t
                  int num_rows, const int32_t* __restrict__ num_rows_dev, const __nv_bfloat16* __restrict__ wr,
                  int hidden, int num_experts, int top_k, int renormalize, float* __restrict__ topk_w,
                  int32_t* __restrict__ topk_ids) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
   __shared__ float s_logits[kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,6 +125,8 @@ moe_align_kernel(const int32_t* __restrict__ topk_ids, const float* __restrict__
                  const int32_t* __restrict__ row_src, int32_t* __restrict__ a_idx, int32_t* __restrict__ pair_idx,
                  float* __restrict__ pair_w, int32_t* __restrict__ tile_expert, int32_t* __restrict__ m_total,
                  int capacity) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   __shared__ int s_count[kMaxExperts];
   __shared__ int s_start[kMaxExperts + 1];
   __shared__ int s_fill[kMaxExperts];
@@ -178,6 +182,8 @@ __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ topk_ids, int num_rows,
                    const int32_t* __restrict__ num_rows_dev, int top_k, int expert_start, int num_local_experts,
                    int hidden, __nv_bfloat16* __restrict__ out, int64_t ldo, const int32_t* __restrict__ out_row_map) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = num_rows_dev ? min(num_rows, *num_rows_dev) : num_rows;
   const int vecs = hidden / 8;
   for (int m = blockIdx.x; m < n; m += gridDim.x) {
@@ -251,7 +257,7 @@ int dyllm_moe_route(const void* x, int x_rows, int hidden, int64_t ldx, const in
     return DYLLM_OK;
   DYLLM_REQUIRE(x && router_weight && topk_weights && topk_ids, DYLLM_ERR_INVALID_ARGUMENT, "moe_route: null pointer");
   const int blocks = min(num_rows, sm_count() * 8);
-  moe_route_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(moe_route_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), ldx, idx, x_rows, num_rows, num_rows_dev,
       static_cast<const __nv_bfloat16*>(router_weight), hidden, num_experts, top_k, renormalize, topk_weights, topk_ids);
   return check_launch("moe_route");
@@ -293,7 +299,7 @@ int dyllm_moe_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int3
   __nv_bfloat16* inter_buf = reinterpret_cast<__nv_bfloat16*>(ws + l.off_inter);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(ws + l.off_y);
 
-  moe_align_kernel<<<1, 1024, 0, s>>>(topk_ids, topk_weights, num_rows, num_rows_dev, top_k, expert_start,
+  DYLLM_LAUNCH(moe_align_kernel, 1, 1024, 0, s, topk_ids, topk_weights, num_rows, num_rows_dev, top_k, expert_start,
                                       num_local_experts, idx, a_idx, pair_idx, pair_w, tile_expert, m_total, l.capacity);
   int rc = check_launch("moe_align");
   if (rc != DYLLM_OK)
@@ -338,7 +344,7 @@ int dyllm_moe_ffn(const void* x, int x_rows, int hidden, int64_t ldx, const int3
   if (rc != DYLLM_OK)
     return rc;
   const int blocks = min(hint_rows, sm_count() * 8);
-  moe_combine_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, s>>>(y, topk_ids, num_rows, num_rows_dev, top_k, expert_start,
+  DYLLM_LAUNCH(moe_combine_kernel, blocks < 1 ? 1 : blocks, 256, 0, s, y, topk_ids, num_rows, num_rows_dev, top_k, expert_start,
                                                             num_local_experts, hidden, static_cast<__nv_bfloat16*>(out),
                                                             ldo, out_row_map);
   return check_launch("moe_combine");

@@ -2,6 +2,7 @@
 // properties, the device status word written by bounded waits, and tensor-map encoding.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -46,6 +47,14 @@ EncodeTiledFn encode_fn() {
   return g_encode;
 }
 }  // namespace
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("DYLLM_PDL");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
 
 int set_error(int code, const char* fmt, ...) {
   va_list args;

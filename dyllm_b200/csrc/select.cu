@@ -35,6 +35,8 @@ constexpr int kStatsWarps = 8;
 __global__ void __launch_bounds__(kStatsWarps * 32)
 context_stats_kernel(const uint4* __restrict__ c_old, const uint4* __restrict__ c_new, float* __restrict__ stats,
                      int rows, int vecs_per_row, int accumulate) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   for (int row = blockIdx.x * kStatsWarps + warp; row < rows; row += gridDim.x * kStatsWarps) {
@@ -86,6 +88,8 @@ __device__ __forceinline__ bool below_threshold(float dot, float a, float b, flo
 
 __global__ void cosine_mask_kernel(const float* __restrict__ stats, uint8_t* __restrict__ mask, int rows,
                                    float threshold) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
     const float* s = stats + static_cast<int64_t>(r) * 3;
     mask[r] = below_threshold(s[0], s[1], s[2], threshold) ? 1 : 0;
@@ -132,6 +136,8 @@ salient_select_kernel(const float* __restrict__ stats, int rows, float threshold
                       int64_t* __restrict__ idx_out, int32_t* __restrict__ idx32_out, int64_t* __restrict__ idx_k_out,
                       int32_t* __restrict__ cu_salientlens_out, int32_t* __restrict__ count_out,
                       uint8_t* __restrict__ mask_out, SelectWorkspace* ws, int* status_word) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   constexpr int kTileRows = kSelWarps * SUPER * 128;
   __shared__ int s_excl[kSelWarps * SUPER * 32];       // per thread and group: flags of the tile before its rows
   __shared__ uint8_t s_nib[kSelWarps * SUPER * 32];    // per thread and group: its 4 flags
@@ -317,6 +323,8 @@ salient_select_kernel(const float* __restrict__ stats, int rows, float threshold
 }
 
 __global__ void select_empty_kernel(int32_t* cu_salientlens_out, int32_t* count_out, int batch) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   for (int b = threadIdx.x; b <= batch; b += blockDim.x)
     cu_salientlens_out[b] = 0;
   if (threadIdx.x == 0)
@@ -330,6 +338,8 @@ __global__ void fused_offset_kernel(const int32_t* __restrict__ idxs, const int3
                                     const int32_t* __restrict__ cu_promptlens,
                                     const int32_t* __restrict__ cu_salientlens, int num_groups,
                                     int64_t* __restrict__ out, int max_threads) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const int n = min(*num_idxs, max_threads);
   for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n; t += gridDim.x * blockDim.x) {
     int left = 0, right = num_groups;
@@ -357,18 +367,18 @@ int launch_salient_select(const float* stats, int rows, float threshold, const i
                           int32_t* cu_salientlens_out, int32_t* count_out, uint8_t* mask_out, void* workspace,
                           cudaStream_t stream) {
   if (rows == 0) {
-    select_empty_kernel<<<1, 128, 0, stream>>>(cu_salientlens_out, count_out, batch);
+    DYLLM_LAUNCH(select_empty_kernel, 1, 128, 0, stream, cu_salientlens_out, count_out, batch);
     return check_launch("salient_select(empty)");
   }
   if (cudaMemsetAsync(workspace, 0, select_workspace_bytes(rows), stream) != cudaSuccess)
     return set_error(DYLLM_ERR_CUDA, "salient_select: clearing the workspace failed");
   SelectWorkspace* w = static_cast<SelectWorkspace*>(workspace);
   if (rows > 64 * 1024)
-    salient_select_kernel<8><<<cdiv_i(rows, kSelWarps * 8 * 128), kSelWarps * 32, 0, stream>>>(
+    DYLLM_LAUNCH(salient_select_kernel<8>, cdiv_i(rows, kSelWarps * 8 * 128), kSelWarps * 32, 0, stream, 
         stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
         cu_salientlens_out, count_out, mask_out, w, device_status_word());
   else
-    salient_select_kernel<2><<<cdiv_i(rows, kSelTileRowsSmall), kSelWarps * 32, 0, stream>>>(
+    DYLLM_LAUNCH(salient_select_kernel<2>, cdiv_i(rows, kSelTileRowsSmall), kSelWarps * 32, 0, stream, 
         stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
         cu_salientlens_out, count_out, mask_out, w, device_status_word());
   return check_launch("salient_select");
@@ -426,7 +436,7 @@ int dyllm_context_stats(const void* c_old, const void* c_new, float* stats, int 
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(c_old) & 15) == 0 && (reinterpret_cast<uintptr_t>(c_new) & 15) == 0,
                 DYLLM_ERR_INVALID_ARGUMENT, "context_stats: inputs must be 16-byte aligned");
   const int blocks = min(cdiv_i(rows, kStatsWarps), sm_count() * 8);
-  context_stats_kernel<<<blocks, kStatsWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(context_stats_kernel, blocks, kStatsWarps * 32, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint4*>(c_old), static_cast<const uint4*>(c_new), stats, rows, width / 8, accumulate);
   return check_launch("context_stats");
 }
@@ -437,7 +447,7 @@ int dyllm_cosine_mask(const float* stats, uint8_t* mask, int rows, float thresho
     return DYLLM_OK;
   DYLLM_REQUIRE(stats && mask, DYLLM_ERR_INVALID_ARGUMENT, "cosine_mask: null pointer");
   const int blocks = min(cdiv_i(rows, 256), sm_count() * 8);
-  cosine_mask_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(stats, mask, rows, threshold);
+  DYLLM_LAUNCH(cosine_mask_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), stats, mask, rows, threshold);
   return check_launch("cosine_mask");
 }
 
@@ -504,7 +514,7 @@ int dyllm_fused_offset(const int32_t* idxs, const int32_t* num_idxs, const int32
   DYLLM_REQUIRE(idxs && num_idxs && cu_promptlens && cu_salientlens && out, DYLLM_ERR_INVALID_ARGUMENT,
                 "fused_offset: null pointer");
   const int blocks = min(cdiv_i(max_threads, 256), sm_count() * 8);
-  fused_offset_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(idxs, num_idxs, cu_promptlens,
+  DYLLM_LAUNCH(fused_offset_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), idxs, num_idxs, cu_promptlens,
                                                                            cu_salientlens, num_groups, out,
                                                                            max_threads);
   return check_launch("fused_offset");

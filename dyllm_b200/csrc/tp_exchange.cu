@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_push_kernel(unsigned char* const* __restrict__ peers, int rank, int world, size_t slot_bytes,
                const VecT* __restrict__ src, int row_vecs, int max_rows, const int32_t* __restrict__ count_dev,
                int row_offset) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   unsigned char* local = peers[rank];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
   const uint32_t parity = epoch & 1u;
@@ -178,6 +180,8 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_reduce_rows_kernel(unsigned char* local, int world, size_t slot_bytes, int row_vecs, int max_rows,
                       const int32_t* __restrict__ count_dev, int row_offset, uint4* __restrict__ out, int64_t ldo_vecs,
                       const int32_t* __restrict__ out_row_map, unsigned long long wait_ns, int* status_word) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
   const uint32_t parity = epoch & 1u;
   const bool ok = wait_flags(local, parity, epoch + 1u, world, wait_ns, status_word);
@@ -212,6 +216,8 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_gather_push_kernel(unsigned char* const* __restrict__ peers, int rank, int world, size_t slot_bytes,
                       const uint4* __restrict__ x, int64_t ldx_vecs, const int32_t* __restrict__ idx, int x_rows,
                       int row_vecs, int max_rows, const int32_t* __restrict__ count_dev) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   unsigned char* local = peers[rank];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
   const uint32_t parity = epoch & 1u;
@@ -256,6 +262,8 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_gather_finish_kernel(unsigned char* local, int world, size_t slot_bytes, int slot_rows, int32_t* __restrict__ idx_all,
                         int32_t* __restrict__ prefix, int32_t* __restrict__ total_out, unsigned long long wait_ns,
                         int* status_word) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   __shared__ int pre[kTpMaxWorld + 1];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
   const uint32_t parity = epoch & 1u;
@@ -288,6 +296,8 @@ tp_gather_finish_kernel(unsigned char* local, int world, size_t slot_bytes, int 
 __global__ void __launch_bounds__(kTpThreads)
 tp_scatter_push_kernel(unsigned char* const* __restrict__ peers, int rank, int world, size_t slot_bytes,
                        const uint4* __restrict__ y, int row_vecs, int max_rows, const int32_t* __restrict__ prefix) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   unsigned char* local = peers[rank];
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
   const uint32_t parity = epoch & 1u;
@@ -327,6 +337,8 @@ tp_scatter_push_kernel(unsigned char* const* __restrict__ peers, int rank, int w
 __global__ void __launch_bounds__(kTpThreads)
 tp_reduce_f32_kernel(unsigned char* local, int world, size_t slot_bytes, float* __restrict__ out, int n,
                      unsigned long long wait_ns, int* status_word) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(local);
   const uint32_t parity = epoch & 1u;
   const bool ok = wait_flags(local, parity, epoch + 1u, world, wait_ns, status_word);
@@ -470,8 +482,7 @@ int dyllm_tp_push_rows(void* comm, const void* src, int width, int max_rows, con
                 "tp_push_rows: %d rows of %d bf16 exceed the slot of %zu bytes", max_rows, width, c->slot_bytes);
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(src) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_push_rows: src must be 16-byte aligned");
   const int row_vecs = width / 8;
-  tp_push_kernel<uint4><<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0,
-                          static_cast<cudaStream_t>(stream)>>>(c->peers_dev, c->rank, c->world, c->slot_bytes,
+  DYLLM_LAUNCH(tp_push_kernel<uint4>, grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, static_cast<cudaStream_t>(stream), c->peers_dev, c->rank, c->world, c->slot_bytes,
                                                                 static_cast<const uint4*>(src), row_vecs, max_rows,
                                                                 count_dev, row_offset);
   return check_launch("tp_push_rows");
@@ -488,8 +499,7 @@ int dyllm_tp_reduce_rows(void* comm, int width, int max_rows, const int32_t* cou
                 "tp_reduce_rows: %d rows of %d bf16 exceed the slot of %zu bytes", max_rows, width, c->slot_bytes);
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_reduce_rows: out must be 16-byte aligned");
   const int row_vecs = width / 8;
-  tp_reduce_rows_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0,
-                          static_cast<cudaStream_t>(stream)>>>(c->local, c->world, c->slot_bytes, row_vecs, max_rows,
+  DYLLM_LAUNCH(tp_reduce_rows_kernel, grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, static_cast<cudaStream_t>(stream), c->local, c->world, c->slot_bytes, row_vecs, max_rows,
                                                                 count_dev, row_offset, static_cast<uint4*>(out), ldo / 8,
                                                                 out_row_map, c->wait_ns, device_status_word());
   return check_launch("tp_reduce_rows");
@@ -519,13 +529,13 @@ int dyllm_tp_gather_rows(void* comm, const void* x, int x_rows, int width, int64
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_rows: x must be 16-byte aligned");
   const int row_vecs = width / 8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  tp_gather_push_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, st>>>(
+  DYLLM_LAUNCH(tp_gather_push_kernel, grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, st, 
       c->peers_dev, c->rank, c->world, c->slot_bytes, static_cast<const uint4*>(x), ldx / 8, idx, x_rows, row_vecs,
       max_rows, count_dev);
   int rc = check_launch("tp_gather_push");
   if (rc != DYLLM_OK)
     return rc;
-  tp_gather_finish_kernel<<<1, kTpThreads, 0, st>>>(c->local, c->world, c->slot_bytes,
+  DYLLM_LAUNCH(tp_gather_finish_kernel, 1, kTpThreads, 0, st, c->local, c->world, c->slot_bytes,
                                                    static_cast<int>(c->slot_bytes / row_bytes), idx_all, prefix,
                                                    total_out, c->wait_ns, device_status_word());
   return check_launch("tp_gather_finish");
@@ -539,8 +549,7 @@ int dyllm_tp_gather_push(void* comm, const void* x, int x_rows, int width, int64
                     static_cast<size_t>(max_rows) * width * 2 <= c->slot_bytes,
                 DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_push: bad shape");
   const int row_vecs = width / 8;
-  tp_gather_push_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0,
-                          static_cast<cudaStream_t>(stream)>>>(c->peers_dev, c->rank, c->world, c->slot_bytes,
+  DYLLM_LAUNCH(tp_gather_push_kernel, grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, static_cast<cudaStream_t>(stream), c->peers_dev, c->rank, c->world, c->slot_bytes,
                                                                 static_cast<const uint4*>(x), ldx / 8, idx, x_rows,
                                                                 row_vecs, max_rows, count_dev);
   return check_launch("tp_gather_push");
@@ -551,7 +560,7 @@ int dyllm_tp_gather_finish(void* comm, int width, int32_t* idx_all, int32_t* pre
   TpComm* c = as_comm(comm);
   const size_t row_bytes = static_cast<size_t>(width) * 2;
   DYLLM_REQUIRE(c->slot_bytes % row_bytes == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_gather_finish: slot is not a whole number of rows");
-  tp_gather_finish_kernel<<<1, kTpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(tp_gather_finish_kernel, 1, kTpThreads, 0, static_cast<cudaStream_t>(stream), 
       c->local, c->world, c->slot_bytes, static_cast<int>(c->slot_bytes / row_bytes), idx_all, prefix, total_out,
       c->wait_ns, device_status_word());
   return check_launch("tp_gather_finish");
@@ -566,8 +575,7 @@ int dyllm_tp_scatter_push(void* comm, const void* y, int width, int max_rows, co
                 width, max_rows);
   DYLLM_REQUIRE((reinterpret_cast<uintptr_t>(y) & 15) == 0, DYLLM_ERR_INVALID_ARGUMENT, "tp_scatter_push: y must be 16-byte aligned");
   const int row_vecs = width / 8;
-  tp_scatter_push_kernel<<<grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0,
-                           static_cast<cudaStream_t>(stream)>>>(c->peers_dev, c->rank, c->world, c->slot_bytes,
+  DYLLM_LAUNCH(tp_scatter_push_kernel, grid_for(static_cast<int64_t>(max_rows) * row_vecs), kTpThreads, 0, static_cast<cudaStream_t>(stream), c->peers_dev, c->rank, c->world, c->slot_bytes,
                                                                  static_cast<const uint4*>(y), row_vecs, max_rows, prefix);
   return check_launch("tp_scatter_push");
 }
@@ -577,7 +585,7 @@ int dyllm_tp_push_f32(void* comm, const float* src, int n, void* stream) {
   TpComm* c = as_comm(comm);
   DYLLM_REQUIRE(static_cast<size_t>(n) * 4 <= c->slot_bytes, DYLLM_ERR_WORKSPACE,
                 "tp_push_f32: %d values exceed the slot of %zu bytes", n, c->slot_bytes);
-  tp_push_kernel<uint32_t><<<grid_for(n), kTpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(tp_push_kernel<uint32_t>, grid_for(n), kTpThreads, 0, static_cast<cudaStream_t>(stream), 
       c->peers_dev, c->rank, c->world, c->slot_bytes, reinterpret_cast<const uint32_t*>(src), 1, n, nullptr, 0);
   return check_launch("tp_push_f32");
 }
@@ -587,7 +595,7 @@ int dyllm_tp_reduce_f32(void* comm, float* out, int n, void* stream) {
   TpComm* c = as_comm(comm);
   DYLLM_REQUIRE(static_cast<size_t>(n) * 4 <= c->slot_bytes, DYLLM_ERR_WORKSPACE,
                 "tp_reduce_f32: %d values exceed the slot of %zu bytes", n, c->slot_bytes);
-  tp_reduce_f32_kernel<<<grid_for(n), kTpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  DYLLM_LAUNCH(tp_reduce_f32_kernel, grid_for(n), kTpThreads, 0, static_cast<cudaStream_t>(stream), 
       c->local, c->world, c->slot_bytes, out, n, c->wait_ns, device_status_word());
   return check_launch("tp_reduce_f32");
 }
