@@ -127,6 +127,37 @@ add_rms_norm_rows_kernel(const uint4* __restrict__ x, const uint4* __restrict__ 
   }
 }
 
+// RMSNorm over the 128 values of every (row, head), in place: one warp per head vector, 8 bytes per lane.
+// y = bf16( bf16(x * rsqrt(mean(x^2) + eps)) * w ), the arithmetic of add_rms_norm without a residual.
+__global__ void __launch_bounds__(256)
+head_rms_norm_kernel(uint2* __restrict__ x, const uint2* __restrict__ w, int rows, int heads, float eps,
+                     const int32_t* __restrict__ num_rows_dev) {
+  pdl_wait();
+  pdl_trigger();
+  const int n = num_rows_dev ? min(rows, *num_rows_dev) : rows;
+  const int64_t total = static_cast<int64_t>(n) * heads;
+  const int lane = threadIdx.x & 31;
+  const uint2 wv = __ldg(w + lane);
+  const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+  for (int64_t v = blockIdx.x * static_cast<int64_t>(blockDim.x >> 5) + (threadIdx.x >> 5); v < total;
+       v += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+    uint2* p = x + v * 32 + lane;
+    const uint2 xv = *p;
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    const float2 a = __bfloat1622float2(x2[0]), b = __bfloat1622float2(x2[1]);
+    float ss = a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+      ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float scale = rsqrtf(ss * (1.0f / 128.0f) + eps);
+    uint2 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+    o2[0] = __hmul2(__floats2bfloat162_rn(a.x * scale, a.y * scale), w2[0]);
+    o2[1] = __hmul2(__floats2bfloat162_rn(b.x * scale, b.y * scale), w2[1]);
+    *p = o;
+  }
+}
+
 // x[r, h, :] rotated in place by the angle table row of positions[pos_idx ? pos_idx[r] : r]:
 // (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin), halves of 64; 8 threads per (row, head).
 __global__ void __launch_bounds__(256)
@@ -342,6 +373,24 @@ int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_r
   }
 #undef DYLLM_NORM_ROWS
   return check_launch("add_rms_norm_rows");
+}
+
+int dyllm_head_rms_norm(void* x, const void* weight, float eps, int rows, const int32_t* num_rows_dev, int heads,
+                        int head_dim, void* stream) {
+  DYLLM_REQUIRE(head_dim == 128, DYLLM_ERR_UNSUPPORTED, "head_rms_norm: head_dim %d (only 128 is built)", head_dim);
+  DYLLM_REQUIRE(rows >= 0 && heads > 0, DYLLM_ERR_INVALID_ARGUMENT, "head_rms_norm: rows %d heads %d", rows, heads);
+  if (rows == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(x && weight, DYLLM_ERR_INVALID_ARGUMENT, "head_rms_norm: null pointer");
+  DYLLM_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight)) & 7) == 0,
+                DYLLM_ERR_INVALID_ARGUMENT, "head_rms_norm: buffers must be 8-byte aligned");
+  const int64_t vectors = static_cast<int64_t>(rows) * heads;
+  const int64_t want = (vectors + 7) / 8;
+  const int cap = sm_count() * 16;
+  const int blocks = static_cast<int>(want < cap ? want : cap);
+  DYLLM_LAUNCH(head_rms_norm_kernel, blocks, 256, 0, static_cast<cudaStream_t>(stream), static_cast<uint2*>(x),
+               static_cast<const uint2*>(weight), rows, heads, eps, num_rows_dev);
+  return check_launch("head_rms_norm");
 }
 
 int dyllm_rope_neox(void* x, const int64_t* positions, const int64_t* pos_idx, const float* cos_sin, int rows,

@@ -313,6 +313,11 @@ class RMSNorm(nn.Module):
             x = x.contiguous()
         return ops.add_rms_norm(x, self.weight, self.eps, residual)
 
+    def forward_heads_(self, x: torch.Tensor, num_rows_dev=None) -> torch.Tensor:
+        """In place over the last dimension of ``x [rows, heads, head_dim]`` (this module's size is head_dim):
+        the per-head q / k norm (ref: dyllm/model_executor/models/lladamoe.py:195-207)."""
+        return ops.head_rms_norm_(x, self.weight, self.eps, num_rows_dev)
+
     def forward_rows(self, x: torch.Tensor, residual: torch.Tensor, sel_idx32: torch.Tensor, sel_count_dev=None):
         """Residual add of every row, normalised values of the listed rows only, packed in list order:
         ``(y_sel, new_residual)``.  What a sparse step needs of the post-attention norm: its output feeds the

@@ -76,16 +76,15 @@ class LLaDAAttention(nn.Module):
         packed in list order (``RMSNorm.forward_with_rows``); the K/V projection then reads them directly."""
         ctx, md = get_context(), get_metadata()
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
-        q = self.q_proj(hidden_states)
+        q = self.q_proj(hidden_states).view(-1, H, D)
         if self.q_norm is not None:
-            q = self.q_norm(q.view(-1, D))
-        q = q.view(-1, H, D)
+            q = self.q_norm.forward_heads_(q)
         if ctx.is_full:
             kv = self.kv_proj(hidden_states)
             k, v = kv.split([self.kv_size, self.kv_size], dim=-1)
-            if self.k_norm is not None:
-                k = self.k_norm(k.reshape(-1, D))
             k, v = k.reshape(-1, Hkv, D), v.reshape(-1, Hkv, D)
+            if self.k_norm is not None:
+                k = self.k_norm.forward_heads_(k.contiguous())
             q, k = self.rotary_emb(positions, q, k)
             self.k_cache.reset_full(k.flatten(-2, -1), md.running_seqs_tensor, seq_ids_list=md.running_seqs)
             o = self.attn(q, k, v)
@@ -102,7 +101,7 @@ class LLaDAAttention(nn.Module):
                                                                  split_col=self.kv_size)
                 rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
                 if self.k_norm is not None:
-                    k_new = self.k_norm(k_new.view(-1, D))       # rows past the live count hold nothing of value
+                    k_new = self.k_norm.forward_heads_(k_new.view(cap, Hkv, D), n_dev).view(cap, -1)
                 v_new = v_new.view(cap, Hkv, D)
                 # rotary embedding of the new keys, K-cache scatter, delta-V and V-cache update in one launch
                 dv = ops.kv_cache_update(k_new.view(cap, Hkv, D), v_new, rows_k, positions, ctx.idx_salient_row,

@@ -297,6 +297,18 @@ def add_rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, residua
     return y_sel, res_out, y_all
 
 
+def head_rms_norm_(x: torch.Tensor, weight: torch.Tensor, eps: float, num_rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """In-place RMSNorm over the last dimension (128) of ``x [rows, heads, 128]``: the per-head q / k norm.
+
+    ref: dyllm/model_executor/models/lladamoe.py:195-207.
+    """
+    require_cuda(x, "x", torch.bfloat16, 3)
+    require_cuda(weight, "weight", torch.bfloat16, 1)
+    call("dyllm_head_rms_norm", ptr(x), ptr(weight), float(eps), x.size(0), ptr(num_rows_dev), x.size(1), x.size(2),
+         stream_ptr(x.device))
+    return x
+
+
 def rope_neox_(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, pos_idx: torch.Tensor | None = None,
                num_rows_dev: torch.Tensor | None = None) -> torch.Tensor:
     """In-place NeoX rotary embedding of ``x [rows, heads, 128]``.

@@ -343,6 +343,14 @@ int dyllm_add_rms_norm_rows(const void* x, int x_seg_rows, int64_t x_seg_pitch_r
                             const int32_t* sel_idx, int sel_max, const int32_t* sel_count_dev, void* y_sel,
                             void* stream);
 
+/* RMSNorm over the head_dim values of every (row, head) of x [rows, heads, 128] (bf16), in place:
+ * x = bf16( bf16(x * rsqrt(mean(x^2) + eps)) * weight ), weight bf16 [128].  num_rows_dev (nullable) bounds the
+ * rows on the device.  The per-head q / k normalisation of LLaDA-MoE.
+ * ref: dyllm/model_executor/models/lladamoe.py:175-176,195-207 (q_norm / k_norm on reshape(-1, head_dim)),
+ *      dyllm/model_executor/layers/layernorm.py:17-29. */
+int dyllm_head_rms_norm(void* x, const void* weight, float eps, int rows, const int32_t* num_rows_dev, int heads,
+                        int head_dim, void* stream);
+
 /* Confidence of the most likely token per row of bf16 logits [rows, vocab] (row pitch in elements,
  * multiple of 8): conf[r] = max_j softmax(logits[r])_j in fp32, token[r] = the first j attaining the maximum.
  * Replaces softmax + max over fp32 copies of the candidate logits.

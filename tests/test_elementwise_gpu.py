@@ -120,3 +120,21 @@ def test_add_rms_norm_rows_equals_full_norm_on_listed_rows(cuda_device, rows, wi
         y_sel, res_out, y_all = ops.add_rms_norm_rows(view, w, 1e-5, res, idx, count, all_rows=True)
         assert torch.equal(res_out, res_full) and torch.equal(y_sel[:live], y_full[idx[:live].long()])
         assert torch.equal(y_all, y_full)
+
+
+@pytest.mark.parametrize("rows,heads,live", [(300, 16, 300), (64, 2, 17), (5000, 4, 5000)])
+def test_head_rms_norm_matches_the_oracle(cuda_device, rows, heads, live):
+    """The per-head q / k normalisation of LLaDA-MoE (lladamoe.py:195-207): RMSNorm over each 128-vector."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + heads)
+    x = torch.randn(rows, heads, 128, generator=g).bfloat16()
+    w = (1.0 + 0.2 * torch.randn(128, generator=g)).bfloat16()
+    count = torch.tensor([live], dtype=torch.int32, device=cuda_device)
+    got = ops.head_rms_norm_(x.to(cuda_device).clone(), w.to(cuda_device), 1e-5, count).cpu()
+    want = orc.rms_norm(x.view(-1, 128), w, 1e-5).view(rows, heads, 128)
+    torch.testing.assert_close(got[:live].float(), want[:live].float(), rtol=1.6e-2, atol=1e-3)
+    assert torch.equal(got[live:], x[live:])
+    # the same bits as the row-wise norm kernel on the flattened view
+    ref = ops.add_rms_norm(x.view(-1, 128).to(cuda_device), w.to(cuda_device), 1e-5).cpu().view(rows, heads, 128)
+    assert torch.equal(got[:live], ref[:live])
