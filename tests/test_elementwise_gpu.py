@@ -137,4 +137,4 @@ def test_head_rms_norm_matches_the_oracle(cuda_device, rows, heads, live):
     assert torch.equal(got[live:], x[live:])
     # the row-wise norm kernel on the flattened view gives the same values up to the order of its fp32 sum
     ref = ops.add_rms_norm(x.view(-1, 128).to(cuda_device), w.to(cuda_device), 1e-5).cpu().view(rows, heads, 128)
-    torch.testing.assert_close(got[:live].float(), ref[:live].float(), rtol=8e-3, atol=1e-3)
+    torch.testing.assert_close(got[:live].float(), ref[:live].float(), rtol=1.6e-2, atol=1e-3)
