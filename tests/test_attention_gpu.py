@@ -95,6 +95,8 @@ CASES = [
     (1, 1700, 220, 2, 2, False, 5),     # 15 key tiles: the longest sequence of the few-rows kernel
     (1, 1800, 248, 2, 1, False, 9),     # 16 key tiles: few rows, but left to the general kernel
     (2, 100, 30, 2, 2, True, [16, 1]),  # ragged single key tile
+    (2, 128, 128, 14, 2, False, [9, 30]),   # Dream heads under tensor parallelism 2 (7 query heads per KV head)
+    (2, 128, 128, 7, 1, True, [20, 3]),     # ... and 4
 ]
 
 

@@ -76,7 +76,9 @@ def test_gathered_linear_scatter_scale_and_device_count(cuda_device, a_mode):
 
 @pytest.mark.parametrize("a_mode", [0, 1], ids=["staged", "gather4"])
 @pytest.mark.parametrize("rows,hidden,inter,tile_n", [(26, 4096, 12288, 0), (410, 4096, 12288, 0), (130, 512, 1024, 64),
-                                                       (130, 512, 1024, 128), (1, 256, 128, 64)])
+                                                       (130, 512, 1024, 128), (1, 256, 128, 64),
+                                                       # Dream-7B FFN shards under tensor parallelism 2 and 4, LLaDA-8B under 8
+                                                       (410, 3584, 9472, 0), (410, 3584, 4736, 0), (48, 4096, 1536, 0)])
 def test_swiglu_ffn_matches_oracle(cuda_device, a_mode, rows, hidden, inter, tile_n):
     from dyllm_b200 import ops
 
