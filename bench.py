@@ -456,7 +456,8 @@ def run_ours(args, cfg, tau):
     barrier()
     t0 = time.perf_counter()
     e2e_gens = max(1, min(args.steps, 2))
-    for _ in range(e2e_gens):
+    out_tokens = None
+    for _ in range(0 if args.no_e2e else e2e_gens):
         out_tokens = sr.generate(prompts, GEN)
     barrier()
     e2e_s = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
@@ -464,7 +465,7 @@ def run_ours(args, cfg, tau):
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_s = float(e2e_s.item())
     io_per_gen = {k: v // e2e_gens for k, v in runner.io_bytes.items()}   # read before the profiling pass adds to it
-    assert len(out_tokens) == B and len(out_tokens[0]) == GEN
+    assert out_tokens is None or (len(out_tokens) == B and len(out_tokens[0]) == GEN)
 
     # ---- per-kernel durations: one more generation of the same workload with CUDA events around this
     # library's main kernels (events cannot be timed inside a graph, so this pass launches eagerly) ----
@@ -567,8 +568,8 @@ def run_ours(args, cfg, tau):
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_d,
         "clocks": clocks, "gpu_launches": launches,
-        "e2e": {"value": e2e_gens * B * GEN / e2e_s, "unit": "tokens/s",
-                "h2d_bytes_per_step": io_per_gen["h2d"], "d2h_bytes_per_step": io_per_gen["d2h"]},
+        "e2e": None if args.no_e2e else {"value": e2e_gens * B * GEN / e2e_s, "unit": "tokens/s",
+                                         "h2d_bytes_per_step": io_per_gen["h2d"], "d2h_bytes_per_step": io_per_gen["d2h"]},
         "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels,
         "salient_rows_per_layer": {"mean": (sum(sal) / len(sal)) if sal else None, "max": max(sal) if sal else None},
     }
@@ -604,6 +605,7 @@ def main():
     ap.add_argument("--denoise-steps", type=int, default=0, help="debug only")
     ap.add_argument("--full-steps", type=int, default=None, help="debug only: dense steps per generation")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="sweeps: skip the end-to-end leg (e2e is then null)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     tau = None if args.dense else (args.tau if args.tau is not None else cfg["tau"])
