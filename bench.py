@@ -409,6 +409,8 @@ def run_ours(args, cfg, tau):
             comm = TpComm.from_process_group(dev, slot_bytes=slot_rows * hidden * 2)
             layers.set_tp_comm(comm)
         layers.set_layout(layout)
+    layers.set_projection_backend(args.projection)
+    layers.set_dense_attention_backend(args.dense_attention)
 
     tp_parity = None
     if world > 1 and not args.no_tp_parity:
@@ -557,6 +559,8 @@ def run_ours(args, cfg, tau):
                "stage_seconds_per_layer_step": stages}
     cfg_d = config_dict(cfg, tau, world, args)
     cfg_d["tp_exchange"] = exchange
+    cfg_d["all_row_projections"] = args.projection
+    cfg_d["dense_step_attention"] = args.dense_attention
     if world > 1:
         cfg_d["layout"] = layout
         if layout == "sequence":
@@ -604,6 +608,10 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers marks the line invalid")
     ap.add_argument("--denoise-steps", type=int, default=0, help="debug only")
     ap.add_argument("--full-steps", type=int, default=None, help="debug only: dense steps per generation")
+    ap.add_argument("--projection", default="cublas", choices=["cublas", "tcgen05"],
+                    help="GEMM of the all-row q / o projections: cuBLAS (default) or this package's tcgen05 GEMM")
+    ap.add_argument("--dense-attention", default="sdpa", choices=["tcgen05", "sdpa"],
+                    help="attention of the dense steps: torch SDPA (default) or this package's exact-attention kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="sweeps: skip the end-to-end leg (e2e is then null)")
     args = ap.parse_args()

@@ -53,6 +53,7 @@ SIGNATURES: dict[str, tuple] = {
     "dyllm_head_rms_norm": (I, [P, P, F, I, P, I, I, P]),
     "dyllm_rope_neox": (I, [P, P, P, P, I, P, I, I, I, P]),
     "dyllm_row_confidence": (I, [P, I, I, c_int64, P, P, P]),
+    "dyllm_confidence_unmask": (I, [P, P, P, I, c_int64, P, I, I, I, I, I, c_int64, P, P, P]),
     "dyllm_kv_cache_update": (I, [P, P, P, P, P, P, I, P, P, P, P, I, I, P, I, I, P, P, P, P]),
     "dyllm_tp_comm_create": (I, [I, I, Z, P]),
     "dyllm_tp_comm_region_bytes": (Z, [P]),
@@ -82,7 +83,7 @@ KERNELS_PER_CALL = {
     "dyllm_cache_get_seqs": 1, "dyllm_cache_get_block": 1, "dyllm_cache_reset_full": 1, "dyllm_cache_reset_block": 1,
     "dyllm_cache_scatter_update": 1, "dyllm_gathered_linear": 2, "dyllm_swiglu_ffn": 3, "dyllm_cache_dest_rows": 1, "dyllm_moe_route": 1, "dyllm_moe_ffn": 5,
     "dyllm_attention_sparse_varlen": 2, "dyllm_attention_salient_rows": 2, "dyllm_delta_v_update": 1,
-    "dyllm_add_rms_norm": 1, "dyllm_add_rms_norm_segmented": 1, "dyllm_add_rms_norm_rows": 1, "dyllm_head_rms_norm": 1, "dyllm_rope_neox": 1, "dyllm_row_confidence": 1, "dyllm_kv_cache_update": 1,
+    "dyllm_add_rms_norm": 1, "dyllm_add_rms_norm_segmented": 1, "dyllm_add_rms_norm_rows": 1, "dyllm_head_rms_norm": 1, "dyllm_rope_neox": 1, "dyllm_row_confidence": 1, "dyllm_confidence_unmask": 1, "dyllm_kv_cache_update": 1,
     "dyllm_tp_push_rows": 1, "dyllm_tp_reduce_rows": 1, "dyllm_tp_allreduce_rows": 2, "dyllm_tp_push_f32": 1,
     "dyllm_tp_reduce_f32": 1, "dyllm_tp_allreduce_f32": 2, "dyllm_tp_gather_rows": 2, "dyllm_tp_gather_push": 1,
     "dyllm_tp_gather_finish": 1, "dyllm_tp_scatter_push": 1,

@@ -201,6 +201,95 @@ rope_neox_kernel(uint4* __restrict__ x, const int64_t* __restrict__ positions, c
 // exp(x_j - max), token = the first j that attains the maximum.  One CTA per row, one pass over the row
 // with 16-byte loads: every thread keeps a running (max, sum, argmax) and rescales its sum when its
 // maximum grows; the block then merges the 256 triples.
+// Confidence rule of the sampler for one block of candidates per sequence (ref: sampler.py:244-315): among the
+// block's positions that still hold the mask token, the num_transfer most confident ones (ties: the lowest
+// position) take their best token.  One CTA per sequence; the chosen positions come out ascending.
+constexpr int kUnmaskThreads = 128;
+constexpr int kUnmaskMaxBlock = 1024;
+constexpr int kUnmaskMaxPicks = 64;
+
+__global__ void __launch_bounds__(kUnmaskThreads)
+confidence_unmask_kernel(const float* __restrict__ conf, const int64_t* __restrict__ best_token,
+                         int64_t* __restrict__ tokens, int64_t seq_pitch, const int64_t* __restrict__ step_counter,
+                         int steps_per_block, int num_blocks, int prompt_len, int block_len, int num_transfer,
+                         int64_t mask_id, int64_t* __restrict__ picked_pos, int32_t* __restrict__ picked_count) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float s_conf[kUnmaskMaxBlock];
+  __shared__ float s_best[kUnmaskThreads / 32];
+  __shared__ int s_arg[kUnmaskThreads / 32];
+  __shared__ int s_pick[kUnmaskMaxPicks];
+  __shared__ int s_n;
+  const int b = blockIdx.x;
+  int64_t blk = step_counter ? *step_counter / steps_per_block : 0;
+  blk = blk > num_blocks - 1 ? num_blocks - 1 : blk;
+  const int start = prompt_len + static_cast<int>(blk) * block_len;
+  int64_t* row = tokens + static_cast<int64_t>(b) * seq_pitch;
+  for (int i = threadIdx.x; i < block_len; i += kUnmaskThreads)
+    s_conf[i] = row[start + i] == mask_id ? conf[static_cast<int64_t>(b) * block_len + i] : -1.0f;
+  if (threadIdx.x == 0)
+    s_n = 0;
+  __syncthreads();
+  for (int pick = 0; pick < num_transfer; ++pick) {
+    float best = -1.0f;
+    int arg = 0x7fffffff;
+    for (int i = threadIdx.x; i < block_len; i += kUnmaskThreads) {
+      const float c = s_conf[i];
+      if (c > best || (c == best && c >= 0.f && i < arg)) {
+        best = c;
+        arg = i;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, off);
+      if (ob > best || (ob == best && oa < arg)) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    if ((threadIdx.x & 31) == 0) {
+      s_best[threadIdx.x >> 5] = best;
+      s_arg[threadIdx.x >> 5] = arg;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < kUnmaskThreads / 32; ++w)
+        if (s_best[w] > best || (s_best[w] == best && s_arg[w] < arg)) {
+          best = s_best[w];
+          arg = s_arg[w];
+        }
+      if (best >= 0.f) {         // a masked candidate is left
+        s_pick[s_n++] = arg;
+        s_conf[arg] = -2.0f;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const int n = s_n;
+    for (int i = 1; i < n; ++i) {   // ascending positions (the kernels that follow expect sorted row lists)
+      const int v = s_pick[i];
+      int j = i - 1;
+      while (j >= 0 && s_pick[j] > v) {
+        s_pick[j + 1] = s_pick[j];
+        --j;
+      }
+      s_pick[j + 1] = v;
+    }
+    for (int i = 0; i < n; ++i) {
+      const int pos = start + s_pick[i];
+      row[pos] = best_token[static_cast<int64_t>(b) * block_len + s_pick[i]];
+      picked_pos[static_cast<int64_t>(b) * num_transfer + i] = pos;
+    }
+    for (int i = n; i < num_transfer; ++i)
+      picked_pos[static_cast<int64_t>(b) * num_transfer + i] = -1;
+    if (picked_count)
+      picked_count[b] = n;
+  }
+}
+
 constexpr int kConfThreads = 256;
 
 __global__ void __launch_bounds__(kConfThreads)
@@ -424,6 +513,26 @@ int dyllm_row_confidence(const void* logits, int rows, int vocab, int64_t pitch,
   DYLLM_LAUNCH(row_confidence_kernel, rows, kConfThreads, 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(logits), vocab, pitch, conf, token);
   return check_launch("row_confidence");
+}
+
+int dyllm_confidence_unmask(const float* conf, const int64_t* best_token, int64_t* tokens, int batch,
+                            int64_t seq_pitch, const int64_t* step_counter, int steps_per_block, int num_blocks,
+                            int prompt_len, int block_len, int num_transfer, int64_t mask_id, int64_t* picked_pos,
+                            int32_t* picked_count, void* stream) {
+  DYLLM_REQUIRE(batch >= 0 && block_len > 0 && block_len <= kUnmaskMaxBlock && num_transfer > 0 &&
+                    num_transfer <= kUnmaskMaxPicks && num_transfer <= block_len,
+                DYLLM_ERR_INVALID_ARGUMENT, "confidence_unmask: batch %d block %d (<= %d) picks %d (<= %d)", batch,
+                block_len, kUnmaskMaxBlock, num_transfer, kUnmaskMaxPicks);
+  DYLLM_REQUIRE(steps_per_block > 0 && num_blocks > 0 && prompt_len >= 0 &&
+                    seq_pitch >= static_cast<int64_t>(prompt_len) + static_cast<int64_t>(num_blocks) * block_len,
+                DYLLM_ERR_INVALID_ARGUMENT, "confidence_unmask: the blocks do not fit the token rows");
+  if (batch == 0)
+    return DYLLM_OK;
+  DYLLM_REQUIRE(conf && best_token && tokens && picked_pos, DYLLM_ERR_INVALID_ARGUMENT, "confidence_unmask: null pointer");
+  DYLLM_LAUNCH(confidence_unmask_kernel, batch, kUnmaskThreads, 0, static_cast<cudaStream_t>(stream), conf, best_token,
+               tokens, seq_pitch, step_counter, steps_per_block, num_blocks, prompt_len, block_len, num_transfer, mask_id,
+               picked_pos, picked_count);
+  return check_launch("confidence_unmask");
 }
 
 }  // extern "C"

@@ -254,6 +254,55 @@ def bench_salient_attention(args):
     return ms, 2.0 * k.numel() * 2 + 2.0 * iq.numel() * H * D * 2, "B"
 
 
+def _bench_projection(args, backend):
+    """q / o projection of every row of the batch (8192 x 4096 x 4096): cuBLAS or this package's tcgen05 GEMM."""
+    from . import layers
+
+    dev = torch.device("cuda")
+    x = torch.randn(B * L, HID, device=dev).bfloat16()
+    w = (torch.randn(HID, HID, device=dev) * 0.02).bfloat16()
+    layers.set_projection_backend(backend)
+    try:
+        ms = time_launches(lambda: layers._project(x, w, None), args.iters, args.flush)
+    finally:
+        layers.set_projection_backend("cublas")
+    return ms, 2.0 * B * L * HID * HID, "F"
+
+
+def bench_proj_cublas(args):
+    return _bench_projection(args, "cublas")
+
+
+def bench_proj_own(args):
+    return _bench_projection(args, "tcgen05")
+
+
+def _bench_dense_attention(args, backend):
+    """Attention of a dense step (every row a query) on the exact-attention kernel or torch's SDPA."""
+    from types import SimpleNamespace
+
+    from . import layers
+
+    dev = torch.device("cuda")
+    q, k, v = (torch.randn(B * L, H, D, device=dev).bfloat16() for _ in range(3))
+    cu = torch.arange(0, B * L + 1, L, dtype=torch.int32, device=dev)
+    ctx = SimpleNamespace(cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=L, context_lens_cpu=[L] * B)
+    layers.set_dense_attention_backend(backend)
+    try:
+        ms = time_launches(lambda: layers._dense_attention(q, k, v, ctx, D ** -0.5), args.iters, args.flush)
+    finally:
+        layers.set_dense_attention_backend("sdpa")
+    return ms, 4.0 * B * L * L * H * D, "F"
+
+
+def bench_dense_attention_own(args):
+    return _bench_dense_attention(args, "tcgen05")
+
+
+def bench_dense_attention_sdpa(args):
+    return _bench_dense_attention(args, "sdpa")
+
+
 def bench_steps(args):
     """One refresh period of sparse denoising steps (3 response-only + 1 full-sequence) of the 32-layer
     LLaDA-8B shape at batch 16, launched eagerly after one dense step: the launch sequence of the
@@ -291,7 +340,9 @@ def bench_steps(args):
 KERNELS = {"stats": bench_stats, "select": bench_select, "scatter": bench_scatter, "get_seqs": bench_get_seqs,
            "ffn": bench_ffn, "ffn_graph": bench_ffn_graph, "kv_proj": bench_kv_proj, "norm": bench_norm,
            "norm_rows": bench_norm_rows, "rope": bench_rope, "attention": bench_attention,
-           "salient_attention": bench_salient_attention, "steps": bench_steps}
+           "salient_attention": bench_salient_attention, "proj_cublas": bench_proj_cublas, "proj_own": bench_proj_own,
+           "dense_attention_own": bench_dense_attention_own, "dense_attention_sdpa": bench_dense_attention_sdpa,
+           "steps": bench_steps}
 
 
 def main():

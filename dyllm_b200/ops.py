@@ -339,6 +339,27 @@ def row_confidence(logits: torch.Tensor):
     return conf, token
 
 
+def confidence_unmask_(conf: torch.Tensor, best_token: torch.Tensor, tokens: torch.Tensor, step_counter: torch.Tensor | None,
+                       steps_per_block: int, prompt_len: int, block_len: int, num_transfer: int, mask_id: int,
+                       picked_pos: torch.Tensor | None = None):
+    """Unmasks, in place in ``tokens [batch, length]``, the ``num_transfer`` most confident still-masked positions
+    of every sequence's current block and returns their positions ``[batch, num_transfer]`` (ascending; -1 padding).
+
+    ref: dyllm/model_executor/layers/sampler.py:244-315.
+    """
+    require_cuda(conf, "conf", torch.float32, 2)
+    require_cuda(best_token, "best_token", torch.int64, 2)
+    require_cuda(tokens, "tokens", torch.int64, 2)
+    batch, length = tokens.shape
+    num_blocks = (length - prompt_len) // block_len
+    if picked_pos is None:
+        picked_pos = torch.empty((batch, num_transfer), dtype=torch.int64, device=tokens.device)
+    call("dyllm_confidence_unmask", ptr(conf), ptr(best_token), ptr(tokens), batch, tokens.stride(0), ptr(step_counter),
+         int(steps_per_block), int(num_blocks), int(prompt_len), int(block_len), int(num_transfer), int(mask_id),
+         ptr(picked_pos), None, stream_ptr(tokens.device))
+    return picked_pos
+
+
 def moe_route(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, renormalize: bool = False,
               idx: torch.Tensor | None = None, num_rows: int | None = None, num_rows_dev: torch.Tensor | None = None):
     """fp32 softmax router with top-k selection; returns (weights fp32 [rows, k], expert ids int32 [rows, k]).

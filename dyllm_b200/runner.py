@@ -387,14 +387,9 @@ class StepRunner:
         else:
             rows = st.row_base_full + start + st.blk_ar
         conf, tok = self._confidence(self._block_logits(hidden, rows.reshape(-1)), B, blk_len)
-        cols = (start + st.blk_ar).expand(B, -1)
-        still_masked = tokens.gather(1, cols) == self.mask_id
-        conf = torch.where(still_masked, conf, torch.full_like(conf, -1.0))
-        _, top_i = conf.topk(st.num_transfer, dim=-1)
-        top_i, _ = torch.sort(top_i, dim=-1)          # ascending rows for the kernels
-        new_pos = top_i + start
-        tokens.scatter_(1, new_pos, tok.gather(1, top_i))
-        st.last_pos.copy_(new_pos)
+        # masked candidates of the block -> the num_transfer most confident ones take their token (one kernel)
+        ops.confidence_unmask_(conf, tok, tokens, st.step_t, st.steps_per_block, P, blk_len, st.num_transfer, self.mask_id,
+                               picked_pos=st.last_pos)
         st.step_t.add_(1)
 
     def _run_step(self, st, kind: str) -> None:

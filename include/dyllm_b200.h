@@ -358,6 +358,23 @@ int dyllm_head_rms_norm(void* x, const void* weight, float eps, int rows, const 
 int dyllm_row_confidence(const void* logits, int rows, int vocab, int64_t pitch, float* conf, int64_t* token,
                          void* stream);
 
+/* The unmasking rule of the confidence sampler for the current block of every sequence, on the device:
+ * block = min(*step_counter / steps_per_block, num_blocks - 1) (step_counter null = block 0), candidates =
+ * the block's positions prompt_len + block * block_len + i, i < block_len, that still hold mask_id in
+ * tokens [batch, seq_pitch] (int64); conf / best_token [batch, block_len] are their confidences and most likely
+ * tokens (dyllm_row_confidence).  The num_transfer most confident candidates (ties: the lowest position) get
+ * their token written into `tokens`; their positions go to picked_pos [batch, num_transfer] in ascending order
+ * (-1 padding when fewer masked candidates were left) and their number to picked_count [batch] (nullable).
+ * block_len <= 1024, num_transfer <= 64.  Replaces the gather / compare / where / top-k / sort / scatter sequence
+ * of torch kernels a step driver would issue.
+ * ref: dyllm/model_executor/layers/sampler.py:244-315 (scores sorted per sequence, the first num_transfer kept;
+ *      the Triton helpers ragged_to_dense_kernel / filter_and_count_kernel, sampler.py:43-175),
+ *      dyllm/engine/sequence.py:69-75 (update_token). */
+int dyllm_confidence_unmask(const float* conf, const int64_t* best_token, int64_t* tokens, int batch,
+                            int64_t seq_pitch, const int64_t* step_counter, int steps_per_block, int num_blocks,
+                            int prompt_len, int block_len, int num_transfer, int64_t mask_id, int64_t* picked_pos,
+                            int32_t* picked_count, void* stream);
+
 /* NeoX-style rotary embedding applied in place to x [rows, heads, 128] (bf16): row r uses the angle
  * table row of positions[pos_idx ? pos_idx[r] : r], clamped to [0, max_pos); cos_sin is fp32
  * [max_pos, 128] = cos(64) | sin(64).  num_rows_dev (nullable) bounds the rows on the device.

@@ -289,6 +289,23 @@ def swiglu_ffn(x, w_gate_up, w_down, round_bf16=True):
     return r(h @ w2.t())
 
 
+def confidence_unmask(conf, best_token, tokens, block_start, block_len, num_transfer, mask_id):
+    """Unmasking rule of the confidence sampler for one block (ref: dyllm/model_executor/layers/sampler.py:244-315:
+    candidates = still-masked positions of the block, scores sorted descending per sequence, the first
+    num_transfer kept; engine/sequence.py:69-75 writes the kept tokens).  Ties go to the lowest position.
+    Returns (tokens_after, picked positions per sequence ascending)."""
+    conf, best_token, tokens = _np(conf), _np(best_token), _np(tokens).copy()
+    picked = []
+    for b in range(tokens.shape[0]):
+        cand = [i for i in range(block_len) if tokens[b, block_start + i] == mask_id]
+        cand.sort(key=lambda i: (-float(conf[b, i]), i))
+        keep = sorted(cand[:num_transfer])
+        for i in keep:
+            tokens[b, block_start + i] = best_token[b, i]
+        picked.append([block_start + i for i in keep])
+    return tokens, picked
+
+
 def moe_gate(x, router_weight, top_k, renormalize=False):
     """fp32 softmax router, top-k.  ref: dyllm/model_executor/layers/fused_moe.py:375-407."""
     logits = _f32(x) @ _f32(router_weight).t()

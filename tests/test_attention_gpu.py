@@ -269,3 +269,31 @@ def test_attention_cache_resident_context_equals_packed_path(cuda_device, case_i
                                    case["max_q"], case["max_k"], Tq, d(case["cu_sal"]), d(case["idx_q"]), stats2, mask2, TAU,
                                    ro, None, v_layout=1 | 4, c_cache=(d(seq_starts), d(seq_ids), True))
     assert torch.equal(out2.cpu(), ref_out) and torch.equal(stats2.cpu(), ref_stats) and torch.equal(mask2.cpu(), ref_mask)
+
+
+@pytest.mark.parametrize("lens,H,Hkv", [([512] * 4, 4, 4), ([200, 75, 333], 4, 2), ([768] * 2, 14, 2), ([128], 2, 1)])
+def test_dense_step_attention_on_the_exact_kernel(cuda_device, lens, H, Hkv):
+    """Dense steps list every query row of the batch for the exact-attention kernel (flash-attn varlen call of
+    dyllm/model_executor/layers/attention.py:39-52); both backends agree with the fp32 oracle."""
+    from types import SimpleNamespace
+
+    from dyllm_b200 import _lib, layers
+
+    g = torch.Generator().manual_seed(sum(lens) + H)
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    q, k, v = (torch.randn(T, h, 128, generator=g).bfloat16() for h in (H, Hkv, Hkv))
+    want = orc.exact_attention_varlen(q, k, v, cu, cu)
+    ctx = SimpleNamespace(cu_seqlens_q=cu.to(cuda_device), cu_seqlens_k=cu.to(cuda_device), max_seqlen_q=max(lens),
+                          context_lens_cpu=lens)
+    d = lambda t: t.to(cuda_device)
+    try:
+        for backend in ("tcgen05", "sdpa"):
+            layers.set_dense_attention_backend(backend)
+            got = layers._dense_attention(d(q), d(k), d(v), ctx, 128 ** -0.5).float().cpu()
+            assert _lib.load().dyllm_device_status() == 0
+            diff = got - want
+            assert diff.abs().max().item() <= 2e-2, backend
+            assert (diff.norm() / want.norm()).item() <= 1e-2, backend
+    finally:
+        layers.set_dense_attention_backend("sdpa")

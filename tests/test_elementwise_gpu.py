@@ -138,3 +138,41 @@ def test_head_rms_norm_matches_the_oracle(cuda_device, rows, heads, live):
     # the row-wise norm kernel on the flattened view gives the same values up to the order of its fp32 sum
     ref = ops.add_rms_norm(x.view(-1, 128).to(cuda_device), w.to(cuda_device), 1e-5).cpu().view(rows, heads, 128)
     torch.testing.assert_close(got[:live].float(), ref[:live].float(), rtol=1.6e-2, atol=1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch,prompt,block_len,blocks,num_transfer,step", [
+    (16, 256, 32, 8, 1, 0), (16, 256, 32, 8, 1, 100), (3, 40, 8, 4, 2, 9), (5, 7, 64, 2, 4, 40), (2, 0, 1024, 1, 64, 0),
+    (4, 16, 32, 2, 8, 3),
+])
+def test_confidence_unmask_matches_the_sampler_rule(cuda_device, batch, prompt, block_len, blocks, num_transfer, step):
+    g = torch.Generator().manual_seed(batch * 131 + block_len)
+    mask_id, steps_per_block = 126336, 32
+    length = prompt + blocks * block_len
+    block = min(step // steps_per_block, blocks - 1)
+    start = prompt + block * block_len
+    tokens = torch.randint(0, 1000, (batch, length), generator=g)
+    masked = torch.rand(batch, length, generator=g) < 0.6
+    tokens = torch.where(masked, torch.full_like(tokens, mask_id), tokens)
+    tokens[0, start:start + block_len] = mask_id                    # everything masked
+    if batch > 1:
+        tokens[1, start:start + block_len] = 7                       # nothing masked: no pick
+    if batch > 2:
+        tokens[2, start:start + block_len] = 7
+        tokens[2, start + block_len - 1] = mask_id                   # fewer candidates than picks (when picks > 1)
+    conf = torch.rand(batch, block_len, generator=g)
+    conf[:, ::3] = conf[:, :1]                                       # ties: the lowest position wins
+    best = torch.randint(0, 1000, (batch, block_len), generator=g)
+    want_tokens, want_picked = orc.confidence_unmask(conf, best, tokens, start, block_len, num_transfer, mask_id)
+
+    dev_tokens = torch.zeros(batch, length + 3, dtype=torch.int64, device=cuda_device)[:, :length]   # pitch != length
+    dev_tokens.copy_(tokens)
+    assert dev_tokens.stride(0) == length + 3
+    counter = torch.tensor([step], dtype=torch.int64, device=cuda_device)
+    picked = ops.confidence_unmask_(conf.to(cuda_device), best.to(cuda_device), dev_tokens, counter, steps_per_block, prompt,
+                                    block_len, num_transfer, mask_id)
+    assert torch.equal(dev_tokens.cpu(), torch.from_numpy(want_tokens))
+    for b in range(batch):
+        got = [p for p in picked[b].tolist() if p >= 0]
+        assert got == want_picked[b], (b, got, want_picked[b])
+        assert picked[b].tolist()[len(got):] == [-1] * (num_transfer - len(got))
