@@ -127,8 +127,9 @@ __device__ __forceinline__ int lower_bound_i32(const int32_t* a, int n, int key)
 // so a warp reads 1536 contiguous bytes per group; a warp takes SUPER groups, a tile 8 * SUPER * 128
 // rows.  Flags become a 4-bit nibble per thread; positions come from a warp prefix sum of the nibble
 // popcounts, a block scan over the warps and a decoupled look-back over the tiles (32 predecessors per
-// step).  The prefix front moves a bounded number of tiles per microsecond, so large inputs use large
-// tiles (SUPER = 8) and small inputs small ones (SUPER = 2) for parallelism.
+// step).  The prefix front moves a bounded number of tiles per microsecond, which is what small inputs
+// (up to 64 Ki rows, SUPER = 2) want: many small tiles in flight.  Larger inputs take
+// salient_select_ranges_kernel below.
 template <int SUPER>
 __global__ void __launch_bounds__(kSelWarps * 32)
 salient_select_kernel(const float* __restrict__ stats, int rows, float threshold,
@@ -322,6 +323,222 @@ salient_select_kernel(const float* __restrict__ stats, int rows, float threshold
   }
 }
 
+// Large inputs: one pass over contiguous row ranges.  The grid holds as many CTAs as the device runs at once;
+// CTA number c (by arrival) owns rows [c * rows_per_cta, (c + 1) * rows_per_cta).  It streams the statistics of
+// its range once (twelve 16-byte loads in flight per thread), writes the mask bytes and keeps the flags of the
+// range in shared memory (one nibble per four rows).  Then every thread counts 32 rows at a time from those
+// flags, a block scan turns the counts into positions, the CTA publishes the count of its range, adds the counts
+// of the ranges before it (each belongs to a CTA that arrived earlier, so the wait cannot deadlock, and it is
+// bounded) and writes its part of the lists.  No chain of dependent tiles: one exchange of ~600 counts for the
+// whole input, and the statistics are read exactly once.
+constexpr int kRangeGroups = 4;             // 128-row groups per warp and iteration (twelve loads per thread)
+constexpr int kRangeMaxRows = 64 * 1024;    // rows of one range (16 KB of flags)
+constexpr int kRangeThreads = kSelWarps * 32;
+
+__global__ void __launch_bounds__(kRangeThreads, 4)
+salient_select_ranges_kernel(const float* __restrict__ stats, int rows, float threshold,
+                             const int32_t* __restrict__ cu_seqlens_q, int batch,
+                             const int32_t* __restrict__ cu_promptlens, int64_t* __restrict__ idx_out,
+                             int32_t* __restrict__ idx32_out, int64_t* __restrict__ idx_k_out,
+                             int32_t* __restrict__ cu_salientlens_out, int32_t* __restrict__ count_out,
+                             uint8_t* __restrict__ mask_out, SelectWorkspace* ws, int rows_per_cta, int* status_word) {
+  pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
+  pdl_trigger();
+  __shared__ __align__(8) uint8_t s_nib[kRangeMaxRows / 4];   // flags of four consecutive rows per byte
+  __shared__ int s_pre[kRangeMaxRows / 32];                    // flags of the range before each 32-row chunk
+  __shared__ int s_warp_sum[2][kSelWarps];
+  __shared__ int s_cta;
+  __shared__ int s_prefix;
+  __shared__ int s_b_range[2];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0)
+    s_cta = static_cast<int>(atomicAdd(&ws->ticket, 1u));
+  __syncthreads();
+  const int cta = s_cta;
+  const int64_t r0_64 = static_cast<int64_t>(cta) * rows_per_cta;
+  if (r0_64 >= rows)
+    return;   // not reached: the grid holds exactly the ranges of the input
+  const int range0 = static_cast<int>(r0_64);
+  const int range1 = static_cast<int>(min(r0_64 + rows_per_cta, static_cast<int64_t>(rows)));
+  const int n_groups = (range1 - range0 + 127) >> 7;
+  const int iters = (n_groups + kSelWarps * kRangeGroups - 1) / (kSelWarps * kRangeGroups);
+  if (threadIdx.x == 32)
+    s_b_range[0] = lower_bound_i32(cu_seqlens_q, batch + 1, range0);
+  if (threadIdx.x == 64)
+    s_b_range[1] = lower_bound_i32(cu_seqlens_q, batch + 1, range1);
+
+  // 1. one pass over the statistics: flags to shared memory, mask bytes out.  A group that lies completely
+  // inside the range (every group but the last one of the input) takes the branch-free path: the test is
+  // uniform over the warp.
+  for (int it = 0; it < iters; ++it) {
+    float4 v[kRangeGroups][3];
+    const int grp0 = (it * kSelWarps + warp) * kRangeGroups;
+#pragma unroll
+    for (int g = 0; g < kRangeGroups; ++g) {
+      const int grp = grp0 + g;
+      const int row0 = range0 + grp * 128 + lane * 4;
+      if (grp < n_groups && range0 + grp * 128 + 128 <= range1) {
+        const float4* src = reinterpret_cast<const float4*>(stats + static_cast<int64_t>(row0) * 3);
+        v[g][0] = __ldg(src);
+        v[g][1] = __ldg(src + 1);
+        v[g][2] = __ldg(src + 2);
+      } else if (grp < n_groups) {
+        float t[12];
+#pragma unroll
+        for (int i = 0; i < 12; ++i) {
+          const int64_t e = static_cast<int64_t>(row0) * 3 + i;
+          t[i] = e < static_cast<int64_t>(rows) * 3 ? __ldg(stats + e) : 0.f;
+        }
+        v[g][0] = make_float4(t[0], t[1], t[2], t[3]);
+        v[g][1] = make_float4(t[4], t[5], t[6], t[7]);
+        v[g][2] = make_float4(t[8], t[9], t[10], t[11]);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < kRangeGroups; ++g) {
+      const int grp = grp0 + g;
+      if (grp >= n_groups)
+        continue;   // uniform over the warp
+      const int row0 = range0 + grp * 128 + lane * 4;
+      const float4 a = v[g][0], b = v[g][1], c = v[g][2];
+      uint32_t f = (below_threshold(a.x, a.y, a.z, threshold) ? 1u : 0u) |
+                   (below_threshold(a.w, b.x, b.y, threshold) ? 2u : 0u) |
+                   (below_threshold(b.z, b.w, c.x, threshold) ? 4u : 0u) |
+                   (below_threshold(c.y, c.z, c.w, threshold) ? 8u : 0u);
+      if (range0 + grp * 128 + 128 <= range1) {
+        if (mask_out)   // bits 0..3 of f to bytes 0..3
+          *reinterpret_cast<uint32_t*>(mask_out + row0) = (f | (f << 7) | (f << 14) | (f << 21)) & 0x01010101u;
+      } else {
+        const int left = range1 - row0;   // rows of this thread inside the input
+        f &= left >= 4 ? 15u : (left > 0 ? (1u << left) - 1u : 0u);
+        if (mask_out) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j < left)
+              mask_out[row0 + j] = (f >> j) & 1u;
+        }
+      }
+      s_nib[grp * 32 + lane] = static_cast<uint8_t>(f);
+    }
+  }
+  __syncthreads();
+
+  // 2. positions inside the range: pass p gives thread t the 32 rows of chunk p * 256 + t (eight flag bytes);
+  // a block scan per pass.  The chunk's flags stay in a register for the writes below.
+  const int n_chunks = n_groups * 4;
+  const int passes = (n_chunks + kRangeThreads - 1) / kRangeThreads;
+  unsigned long long bits[kRangeMaxRows / 32 / kRangeThreads];
+  int running = 0;   // flags of the passes so far (the same value in every thread)
+#pragma unroll
+  for (int ps = 0; ps < kRangeMaxRows / 32 / kRangeThreads; ++ps) {
+    bits[ps] = 0ull;
+    if (ps >= passes)
+      continue;   // uniform over the block
+    const int chunk = ps * kRangeThreads + threadIdx.x;
+    if (chunk < n_chunks)
+      bits[ps] = *reinterpret_cast<const unsigned long long*>(s_nib + chunk * 8) & 0x0f0f0f0f0f0f0f0full;
+    const int mine = __popcll(bits[ps]);
+    int incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off)
+        incl += o;
+    }
+    if (lane == 31)
+      s_warp_sum[ps & 1][warp] = incl;
+    __syncthreads();
+    int before = running, total = 0;
+#pragma unroll
+    for (int w = 0; w < kSelWarps; ++w) {
+      const int ws_w = s_warp_sum[ps & 1][w];
+      before += w < warp ? ws_w : 0;
+      total += ws_w;
+    }
+    if (chunk < n_chunks)
+      s_pre[chunk] = before + incl - mine;
+    running += total;
+  }
+  // 3. count of this range out, counts of the earlier ranges in
+  if (warp == 0) {
+    volatile unsigned long long* tiles = ws->tiles;
+    if (lane == 0) {
+      tiles[cta] = (1ull << 32) | static_cast<unsigned int>(running);
+      __threadfence();
+    }
+    int before = 0;
+    bool gave_up = false;
+    for (int pr = lane; pr < cta; pr += 32) {
+      unsigned long long d = 0;
+      uint32_t spins = 0;
+      while ((((d = tiles[pr]) >> 32) & 3ull) == 0) {
+        if (++spins > kLookbackSpinLimit) {
+          gave_up = true;
+          break;
+        }
+      }
+      before += static_cast<int>(static_cast<unsigned int>(d));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+      before += __shfl_xor_sync(0xffffffffu, before, off);
+    gave_up = __any_sync(0xffffffffu, gave_up);
+    if (lane == 0) {
+      if (gave_up && status_word)
+        atomicCAS(status_word, 0, 102);
+      s_prefix = before;
+      if (range1 == rows)
+        count_out[0] = before + running;
+    }
+  }
+  __syncthreads();
+  const int prefix = s_prefix;
+
+  // 4. ordered writes: every thread walks over the set flags of its chunks
+#pragma unroll
+  for (int ps = 0; ps < kRangeMaxRows / 32 / kRangeThreads; ++ps) {
+    unsigned long long x = bits[ps];
+    if (x == 0ull)
+      continue;
+    const int chunk = ps * kRangeThreads + threadIdx.x;
+    int pos = prefix + s_pre[chunk];
+    const int row_base = range0 + chunk * 32;
+    while (x) {
+      const int i = __ffsll(static_cast<long long>(x)) - 1;   // bit 8 * byte + j: row 4 * byte + j of the chunk
+      x &= x - 1;
+      const int r = row_base + ((i >> 3) << 2) + (i & 7);
+      idx_out[pos] = r;
+      if (idx32_out)
+        idx32_out[pos] = r;
+      if (idx_k_out) {
+        const int b = lower_bound_i32(cu_seqlens_q, batch + 1, r + 1) - 1;   // sequence with cu_q[b] <= r < cu_q[b + 1]
+        idx_k_out[pos] = static_cast<int64_t>(r) + cu_promptlens[b + 1];
+      }
+      ++pos;
+    }
+  }
+  // 5. per-sequence prefix counts for the sequence boundaries inside this range
+  const int b_lo = s_b_range[0];
+  const int b_hi = s_b_range[1];
+  for (int b = b_lo + threadIdx.x; b < b_hi; b += blockDim.x) {
+    const int local = cu_seqlens_q[b] - range0;   // in [0, rows of the range)
+    const int chunk = local >> 5, within = local & 31;
+    unsigned long long x = *reinterpret_cast<const unsigned long long*>(s_nib + chunk * 8) & 0x0f0f0f0f0f0f0f0full;
+    // rows before `within`: whole bytes below byte within / 4, then the low bits of that byte
+    const int byte = within >> 2, j = within & 3;
+    const unsigned long long below = byte == 0 ? 0ull : (~0ull >> (64 - 8 * byte));
+    const unsigned long long part = ((1ull << j) - 1ull) << (8 * byte);
+    cu_salientlens_out[b] = prefix + s_pre[chunk] + __popcll(x & (below | part));
+  }
+  if (range1 == rows) {  // last range: boundaries at or beyond the end
+    const int total = prefix + running;
+    for (int b = b_hi + threadIdx.x; b <= batch; b += blockDim.x)
+      cu_salientlens_out[b] = total;
+  }
+}
+
 __global__ void select_empty_kernel(int32_t* cu_salientlens_out, int32_t* count_out, int batch) {
   pdl_wait();      // programmatic dependent launch: nothing before this reads an earlier kernel's data
   pdl_trigger();
@@ -373,11 +590,18 @@ int launch_salient_select(const float* stats, int rows, float threshold, const i
   if (cudaMemsetAsync(workspace, 0, select_workspace_bytes(rows), stream) != cudaSuccess)
     return set_error(DYLLM_ERR_CUDA, "salient_select: clearing the workspace failed");
   SelectWorkspace* w = static_cast<SelectWorkspace*>(workspace);
-  if (rows > 64 * 1024)
-    DYLLM_LAUNCH(salient_select_kernel<8>, cdiv_i(rows, kSelWarps * 8 * 128), kSelWarps * 32, 0, stream, 
+  if (rows > 64 * 1024) {
+    // contiguous ranges, one per CTA the device runs at once (four per SM: 63 registers, 18 KB of shared memory)
+    const int64_t resident = 4ll * sm_count();
+    int64_t per = (static_cast<int64_t>(rows) + resident - 1) / resident;
+    per = (per + 127) / 128 * 128;   // whole 128-row groups; the ranges stay balanced over the SMs
+    per = per < kSelTileRowsSmall ? kSelTileRowsSmall : per;   // the workspace holds one descriptor per 2048 rows
+    per = per > kRangeMaxRows ? kRangeMaxRows : per;
+    const int rows_per_cta = static_cast<int>(per);
+    DYLLM_LAUNCH(salient_select_ranges_kernel, cdiv_i(rows, rows_per_cta), kSelWarps * 32, 0, stream,
         stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
-        cu_salientlens_out, count_out, mask_out, w, device_status_word());
-  else
+        cu_salientlens_out, count_out, mask_out, w, rows_per_cta, device_status_word());
+  } else
     DYLLM_LAUNCH(salient_select_kernel<2>, cdiv_i(rows, kSelTileRowsSmall), kSelWarps * 32, 0, stream, 
         stats, rows, threshold, cu_seqlens_q, batch, cu_promptlens, idx_out, idx32_out, idx_k_out,
         cu_salientlens_out, count_out, mask_out, w, device_status_word());

@@ -349,7 +349,8 @@ def confidence_unmask_(conf: torch.Tensor, best_token: torch.Tensor, tokens: tor
     """
     require_cuda(conf, "conf", torch.float32, 2)
     require_cuda(best_token, "best_token", torch.int64, 2)
-    require_cuda(tokens, "tokens", torch.int64, 2)
+    if not (tokens.is_cuda and tokens.dtype == torch.int64 and tokens.dim() == 2 and tokens.stride(1) == 1):
+        raise RuntimeError("tokens must be a CUDA int64 matrix with unit column stride")
     batch, length = tokens.shape
     num_blocks = (length - prompt_len) // block_len
     if picked_pos is None:

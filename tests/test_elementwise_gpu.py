@@ -3,6 +3,7 @@ reference modules (bf16 outputs, one bf16 ulp of slack)."""
 import pytest
 import torch
 
+from dyllm_b200 import ops
 from oracle import dyllm_oracle as orc
 
 pytestmark = pytest.mark.gpu
