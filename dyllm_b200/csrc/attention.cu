@@ -20,9 +20,10 @@
 // other's exponentials.
 //
 // Pass B works on the salient keys rounded up to a multiple of 16 (the MMA shapes are chosen at run
-// time).  With at most 16 salient keys in the sequence (the common case) their K and dV rows are gathered
-// into a small dedicated buffer while the first tiles are still in flight, so pass B starts as soon as
-// pass A ends.
+// time).  With at most 16 salient keys in the sequence (the common case) their K and dV rows are requested
+// at the start of the item and land in a small dedicated buffer right after pass A, so pass B starts as
+// soon as pass A ends and nothing of the item's set-up delays the first logits.  The new context tile of a
+// full tile is stored (TMA) by the otherwise idle producer warp once the softmax threads have written it.
 #include "common.cuh"
 
 namespace dyllm {
@@ -217,6 +218,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __shared__ uint64_t q_full, k_full[2], k_empty[2], s_full[2], s_empty[2], b_full, p_full, pv_done, a_done, c_full;
   // delta kernel: buffers handed back to the producer / the MMA warp while the item is still in its epilogue
   __shared__ uint64_t q_free, kv0_free, kv1_free, o_free;
+  // delta kernel, full tiles: the softmax threads have written the new context tile; the producer stores it
+  __shared__ uint64_t c_stored;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_src[128];        // source row of each gather slot (-1 = none)
@@ -261,6 +264,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(&kv0_free, 1);
     mbar_init(&kv1_free, 1);
     mbar_init(&o_free, 256);
+    mbar_init(&c_stored, 256);
     fence_mbar_init();
     if (!EXACT)
       tma_prefetch_desc(&tmap_q);
@@ -284,6 +288,30 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     int n_items = 0;            // items started so far
     int kuse[2] = {0, 0};       // loads issued into each K stage
     int n_pv = 0;               // P V products waited for (EXACT)
+    int n_kv1 = 0, n_cst = 0;   // phases of kv1_free and c_stored waited for
+    AttnItem prev_it;           // the previous item of this CTA (its context tile may still have to be stored)
+    prev_it.tile_tma = false;
+    // K stage 1 of the previous item becomes free.  A full tile's new context sits there: once the softmax
+    // threads have written it, this warp stores it (out and, with an in-place cache, the cache rows) and waits
+    // until the stores have read shared memory.  Otherwise the softmax threads signal kv1_free themselves.
+    auto release_stage1 = [&]() {
+      if (prev_it.tile_tma) {
+        mbar_wait(&c_stored, (n_cst++) & 1, &abort_flag, p.status_word, 320);
+        if (lane == 0) {
+          tma_store_2d(&tmap_out, kv_smem1, prev_it.h * kD, prev_it.q0);
+          tma_store_2d(&tmap_out, kv_smem1 + kHalfBytes, prev_it.h * kD + 64, prev_it.q0);
+          if (p.c_cache) {
+            tma_store_2d(&tmap_c, kv_smem1, prev_it.h * kD, static_cast<int>(prev_it.q0 + prev_it.c_delta));
+            tma_store_2d(&tmap_c, kv_smem1 + kHalfBytes, prev_it.h * kD + 64, static_cast<int>(prev_it.q0 + prev_it.c_delta));
+          }
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        __syncwarp();
+      } else {
+        mbar_wait(&kv1_free, (n_kv1++) & 1, &abort_flag, p.status_word, 316);
+      }
+    };
     for (int item = blockIdx.x; item < p.num_items; item += gridDim.x) {
       AttnItem it;
       if (!decode_item<EXACT>(p, item, it))
@@ -318,8 +346,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       for (int kt = 0; kt < it.num_kt; ++kt) {
         const int s = kt & 1;
         const int u = kuse[s]++;
-        if (!EXACT && n_items > 0 && kt < 2)
-          mbar_wait(kt == 0 ? &kv0_free : &kv1_free, prev, &abort_flag, p.status_word, 316);
+        if (!EXACT && n_items > 0 && kt == 0)
+          mbar_wait(&kv0_free, prev, &abort_flag, p.status_word, 316);
+        if (!EXACT && n_items > 0 && kt == 1)
+          release_stage1();
         mbar_wait(&k_empty[s], (u & 1) ^ 1, &abort_flag, p.status_word, 301);
         if (lane == 0) {
           uint8_t* dst = s ? kv_smem1 : kv_smem0;
@@ -348,9 +378,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (it.num_st > 0)   // the last product has read both buffers: the next item may load into them
           mbar_wait(&pv_done, (n_pv++) & 1, &abort_flag, p.status_word, 315);
       } else if (n_items > 0 && it.num_kt < 2) {
-        mbar_wait(&kv1_free, prev, &abort_flag, p.status_word, 317);   // keep in step with every phase
+        release_stage1();   // no second key tile: the previous item's context tile still has to go out
       }
+      prev_it = it;
       ++n_items;
+    }
+    if (!EXACT && n_items > 0 && prev_it.tile_tma) {
+      release_stage1();   // context tile of the last item
+      if (lane == 0)
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
@@ -488,43 +524,23 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // a warp whose 32 query rows all lie past the end of the sequence keeps the barrier protocol going
       // but computes nothing
       const bool warp_live = q0 + qd * 32 < q_end;
-      // source rows of the first gather (salient key rows, or the query rows of the EXACT variant)
-      if (half == 0) {
-        int src = -1;
-        if (EXACT) {
-          if (q0 + row < q_end)
-            src = p.idx_q[sal_begin + q0 + row];
-        } else if (row < n_sal) {
-          src = p.idx_k ? p.idx_k[sal_begin + row] : p.idx_q[sal_begin + row] + k_shift;
-        }
-        s_src[row] = src;
-        s_sal_pos[row] = 0;
-      }
-      if (!EXACT) {
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        // mark the query rows of this tile that are salient (they take the exactly attended values)
-        for (int j = st_tid; j < n_sal; j += 256) {
-          const int rr = p.idx_q[sal_begin + j] - q0;
-          if (rr >= 0 && rr < kBQ)
-            s_sal_pos[rr] = static_cast<uint16_t>(j + 1);
-        }
-        if (fast) {
-          // early gather: 16 slots x 16 chunks of 16 bytes, one per thread, zeros past the list
-          const int r = st_tid >> 4, ch = st_tid & 15;
-          const int src = s_src[r];
-          const uint4 zero = make_uint4(0, 0, 0, 0);
-          const uint4 kv = src >= 0
-              ? __ldg(reinterpret_cast<const uint4*>(p.k + (static_cast<int64_t>(src) * p.Hkv + hk) * kD) + ch) : zero;
+      // Delta kernel, few salient keys: their K and dV rows (16 slots x 16 chunks of 16 bytes, one per thread,
+      // zeros past the list) are requested now and written to shared memory after pass A, so that nothing of
+      // the item's set-up stands between the softmax threads and the first logits.
+      uint4 early_k = make_uint4(0, 0, 0, 0), early_v = make_uint4(0, 0, 0, 0);
+      if (!EXACT && fast) {
+        const int r = st_tid >> 4, ch = st_tid & 15;
+        if (r < n_sal) {
+          const int src = p.idx_k ? p.idx_k[sal_begin + r] : p.idx_q[sal_begin + r] + k_shift;
+          early_k = __ldg(reinterpret_cast<const uint4*>(p.k + (static_cast<int64_t>(src) * p.Hkv + hk) * kD) + ch);
           const int64_t vrow = p.v_compact ? static_cast<int64_t>(sal_begin + r) : src;
-          const uint4 vv = src >= 0
-              ? __ldg(reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD) + ch) : zero;
-          *reinterpret_cast<uint4*>(ks_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = kv;
-          *reinterpret_cast<uint4*>(dvs_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = vv;
-          fence_proxy_async_smem();
-          mbar_arrive(&b_full);
+          early_v = __ldg(reinterpret_cast<const uint4*>(p.v + (vrow * p.Hkv + hk) * kD) + ch);
         }
       }
       if (EXACT) {
+        // source rows of the query gather
+        if (half == 0)
+          s_src[row] = q0 + row < q_end ? p.idx_q[sal_begin + q0 + row] : -1;
         // cooperative gather of the query rows (zeros past the list) into the swizzled Q tile
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -599,6 +615,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           m = m_new;
         }
       }
+      if (!EXACT) {
+        if (fast) {
+          const int r = st_tid >> 4, ch = st_tid & 15;
+          *reinterpret_cast<uint4*>(ks_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = early_k;
+          *reinterpret_cast<uint4*>(dvs_smem + (ch >> 3) * kSalHalfBytes + sw128_offset(r, ch & 7)) = early_v;
+          fence_proxy_async_smem();
+          mbar_arrive(&b_full);
+        }
+        if (half == 0) {
+          // source rows of the first gathered tile of pass B (more than kFastSal salient keys)
+          s_src[row] = row < n_sal ? (p.idx_k ? p.idx_k[sal_begin + row] : p.idx_q[sal_begin + row] + k_shift) : -1;
+          s_sal_pos[row] = 0;
+        }
+      }
       // merge the two column halves of each row: m = max, l rescaled to the common maximum
       s_ml[half][row] = make_float2(m, l);
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -607,6 +637,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const float m_all = fmaxf(m, other.x);
         l = l * ex2((m - m_all) * c) + other.y * ex2((other.x - m_all) * c);
         m = m_all;
+      }
+      if (!EXACT) {
+        // mark the query rows of this tile that are salient (they take the exactly attended values); the
+        // epilogue reads the marks after the P dV product, which every thread's arrival on p_full precedes
+        for (int j = st_tid; j < n_sal; j += 256) {
+          const int rr = p.idx_q[sal_begin + j] - q0;
+          if (rr >= 0 && rr < kBQ)
+            s_sal_pos[rr] = static_cast<uint16_t>(j + 1);
+        }
       }
 
       // pass B: salient keys (EXACT: all keys again, with their values)
@@ -775,27 +814,36 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         if (live) {
           const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(old_row + cc / 8);
-          uint4 sal_row[4];
-          if (sal_src) {
+          uint32_t pk[16];
+          float2 d2 = make_float2(0.f, 0.f), n2 = make_float2(0.f, 0.f), q2 = make_float2(0.f, 0.f);
+          if (!sal_src) {
+            const float2 il2 = make_float2(inv_l, inv_l);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 of = __bfloat1622float2(o2[i]);
+              const float2 nv = ffma2(make_float2(__uint_as_float(orr[2 * i]), __uint_as_float(orr[2 * i + 1])), il2, of);
+              d2 = ffma2(nv, of, d2);
+              n2 = ffma2(nv, nv, n2);
+              q2 = ffma2(of, of, q2);
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(nv.x, nv.y);
+              pk[i] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+          } else {
+            // salient query row (a few per sequence): the exactly attended row is the new value
+            uint4 sal_row[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               sal_row[j] = __ldg(sal_src + cc / 8 + j);
-          }
-          const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(sal_row);
-          uint32_t pk[16];
-          const float2 il2 = make_float2(inv_l, inv_l);
-          float2 d2 = make_float2(0.f, 0.f), n2 = make_float2(0.f, 0.f), q2 = make_float2(0.f, 0.f);
+            const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(sal_row);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 of = __bfloat1622float2(o2[i]);
-            float2 nv = ffma2(make_float2(__uint_as_float(orr[2 * i]), __uint_as_float(orr[2 * i + 1])), il2, of);
-            if (sal_src)
-              nv = __bfloat1622float2(x2[i]);
-            d2 = ffma2(nv, of, d2);
-            n2 = ffma2(nv, nv, n2);
-            q2 = ffma2(of, of, q2);
-            __nv_bfloat162 v2 = __floats2bfloat162_rn(nv.x, nv.y);
-            pk[i] = *reinterpret_cast<uint32_t*>(&v2);
+            for (int i = 0; i < 16; ++i) {
+              const float2 of = __bfloat1622float2(o2[i]);
+              const float2 nv = __bfloat1622float2(x2[i]);
+              d2 = ffma2(nv, of, d2);
+              n2 = ffma2(nv, nv, n2);
+              q2 = ffma2(of, of, q2);
+              pk[i] = reinterpret_cast<const uint32_t*>(sal_row)[i];
+            }
           }
           dot += d2.x + d2.y;
           nn += n2.x + n2.y;
@@ -825,19 +873,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // the two halves of a row add their statistics in a fixed order (half 0 + half 1)
         if (half == 1)
           s_st[row] = make_float4(dot, nn, no, 0.f);
-        if (tile_tma)
-          fence_proxy_async_smem();   // the updated tile is read by the TMA stores below
+        if (tile_tma) {
+          fence_proxy_async_smem();   // the updated tile is read by the TMA stores that the producer warp issues
+          mbar_arrive(&c_stored);
+        }
         DYLLM_TRACE(9);
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (tile_tma && st_tid == 0) {
-          tma_store_2d(&tmap_out, kv_smem1, h * kD, q0);
-          tma_store_2d(&tmap_out, kv_smem1 + kHalfBytes, h * kD + 64, q0);
-          if (p.c_cache) {
-            tma_store_2d(&tmap_c, kv_smem1, h * kD, static_cast<int>(q0 + c_delta));
-            tma_store_2d(&tmap_c, kv_smem1 + kHalfBytes, h * kD + 64, static_cast<int>(q0 + c_delta));
-          }
-          tma_store_commit();
-        }
         DYLLM_TRACE(10);
         if (half == 0 && live) {
           const float4 o = s_st[row];
@@ -851,10 +892,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // small shared arrays; then the producer may refill the tile buffers
       tc_fence_before_sync();
       asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (!EXACT && tile_tma && st_tid == 0) {
-        tma_store_wait_read();   // the stores have read the context tile
-        mbar_arrive(&kv1_free);
-      }
       DYLLM_TRACE(6);
     }
   }

@@ -710,8 +710,10 @@ class Attention(nn.Module):
         rows_k32 = None      # response-only steps: the kernel derives the key rows from the query rows
         # algorithmic flops: Q K^T over all keys (sum over sequences of len_q * len_k, equal lengths here)
         flops = 2.0 * ctx.total_seqlen * ctx.max_seqlen_k * H * D
-        # algorithmic bytes: Q and the previous context read, the new context written, K read once
-        nbytes = 3.0 * ctx.total_seqlen * H * D * 2 + ctx.total_seqlen_k * Hkv * D * 2
+        # algorithmic bytes of the fused call: Q and the previous context (straight from the context cache) read, the
+        # new context written twice (the packed tensor that o_proj reads, and the cache rows in place: the reference's
+        # reset_block / reset_full copy after its kernel, attention.py:153,168), K read once
+        nbytes = 4.0 * ctx.total_seqlen * H * D * 2 + ctx.total_seqlen_k * Hkv * D * 2
         with profiling.region("delta_attention", flops, nbytes):
             new_c = attention_sparse_varlen(q, k, dv, c_arena, o_sal, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
                                             ctx.max_seqlen_q, ctx.max_seqlen_k, ctx.total_seqlen, ctx.cu_salientlens,
