@@ -502,7 +502,9 @@ def run_ours(args, cfg, tau):
     traffic = ncu_traffic_bytes() if args.config == 1 and world == 1 else {}
     # dominant kernel of this library; its bound is the roofline that gives the longer time
     mine = {k: v for k, v in prof.items() if v["launches"]}
-    dominant = max(mine, key=lambda k: mine[k]["total_ms"]) if mine else None
+    # (the exchange regions of several ranks are NVLink latency, not a roofline of this GPU: listed, never dominant)
+    compute = {k: v for k, v in mine.items() if not k.endswith(("_exchange", "_all_reduce"))}
+    dominant = max(compute, key=lambda k: compute[k]["total_ms"]) if compute else None
     roofline = None
     if dominant:
         d = mine[dominant]

@@ -151,7 +151,8 @@ def tensor_parallel_cosine_mask(stats: torch.Tensor, threshold: float) -> torch.
     return ops.cosine_mask(stats, threshold)      # raises unless the statistics are fp32 [rows, 3] on a GPU
 
 
-def _gathered_ffn(ffn_shard, x: torch.Tensor, idx32, cap_local: int, count_dev, hint: int, out=None, out_row_map=None):
+def _gathered_ffn(ffn_shard, x: torch.Tensor, idx32, cap_local: int, count_dev, hint: int, out=None, out_row_map=None,
+                  region=None):
     """FFN of the sequence-sharded layout: the rows ``x[idx32[:count]]`` of every rank are gathered on all ranks
     (peer-memory stores), ``ffn_shard(matrix, idx_all, capacity, total_dev, hint)`` runs this rank's weight shard
     over all of them, and each partial output row returns to the rank that owns the row, which adds the ranks'
@@ -160,12 +161,17 @@ def _gathered_ffn(ffn_shard, x: torch.Tensor, idx32, cap_local: int, count_dev, 
     comm = get_tp_comm()
     if comm is None:
         raise RuntimeError("the sequence-sharded layout needs the peer-memory exchange (layers.set_tp_comm)")
-    mat, idx_all, prefix, total = comm.gather_rows(x, idx32, count_dev, cap_local)
+    # timed regions (when region timing is on): the two exchanges apart from the GEMMs between them
+    row_bytes = float((hint or cap_local) * x.size(1) * 2 * comm.world)
+    with profiling.region("ffn_gather_exchange", 0.0, row_bytes):
+        mat, idx_all, prefix, total = comm.gather_rows(x, idx32, count_dev, cap_local)
     cap_total = idx_all.numel()
-    y = ffn_shard(mat, idx_all, cap_total, total, hint * comm.world if hint else 0)
+    with profiling.region(*region) if region else contextlib.nullcontext():
+        y = ffn_shard(mat, idx_all, cap_total, total, hint * comm.world if hint else 0)
     if out is None:
         out = torch.empty((cap_local, x.size(1)), dtype=x.dtype, device=x.device)
-    comm.scatter_reduce_rows(y, prefix, cap_total, count_dev, cap_local, out, out_row_map)
+    with profiling.region("ffn_scatter_exchange", 0.0, row_bytes):
+        comm.scatter_reduce_rows(y, prefix, cap_total, count_dev, cap_local, out, out_row_map)
     return out
 
 
@@ -464,8 +470,8 @@ class LLaDAMLP(nn.Module):
             if sequence_sharded():
                 dest = ops.cache_dest_rows(rows_k, ctx.cu_seqlens_k, cm.seq_start_gpu, md.running_seqs_tensor, n_dev)
                 world = _world_size()
-                with profiling.region("swiglu_ffn", 6.0 * rows * world * width * inter, nbytes):
-                    _gathered_ffn(self._ffn_shard, hidden, idx32, cap, n_dev, hint, out=cm.cache, out_row_map=dest)
+                _gathered_ffn(self._ffn_shard, hidden, idx32, cap, n_dev, hint, out=cm.cache, out_row_map=dest,
+                              region=("swiglu_ffn", 6.0 * rows * world * width * inter, nbytes))
             elif self.down_proj.tp_size > 1:
                 with profiling.region("swiglu_ffn", 6.0 * rows * width * inter, nbytes):
                     y = ops.swiglu_ffn(hidden, self.gate_up_proj.weight, self.down_proj.weight, idx32,

@@ -162,18 +162,27 @@ def bench_get_seqs(args):
 
 
 def bench_ffn(args):
+    """SwiGLU FFN on ``--rows`` gathered rows; ``--inter`` sets the intermediate size (12288 / 8 = 1536 is the
+    weight shard of one of eight tensor-parallel ranks).  More than 4096 rows: a random sorted row list over a
+    larger activation (the at-scale workload's batch 64 x 512 response rows)."""
     dev = torch.device("cuda")
-    x = torch.randn(B * L, HID, device=dev).bfloat16()
-    w1 = (torch.randn(2 * INTER, HID, device=dev) * 0.02).bfloat16()
-    w2 = (torch.randn(HID, INTER, device=dev) * 0.02).bfloat16()
-    idx_q, _, _, _ = salient_lists(args.rows, dev)
-    idx32 = idx_q.to(torch.int32)
+    inter = args.inter or INTER
+    if args.rows <= B * R:
+        x = torch.randn(B * L, HID, device=dev).bfloat16()
+        idx_q, _, _, _ = salient_lists(args.rows, dev)
+        idx32 = idx_q.to(torch.int32)
+    else:
+        x = torch.randn(64 * 1024, HID, device=dev).bfloat16()
+        g = torch.Generator().manual_seed(0)
+        idx32 = torch.sort(torch.randperm(x.size(0), generator=g)[: args.rows]).values.to(torch.int32).to(dev)
+    w1 = (torch.randn(2 * inter, HID, device=dev) * 0.02).bfloat16()
+    w2 = (torch.randn(HID, inter, device=dev) * 0.02).bfloat16()
     out = torch.empty(idx32.numel(), HID, device=dev, dtype=torch.bfloat16)
     ms = time_launches(lambda: ops.swiglu_ffn(x, w1, w2, idx32, out=out, a_mode=args.a_mode, tile_n=args.tile_n),
                        args.iters, args.flush)
     s = idx32.numel()
-    flops = 6.0 * s * HID * INTER
-    wbytes = 3.0 * HID * INTER * 2 + s * HID * 2 * 2 + 2.0 * s * INTER * 2
+    flops = 6.0 * s * HID * inter
+    wbytes = 3.0 * HID * inter * 2 + s * HID * 2 * 2 + 2.0 * s * inter * 2
     # the bound is whichever roofline gives the longer time
     hbm, tf, _ = peaks()
     if flops / (tf * 1e12) >= wbytes / (hbm * 1e9):
@@ -418,6 +427,7 @@ def main():
                          "size in all) instead of isolated launches with L2 flushes")
     ap.add_argument("--a-mode", type=int, default=-1)
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--inter", type=int, default=0, help="ffn: intermediate size (default 12288)")
     ap.add_argument("--response-only", action="store_true")
     args = ap.parse_args()
     hbm, tf, src = peaks()
