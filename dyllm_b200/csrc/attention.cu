@@ -192,6 +192,8 @@ __device__ __forceinline__ bool decode_item(const AttnParams& p, int item, AttnI
   return true;
 }
 
+#include "attention_pair.cuh"
+
 // EXACT = false: the delta attention described at the top of this file.
 // EXACT = true: plain softmax attention of the salient query rows against the full K / V of their
 // sequence, o_sal[i] = softmax(q[idx_q[i]] K^T / sqrt(D)) V: the query tile is gathered through idx_q,
@@ -1233,6 +1235,41 @@ int launch_attention(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
   return check_launch(EXACT ? "salient_attention" : "delta_attention");
 }
 
+bool g_pair_smem_set[64] = {};
+
+// Pair decomposition of the delta attention (attention_pair.cuh): one CTA per SM; the default when dV arrives as
+// rows ([keys][d]).  DYLLM_ATTN_PAIR=0 selects the two-CTAs-per-SM kernel above instead.
+bool pair_kernel_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("DYLLM_ATTN_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
+int launch_delta_pair(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tout, const CUtensorMap& tc,
+                      const AttnParams& p_in, cudaStream_t s) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = (dev < 0 || dev >= 64) ? 0 : dev;
+  if (!g_pair_smem_set[dev]) {
+    if (cudaFuncSetAttribute(delta_attention_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kPairSmem)) != cudaSuccess)
+      return set_error(DYLLM_ERR_CUDA, "attention: cudaFuncSetAttribute failed: %s",
+                       cudaGetErrorString(cudaGetLastError()));
+    g_pair_smem_set[dev] = true;
+  }
+  AttnParams p = p_in;
+  const int64_t items = static_cast<int64_t>(p.batch) * p.H * ((p.n_qtiles + 1) / 2);
+  DYLLM_REQUIRE(items > 0 && items < (1ll << 31), DYLLM_ERR_UNSUPPORTED, "attention: %lld work items",
+                static_cast<long long>(items));
+  p.num_items = static_cast<int>(items);
+  const int64_t resident = sm_count();
+  const unsigned blocks = static_cast<unsigned>(items < resident ? items : resident);
+  DYLLM_LAUNCH(delta_attention_pair_kernel, blocks, kPairThreads, kPairSmem, s, tq, tk, tout, tc, p);
+  return check_launch("delta_attention(pair)");
+}
+
 }  // namespace
 }  // namespace dyllm
 
@@ -1334,7 +1371,11 @@ int dyllm_attention_sparse_varlen(const void* q, const void* k, const void* v, c
                            static_cast<uint64_t>(num_heads) * kD, static_cast<uint64_t>(num_heads) * kD, kBQ, 64, true);
   if (rc != DYLLM_OK)
     return rc;
-  rc = launch_attention<false>(tq, tk, tk, tout, tc, p, blocks, s);
+  if (v_mn_major && pair_kernel_enabled()) {
+    rc = launch_delta_pair(tq, tk, tout, tc, p, s);
+  } else {
+    rc = launch_attention<false>(tq, tk, tk, tout, tc, p, blocks, s);
+  }
   if (rc != DYLLM_OK)
     return rc;
   DYLLM_LAUNCH(attention_finalize_kernel, cdiv_i(total_q, 256), 256, 0, s, p.partial, num_heads, total_q, cosine_stats,

@@ -85,12 +85,20 @@ Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_
   const int h = (hint > 0 && hint < M) ? hint : M;
   const int mt_h = cdiv_i(h, kGemmBM);
   Plan plan;
-  if (tile_n == 0)
+  if (tile_n == 0) {
     tile_n = (n % 128 == 0 && mt_h * (n / 128) >= sms * 3 / 4) ? 128 : 64;
+    // Many rows, plain product: 256 x 256 tiles.  The MMA warp issues one tcgen05.mma per ~68 clocks, which is
+    // what an N = 128 product keeps the tensor pipe busy for; N = 256 doubles the work per instruction, and the
+    // tile moves 62 B/clk of operands from L2 where 256 x 128 moves 94.
+    if (!swiglu && allow_tall && n % 256 == 0 && h > 256 && cdiv_i(h, 2 * kGemmBM) * (n / 256) >= sms * 3 / 4)
+      tile_n = 256;
+  }
   plan.tile_n = tile_n;
   const int n_tiles = n / tile_n;
   // many rows: the 128-row tile is limited by weight traffic from L2; 256-row tiles halve it
-  plan.tall = allow_tall && tile_n == 128 && h > 256 && cdiv_i(h, 2 * kGemmBM) * n_tiles >= sms;
+  plan.tall = allow_tall && h > 256 &&
+              ((tile_n == 128 && cdiv_i(h, 2 * kGemmBM) * n_tiles >= sms) ||
+               (tile_n == 256 && cdiv_i(h, 2 * kGemmBM) * n_tiles >= sms * 3 / 4));
   plan.two_per_sm = tile_n == 64 && mt_h <= 2;
   plan.slots = plan.two_per_sm ? 2 * sms : sms;
   // the grid carries the splits a single live row tile would use; CTAs of splits that the live count
@@ -145,7 +153,7 @@ __global__ void cache_dest_rows_kernel(const int64_t* __restrict__ row_idx, cons
 
 // a_mode: 0 = A rows m0..m0+127 by one TMA box (A dense or already staged), 1 = TMA gather4 through
 // p.a_idx.  n is the number of output columns per weight block (the intermediate size for SWIGLU).
-// tile_n: 64 or 128 (0 = choose).  `partial` enables split-K for the non-SwiGLU GEMM.
+// tile_n: 64, 128 or (many rows, no SwiGLU) 256 (0 = choose).  `partial` enables split-K for the non-SwiGLU GEMM.
 int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& p_in, int64_t lda, const void* b,
                          int64_t b_total_rows, int n, int rows_hint, float* partial, cudaStream_t stream) {
   GemmParams p = p_in;
@@ -164,7 +172,9 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
     return DYLLM_OK;
   const Plan plan = make_plan(swiglu, p.M, rows_hint, n, p.K, tile_n, partial != nullptr,
                               a_mode == 0 && !p.tile_expert);
-  DYLLM_REQUIRE((plan.tile_n == 64 || plan.tile_n == 128) && n % plan.tile_n == 0, DYLLM_ERR_UNSUPPORTED,
+  DYLLM_REQUIRE((plan.tile_n == 64 || plan.tile_n == 128 || (plan.tile_n == 256 && plan.tall && !swiglu)) &&
+                    n % plan.tile_n == 0,
+                DYLLM_ERR_UNSUPPORTED,
                 "gemm: tile_n %d does not divide N = %d", plan.tile_n, n);
   p.status_word = device_status_word();
   p.n_total = n;
@@ -190,6 +200,8 @@ int launch_gathered_gemm(bool swiglu, int a_mode, int tile_n, const GemmParams& 
   if (plan.tall) {
     if (swiglu)
       rc = launch_one<128, true, 0, 3, 1, 2>(ta, tb, p, plan.grid, stream);
+    else if (plan.tile_n == 256)
+      rc = launch_one<256, false, 0, 3, 1, 2>(ta, tb, p, plan.grid, stream);
     else
       rc = launch_one<128, false, 0, 4, 1, 2>(ta, tb, p, plan.grid, stream);
   } else if (swiglu) {

@@ -148,7 +148,7 @@ int dyllm_cache_scatter_update(void* cache, const void* new_rows, const int64_t*
  * used to shape the launch, and no host synchronisation is needed.  a_mode selects how activation
  * rows reach the tensor cores: 0 = the indexed rows are first staged into a compact buffer of the
  * workspace and then loaded as plain TMA boxes (default when negative), 1 = TMA gather4 straight from
- * x.  tile_n = 64, 128 or 0 (choose).
+ * x.  tile_n = 64, 128, 256 (plain product with many rows only) or 0 (choose).
  * ---------------------------------------------------------------------------------------------- */
 
 /* Bytes of workspace dyllm_gathered_linear needs for up to max_rows rows (row staging + split-K

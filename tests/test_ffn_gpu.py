@@ -185,3 +185,25 @@ def test_swiglu_ffn_device_count(cuda_device, bound, live, hint):
     _status_ok()
     _check(out[:live], orc.swiglu_ffn(x[idx[:live].long()], w1, w2), "swiglu device count")
     assert bool((out[live:] == 5.0).all())
+
+
+@pytest.mark.parametrize("rows,k,n,tile_n,with_idx", [(2500, 256, 4096, 0, True), (2500, 256, 4096, 256, True),
+                                                       (4096, 512, 4096, 0, False), (2433, 192, 8192, 0, True)])
+def test_gathered_linear_many_rows_on_256_wide_tiles(cuda_device, rows, k, n, tile_n, with_idx):
+    """Plain products with thousands of rows run on 256 x 256 tiles (two 128-row accumulators per 256-column
+    weight tile); ragged last row tile, index list or every row."""
+    from dyllm_b200 import ops
+
+    g = torch.Generator().manual_seed(rows + n)
+    total = rows * 2 if with_idx else rows
+    x = torch.randn(total, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    if with_idx:
+        idx = torch.sort(torch.randperm(total, generator=g)[:rows]).values.to(torch.int32)
+        want = x.float()[idx.long()] @ w.float().t()
+        got = ops.gathered_linear(x.to(cuda_device), w.to(cuda_device), idx.to(cuda_device), tile_n=tile_n)
+    else:
+        want = x.float() @ w.float().t()
+        got = ops.gathered_linear(x.to(cuda_device), w.to(cuda_device), None, num_rows=rows, rows_hint=rows, tile_n=tile_n)
+    _status_ok()
+    _check(got, want.bfloat16(), "gathered_linear on 256-wide tiles")
