@@ -1,7 +1,7 @@
 """Builds the reference's own CUDA extension sources for sm_100 into ``oracle/_ref/`` (test infrastructure).
 
-The sources are compiled where they lie in a checkout of the reference (``--ref``, default
-``/root/reference``); nothing is copied.  The flags are those of the reference's ``setup.py:46-67`` with
+The sources are compiled where they lie in a checkout of the reference (``--ref``, or the environment variable
+``DYLLM_REFERENCE_ROOT``); nothing is copied.  The flags are those of the reference's ``setup.py:46-67`` with
 ``TORCH_CUDA_ARCH_LIST=10.0`` (``setup.py:12-17``: ``-gencode=arch=compute_100,code=sm_100``), ``-DDYLLM_NO_H100``
 (``setup.py:83-87``: no Hopper sources without ``compute_90a``) and without the head_dim-512 files (no
 configuration of this package uses that head size).  The result is the reference's ``mma.sync`` kernel
@@ -84,7 +84,7 @@ def load_ref(name: str):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("DYLLM_REFERENCE_ROOT", "/root/reference"))
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args()
     if not os.path.isdir(os.path.join(a.ref, "dyllm", "csrc")):
