@@ -250,12 +250,14 @@ class ColumnParallelLinear(LinearBase):
         return _project(x, self.weight, self.bias)
 
     def forward_gathered(self, x: torch.Tensor, idx32: torch.Tensor | None, num_rows: int, num_rows_dev=None,
-                         rows_hint: int = 0, split_col: int = 0):
+                         rows_hint: int = 0, split_col: int = 0, out=None):
         """``self(x[idx])`` on the tcgen05 GEMM; ``num_rows`` may be a capacity with the live count on the
         device.  ``idx32`` None: ``x`` already holds the rows packed in list order.  With ``split_col`` the
-        output columns are returned as two tensors (K and V halves)."""
+        output columns are returned as two tensors (K and V halves); ``out`` may bring them (a pair)."""
         n_out = self.weight.size(0)
-        if split_col:
+        if out is not None:
+            out, out2 = out if split_col else (out, None)
+        elif split_col:
             out = torch.empty((num_rows, split_col), dtype=x.dtype, device=x.device)
             out2 = torch.empty((num_rows, n_out - split_col), dtype=x.dtype, device=x.device)
         else:

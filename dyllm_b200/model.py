@@ -12,6 +12,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import os
+
 import torch
 from torch import nn
 
@@ -76,6 +78,8 @@ class LLaDAAttention(nn.Module):
         packed in list order (``RMSNorm.forward_with_rows``); the K/V projection then reads them directly."""
         ctx, md = get_context(), get_metadata()
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        if not ctx.is_full and salient_rows is not None and _kv_overlap() and ctx.idx_salient_row.numel():
+            return self._forward_sparse_overlapped(positions, hidden_states, salient_rows)
         q = self.q_proj(hidden_states).view(-1, H, D)
         if self.q_norm is not None:
             q = self.q_norm.forward_heads_(q)
@@ -115,6 +119,55 @@ class LLaDAAttention(nn.Module):
         out = self.o_proj(o.flatten(-2, -1))
         self.k_cache.finish(md.finished_seqs)
         return out
+
+
+_side_streams: dict = {}
+
+
+def _kv_overlap() -> bool:
+    """DYLLM_KV_OVERLAP=1: the K/V branch of a sparse step (projection of the salient rows, K/V cache update) runs
+    on a second stream beside the query projection."""
+    return os.environ.get("DYLLM_KV_OVERLAP", "0") == "1"
+
+
+def _forward_sparse_overlapped(self, positions, hidden_states, salient_rows):
+    ctx, md = get_context(), get_metadata()
+    H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+    cap = ctx.idx_salient_row.numel()
+    n_dev, hint = ctx.num_salient_dev, ctx.salient_hint
+    dev = hidden_states.device
+    main = torch.cuda.current_stream(dev)
+    side = _side_streams.get(dev)
+    if side is None:
+        side = _side_streams[dev] = torch.cuda.Stream(dev)
+    # outputs of the side branch are allocated here, on the stream that uses them afterwards
+    k_new = torch.empty((cap, self.kv_size), dtype=hidden_states.dtype, device=dev)
+    v_new = torch.empty((cap, self.kv_size), dtype=hidden_states.dtype, device=dev)
+    dv = torch.empty((cap, Hkv, D), dtype=hidden_states.dtype, device=dev)
+    rows_k = ctx.idx_salient_row_k if ctx.idx_salient_row_k is not None else ctx.idx_salient_row
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        self.kv_proj.forward_gathered(salient_rows, None, cap, n_dev, hint, split_col=self.kv_size, out=(k_new, v_new))
+        k3 = k_new.view(cap, Hkv, D)
+        if self.k_norm is not None:
+            k3 = self.k_norm.forward_heads_(k3, n_dev)
+        ops.kv_cache_update(k3, v_new.view(cap, Hkv, D), rows_k, positions, ctx.idx_salient_row,
+                            self.rotary_emb.cos_sin_cache.view(-1, D), ctx.cu_seqlens_k, self.k_cache.seq_start_gpu,
+                            self.attn.v_cache.seq_start_gpu, md.running_seqs_tensor, self.k_cache.cache,
+                            self.attn.v_cache.cache, n_dev, dv=dv)
+    q = self.q_proj(hidden_states).view(-1, H, D)
+    if self.q_norm is not None:
+        q = self.q_norm.forward_heads_(q)
+    q = self.rotary_emb.rotate(positions, q)
+    main.wait_stream(side)
+    k_full = self.k_cache.get_seqs(md.running_seqs_tensor, allow_view=True, seq_ids_list=md.running_seqs)
+    o = self.attn(q, k_full.view(-1, Hkv, D), v_new.view(cap, Hkv, D), dv=dv)
+    out = self.o_proj(o.flatten(-2, -1))
+    self.k_cache.finish(md.finished_seqs)
+    return out
+
+
+LLaDAAttention._forward_sparse_overlapped = _forward_sparse_overlapped
 
 
 def _input_norm(layer, hidden_states, residual):
