@@ -159,17 +159,9 @@ delta_attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       PairItem it;
       if (!decode_pair(p, item, it))
         continue;
-      if (n_items > 0)
-        mbar_wait(&q_free, (n_items - 1) & 1, &abort_flag, p.status_word, 401);
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&q_full, it.live1 ? 2 * kTileBytes : kTileBytes);
-        for (int s = 0; s < (it.live1 ? 2 : 1); ++s) {
-          tma_load_2d(q_smem + s * kTileBytes, &tmap_q, &q_full, it.h * kD, it.q0 + s * kBQ);
-          tma_load_2d(q_smem + s * kTileBytes + kHalfBytes, &tmap_q, &q_full, it.h * kD + 64, it.q0 + s * kBQ);
-        }
-      }
-      __syncwarp();
-      for (int kt = 0; kt < it.num_kt; ++kt, ++ku) {
+      // The first K tiles go out before the Q tiles: their stages have been free since the end of the previous
+      // pair's pass A, while Q is only released by that pair's last product with it.
+      auto load_k = [&](int kt) {
         const int st = ku % kPairKStages;
         mbar_wait(&k_empty[st], ((ku / kPairKStages) & 1) ^ 1, &abort_flag, p.status_word, 402);
         if (lane == 0) {
@@ -179,7 +171,32 @@ delta_attention_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
           tma_load_2d(dst + kPairKHalfBytes, &tmap_k, &k_full[st], it.hk * kD + 64, it.k_begin + kt * kPairKeys);
         }
         __syncwarp();
+        ++ku;
+      };
+      int kt = 0;
+      for (; kt < it.num_kt && kt < kPairKStages; ++kt)
+        load_k(kt);
+      if (n_items > 0)
+        mbar_wait(&q_free, (n_items - 1) & 1, &abort_flag, p.status_word, 401);
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&q_full, it.live1 ? 2 * kTileBytes : kTileBytes);
+        for (int s = 0; s < (it.live1 ? 2 : 1); ++s) {
+          tma_load_2d(q_smem + s * kTileBytes, &tmap_q, &q_full, it.h * kD, it.q0 + s * kBQ);
+          tma_load_2d(q_smem + s * kTileBytes + kHalfBytes, &tmap_q, &q_full, it.h * kD + 64, it.q0 + s * kBQ);
+        }
+        // the Q tiles of this CTA's next pair into L2: they are read from HBM for the first time
+        PairItem nx;
+        const int next = item + gridDim.x;
+        if (next < p.num_items && decode_pair(p, next, nx)) {
+          for (int s = 0; s < (nx.live1 ? 2 : 1); ++s) {
+            tma_prefetch_2d(&tmap_q, nx.h * kD, nx.q0 + s * kBQ);
+            tma_prefetch_2d(&tmap_q, nx.h * kD + 64, nx.q0 + s * kBQ);
+          }
+        }
       }
+      __syncwarp();
+      for (; kt < it.num_kt; ++kt)
+        load_k(kt);
       ++n_items;
     }
   } else if (warp == 1) {
