@@ -114,7 +114,7 @@ Plan make_plan(bool swiglu, int M, int hint, int n, int K, int tile_n, bool can_
     m_groups = kSplitRows / kGemmBM;
   const int mt_all = cdiv_i(M, bm);
   m_groups = m_groups > mt_all ? mt_all : m_groups;
-  plan.grid = dim3(n_tiles, m_groups < 1 ? 1 : m_groups, plan.splits);
+  plan.grid = dim3(n_tiles, plan.splits, m_groups < 1 ? 1 : m_groups);   // row groups last: see gemm.cuh
   return plan;
 }
 

@@ -4,8 +4,10 @@
 //   D[m, n] = sum_k A[a_idx[m], k] * B[b_row0(m_tile) + n, k]          (fp32 accumulation in TMEM)
 //
 // The number of live rows is read on the device (m_count_dev), so a launch needs no host knowledge of
-// it: the grid is (n tiles, row groups, k splits) and every CTA walks over the row tiles
-// blockIdx.y, blockIdx.y + gridDim.y, ... that lie below the live count.
+// it: the grid is (n tiles, k splits, row groups) and every CTA walks over the row tiles
+// blockIdx.z, blockIdx.z + gridDim.z, ... that lie below the live count.  The row groups come last in the grid so
+// that the CTAs of the first row tile, all splits, are dispatched before the CTAs of row groups that usually find
+// nothing to do (they return at once, but each takes a turn in an SM slot first).
 //
 // Warp roles (6 warps):
 //   warp 0      producer: weight tiles by TMA (128-byte swizzle); activation rows by one TMA box per
@@ -38,7 +40,7 @@ struct GemmParams {
   __nv_bfloat16* out2;         // columns >= split_col go here (column - split_col); null = no split
   int64_t ldc2;
   int split_col;
-  float* partial;              // split-K: fp32 [gridDim.z][split_rows][n_total]; null = no split-K
+  float* partial;              // split-K: fp32 [gridDim.y][split_rows][n_total]; null = no split-K
   int* split_tickets;          // split-K: arrival counter per (row tile, column tile), zero between launches
   int split_rows;              // split-K is used only while the live row count is <= split_rows
   int split_slots;             // CTAs the device runs at once; the live split count is derived from it
@@ -101,7 +103,7 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   const int n_tile = blockIdx.x;
   const int m_count = p.m_count_dev ? min(*p.m_count_dev, p.M) : p.M;
-  if (static_cast<int>(blockIdx.y) * BM >= m_count)
+  if (static_cast<int>(blockIdx.z) * BM >= m_count)
     return;
   // split-K only while the live rows fit the partial buffer; otherwise split 0 runs the whole K range
   const int num_kt_all = p.K / BK;
@@ -110,13 +112,13 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   int splits = 1;
   if (p.partial != nullptr) {
     splits = m_count <= p.split_rows
-                 ? effective_splits((m_count + BM - 1) / BM, gridDim.x, p.split_slots, gridDim.z, num_kt_all)
+                 ? effective_splits((m_count + BM - 1) / BM, gridDim.x, p.split_slots, gridDim.y, num_kt_all)
                  : 1;
-    if (static_cast<int>(blockIdx.z) >= splits)
+    if (static_cast<int>(blockIdx.y) >= splits)
       return;
     if (splits > 1) {
       const int per = (num_kt_all + splits - 1) / splits;
-      kt_begin = min(static_cast<int>(blockIdx.z) * per, num_kt_all);
+      kt_begin = min(static_cast<int>(blockIdx.y) * per, num_kt_all);
       kt_end = min(kt_begin + per, num_kt_all);
       write_partial = true;
     }
@@ -162,7 +164,7 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     int it = 0;
-    for (int mt = blockIdx.y; mt * BM < m_count; mt += gridDim.y) {
+    for (int mt = blockIdx.z; mt * BM < m_count; mt += gridDim.z) {
       const int m0 = mt * BM;
       const int b_row0 = (p.tile_expert ? p.tile_expert[mt] : 0) * p.b_rows_per_expert + n_tile * BNH;
       int rows4[4] = {0, 0, 0, 0};
@@ -199,7 +201,7 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------------------------------------------ MMA issuer
     constexpr uint32_t idesc = umma_idesc_bf16(kGemmBM, BN, 0, 0);
     int it = 0, ti = 0;
-    for (int mt = blockIdx.y; mt * BM < m_count; mt += gridDim.y, ++ti) {
+    for (int mt = blockIdx.z; mt * BM < m_count; mt += gridDim.z, ++ti) {
       // MT = 1: accumulators alternate; MT = 2: both belong to this tile and barrier 0 guards them
       const int acc = MT == 1 ? (ti & 1) : 0;
       const uint32_t use = MT == 1 ? (ti >> 1) : ti;
@@ -237,7 +239,7 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int q = warp & 3;            // tensor-memory lane quarter this warp may read
     const int row = q * 32 + lane;     // accumulator row == logical row m0 + row
     int ti = 0;
-    for (int mt = blockIdx.y; mt * BM < m_count; mt += gridDim.y, ++ti) {
+    for (int mt = blockIdx.z; mt * BM < m_count; mt += gridDim.z, ++ti) {
       const int acc = MT == 1 ? (ti & 1) : 0;
       const uint32_t use = MT == 1 ? (ti >> 1) : ti;
       mbar_wait(&tmem_full_bar[acc], use & 1, &abort_flag, p.status_word, 204);
@@ -260,7 +262,7 @@ gathered_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         dst = p.out + static_cast<int64_t>(store ? out_row : 0) * p.ldc + n0;
       float* pdst = nullptr;
       if (write_partial)
-        pdst = p.partial + (static_cast<int64_t>(blockIdx.z) * p.split_rows + (live ? m : 0)) * p.n_total + n0;
+        pdst = p.partial + (static_cast<int64_t>(blockIdx.y) * p.split_rows + (live ? m : 0)) * p.n_total + n0;
 
 #pragma unroll 1
       for (int c0 = 0; c0 < BNH; c0 += 32) {
