@@ -88,3 +88,38 @@ def test_oracle_fused_offset_matches_reference_kernel(golden):
     got = orc.fused_offset(c["idxs"], c["cu_prompt"], c["cu_sal"])
     assert torch.equal(got, rec["fused_offset"][:n])
     assert bool((rec["fused_offset"][n:] == -1).all())       # entries past the device-side count stay untouched
+
+
+def test_unmasking_rule_reproduces_the_reference_samplers_picks():
+    """oracle.confidence_unmask against the picks that the reference's LLaDASampler made on its own candidate
+    confidences (tests/golden/llada_tokens_small.pt, written by make_token_golden.py from the reference's step loop):
+    every step of the generation, both sequences."""
+    import os
+
+    path = os.path.join(os.path.dirname(__file__), "golden", "llada_tokens_small.pt")
+    fx = torch.load(path, weights_only=False)
+    cfg, mask_id = fx["cfg"], fx["mask_id"]
+    block, prompt, gen = cfg["block"], cfg["prompt"], cfg["gen"]
+    steps_per_block = cfg["steps"] * block // gen
+    num_transfer = block // steps_per_block
+    checked = 0
+    for step, rec in enumerate(fx["steps"]):
+        start = prompt + min(step // steps_per_block, gen // block - 1) * block
+        for cands, picks, (gap, _lead) in zip(rec["candidates"], rec["picks"], rec["margins"]):
+            # the recorded confidences are an fp32 restatement of the scores the reference's sampler sorted (its
+            # own come from bf16 logits): where the two best candidates lie closer than that difference the
+            # reference's order is not recoverable from the record
+            if gap < 5e-3:
+                continue
+            conf = torch.full((1, block), -1.0)
+            best = torch.zeros((1, block), dtype=torch.int64)
+            tokens = torch.zeros((1, prompt + gen), dtype=torch.int64)      # 0 = some unmasked token
+            for pos, c, tok, _lead in cands:
+                assert start <= pos < start + block
+                conf[0, pos - start], best[0, pos - start], tokens[0, pos] = c, tok, mask_id
+            after, picked = orc.confidence_unmask(conf, best, tokens, start, block, num_transfer, mask_id)
+            assert picked[0] == sorted(p for p, _ in picks), (step, picked, picks)
+            for p, tok in picks:
+                assert int(after[0, p]) == tok
+            checked += 1
+    assert checked >= cfg["steps"]
