@@ -125,9 +125,12 @@ _side_streams: dict = {}
 
 
 def _kv_overlap() -> bool:
-    """DYLLM_KV_OVERLAP=1: the K/V branch of a sparse step (projection of the salient rows, K/V cache update) runs
-    on a second stream beside the query projection."""
-    return os.environ.get("DYLLM_KV_OVERLAP", "0") == "1"
+    """The K/V branch of a sparse step (projection of the salient rows, K/V cache update) runs on a second stream
+    beside the query projection, whose cuBLAS kernel leaves SMs idle in its last wave (DYLLM_KV_OVERLAP=0: one
+    stream).  Not with this package's own GEMM for the all-row projections: the two would share its workspace."""
+    from . import layers
+
+    return os.environ.get("DYLLM_KV_OVERLAP", "1") != "0" and layers._projection_backend == "cublas"
 
 
 def _forward_sparse_overlapped(self, positions, hidden_states, salient_rows):
